@@ -1,0 +1,422 @@
+#!/usr/bin/env python
+"""Benchmark of the attention hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload prefill|decode]
+
+Headline workload (N=1): BASELINE config 2 -- varlen causal batch prefill, bf16, batch 16, 32 q heads / 8 kv
+heads, hdim 128, lengths uniform in [512, 4096] from a seed.  `value` is causal-effective TFLOP/s
+(4*d*hq*sum L(L+1)/2 FLOP per step) with inputs resident in HBM; `e2e` is the same metric through the public
+API with pinned host buffers, host<->device copies inside the timed region.  The same run also measures
+BASELINE config 3 (paged split-KV decode, HBM GB/s) and reports it under `extra.decode`.
+With N > 1 (torchrun, one rank per GPU) every rank runs its own seeded batch (no collective on the data path;
+weak scaling) and `extra.long_decode` runs BASELINE config 5: one long context sharded by pages across the ranks,
+partial O/LSE merged after one NCCL all-gather.
+
+`--impl reference` times the CPU statement of the same path (the oracle; the reference's own kernels need
+ROCm + ck_tile and cannot run here) on the host cores, on a bounded sample of the same workload.
+All inputs are synthetic (seeded N(0,1)), as the reference's own profiler generates them.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+from flashck_b200.utils.inputs import iota_shuffle, to_seqstarts, uniform_seqlens  # noqa: E402
+
+HQ, HKV, D = 32, 8, 128
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"hbm_gbs": p["hbm_gbs"], "bf16_tflops": p["bf16_tflops"], "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+# ----------------------------------------------------------------------------------------------------
+# clocks
+# ----------------------------------------------------------------------------------------------------
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons of one GPU every 200 ms while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "200"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        sm, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [x.strip() for x in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx = float(parts[1])
+            except ValueError:
+                continue
+            for n, val in zip(names, parts[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(n)
+        sm.sort()
+        med = sm[len(sm) // 2] if sm else None
+        return {"sm_mhz": med, "sm_max_mhz": mx, "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ----------------------------------------------------------------------------------------------------
+# workloads
+# ----------------------------------------------------------------------------------------------------
+def make_prefill(seed: int, device, batch=16, lo=512, hi=4096):
+    lens = uniform_seqlens(batch, lo, hi, seed)
+    cu = to_seqstarts(lens)
+    total = int(cu[-1])
+    g = torch.Generator(device=device).manual_seed(seed)
+    q = torch.randn(total, HQ, D, generator=g, device=device, dtype=torch.float32).to(torch.bfloat16)
+    k = torch.randn(total, HKV, D, generator=g, device=device, dtype=torch.float32).to(torch.bfloat16)
+    v = torch.randn(total, HKV, D, generator=g, device=device, dtype=torch.float32).to(torch.bfloat16)
+    flops = 4.0 * D * HQ * sum(L * (L + 1) / 2 for L in lens)
+    return {"lens": lens, "cu": cu.to(device), "q": q, "k": k, "v": v, "flops": flops, "total": total,
+            "max_len": max(lens)}
+
+
+def make_decode(seed: int, device, batch=64, lo=1024, hi=32768, page=16, hq=HQ, hkv=HKV, lens=None):
+    lens = lens or uniform_seqlens(batch, lo, hi, seed)
+    batch = len(lens)
+    pages = [-(-L // page) for L in lens]
+    total_pages = sum(pages)
+    perm = iota_shuffle(total_pages, seed)
+    table = torch.zeros((batch, max(pages)), dtype=torch.int32)
+    off = 0
+    for b, n in enumerate(pages):
+        table[b, :n] = perm[off:off + n]
+        off += n
+    g = torch.Generator(device=device).manual_seed(seed + 1)
+    kpool = torch.empty(total_pages, page, hkv, D, device=device, dtype=torch.bfloat16)
+    vpool = torch.empty(total_pages, page, hkv, D, device=device, dtype=torch.bfloat16)
+    chunk = max(1, (1 << 28) // (page * hkv * D))  # fill in pieces: fp32 randn of the whole pool would double memory
+    for s in range(0, total_pages, chunk):
+        e = min(total_pages, s + chunk)
+        kpool[s:e] = torch.randn(e - s, page, hkv, D, generator=g, device=device, dtype=torch.float32)
+        vpool[s:e] = torch.randn(e - s, page, hkv, D, generator=g, device=device, dtype=torch.float32)
+    q = torch.randn(batch, 1, hq, D, generator=g, device=device, dtype=torch.float32).to(torch.bfloat16)
+    kv_bytes = sum(lens) * hkv * 2 * D * 2
+    algo_bytes = kv_bytes + q.numel() * 2 * 2 + 4 * total_pages  # K+V once, Q read, O write, block table
+    return {"lens": lens, "q": q, "k": kpool, "v": vpool, "table": table.to(device),
+            "seqlen": torch.tensor(lens, dtype=torch.int32, device=device), "bytes": float(algo_bytes),
+            "page": page, "hq": hq, "hkv": hkv}
+
+
+def time_steps(fn, steps, warmup, barrier=None):
+    """Device time of `steps` calls of fn, in ms (CUDA events on the current stream)."""
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    if barrier:
+        barrier()
+    torch.cuda.synchronize()
+    beg, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    beg.record()
+    for _ in range(steps):
+        fn()
+    end.record()
+    torch.cuda.synchronize()
+    if barrier:
+        barrier()
+    return beg.elapsed_time(end)
+
+
+# ----------------------------------------------------------------------------------------------------
+# CPU baseline (the oracle) -- only this leg and the reference arm touch oracle/
+# ----------------------------------------------------------------------------------------------------
+def cpu_prefill_sample(w, budget_flops=1.5e12):
+    from oracle import cpu as oracle
+    lens, cu = w["lens"], w["cu"].cpu()
+    chosen, fl = [], 0.0
+    for b in sorted(range(len(lens)), key=lambda i: lens[i]):
+        f = 4.0 * D * HQ * lens[b] * (lens[b] + 1) / 2
+        if chosen and fl + f > budget_flops:
+            break
+        chosen.append(b)
+        fl += f
+    parts = [slice(int(cu[b]), int(cu[b + 1])) for b in chosen]
+    q = torch.cat([w["q"][s] for s in parts]).cpu()
+    k = torch.cat([w["k"][s] for s in parts]).cpu()
+    v = torch.cat([w["v"][s] for s in parts]).cpu()
+    cu_s = to_seqstarts([lens[b] for b in chosen])
+    t0 = time.perf_counter()
+    oracle.fmha_fwd(q, k, v, seqstart_q=cu_s, seqstart_k=cu_s, mask_type=1, window=(-1, 0))
+    dt = time.perf_counter() - t0
+    return {"value": fl / dt / 1e12, "unit": "TFLOP/s", "cores": oracle.num_threads(), "kind": "port",
+            "sample": f"{len(chosen)} shortest of {len(lens)} sequences ({sum(lens[b] for b in chosen)} tokens, "
+                      f"{fl:.3g} FLOP) in {dt:.2f} s", "seconds": dt}
+
+
+def cpu_decode_sample(w, nseq=8):
+    from oracle import cpu as oracle
+    lens = w["lens"][:nseq]
+    page = w["page"]
+    # compact the pages of the sampled sequences into a small host pool
+    table = w["table"][:nseq].cpu()
+    npages = [-(-L // page) for L in lens]
+    ids = torch.cat([table[b, :n] for b, n in enumerate(npages)]).long()
+    kpool, vpool = w["k"][ids.to(w["k"].device)].cpu(), w["v"][ids.to(w["k"].device)].cpu()
+    new_table = torch.zeros((nseq, max(npages)), dtype=torch.int32)
+    off = 0
+    for b, n in enumerate(npages):
+        new_table[b, :n] = torch.arange(off, off + n, dtype=torch.int32)
+        off += n
+    q = w["q"][:nseq].cpu()
+    sl = torch.tensor(lens, dtype=torch.int32)
+    t0 = time.perf_counter()
+    oracle.fmha_fwd(q, kpool, vpool, seqlen_k=sl, block_table=new_table)
+    dt = time.perf_counter() - t0
+    nbytes = sum(lens) * w["hkv"] * 2 * D * 2
+    return {"value": nbytes / dt / 1e9, "unit": "GB/s", "cores": oracle.num_threads(), "kind": "port",
+            "sample": f"first {nseq} of {len(w['lens'])} sequences ({sum(lens)} tokens) in {dt:.2f} s", "seconds": dt}
+
+
+# ----------------------------------------------------------------------------------------------------
+def run_reference(args, rank):
+    """Reference arm: the CPU statement of the path on the host cores (rank 0 only)."""
+    if rank != 0:
+        return
+    dev = torch.device("cpu")
+    w = make_prefill(1234, dev)
+    from oracle import cpu as oracle
+    # bounded sample per step so that warmup + steps end within minutes
+    budget = 3.0e11
+    samples = []
+    for _ in range(args.warmup):
+        cpu_prefill_sample(w, budget_flops=budget / 4)
+    t_all = 0.0
+    for _ in range(args.steps):
+        s = cpu_prefill_sample(w, budget_flops=budget)
+        samples.append(s)
+        t_all += s["seconds"]
+    val = sum(s["value"] * s["seconds"] for s in samples) / t_all
+    line = {
+        "impl": "reference", "metric": "prefill_fmha_tflops", "value": val, "unit": "TFLOP/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * t_all / args.steps, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "varlen causal batch prefill (BASELINE config 2): batch 16, 32/8 heads, hdim 128, "
+                               "L~U[512,4096] seed 1234", "note": "CPU statement of the path (oracle port); the "
+                               "reference's own kernels need ROCm + ck_tile"},
+        "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": oracle.num_threads(), "kind": "port",
+                         "sample": samples[-1]["sample"]},
+        "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-decode", action="store_true")
+    ap.add_argument("--small", action="store_true", help="reduced sizes (for profiler captures)")
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+
+    from flashck_b200 import ops
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback for the product path)")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=device)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+
+    def max_over_ranks(x: float) -> float:
+        if dist is None:
+            return x
+        t = torch.tensor([x], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def sum_over_ranks(x: float) -> float:
+        if dist is None:
+            return x
+        t = torch.tensor([x], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        return float(t.item())
+
+    peaks = load_peaks()
+    steps, warmup = args.steps, max(args.warmup, 3)
+
+    # ------------------------------------------------------------------ prefill (headline)
+    if args.small:
+        w = make_prefill(1234 + rank, device, batch=4, lo=512, hi=2048)
+    else:
+        w = make_prefill(1234 + rank, device)
+
+    def prefill_step():
+        return ops.fmha_fwd_var_len(w["q"], w["k"], w["v"], w["cu"], w["cu"], w["max_len"], causal=True,
+                                    return_lse=True)
+
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    ms = time_steps(prefill_step, steps, warmup, barrier)
+    ms = max_over_ranks(ms)
+    clocks = sampler.stop()
+    total_flops = sum_over_ranks(w["flops"])
+    value = total_flops * steps / (ms * 1e-3) / 1e12
+    kernel_tflops = w["flops"] * steps / (ms * 1e-3) / 1e12  # per GPU; the step is one kernel launch
+
+    # e2e: pinned host inputs -> device -> kernel -> host outputs, every step
+    hq_, hk_, hv_ = (w[n].cpu().pin_memory() for n in ("q", "k", "v"))
+    dq, dk, dv_ = torch.empty_like(w["q"]), torch.empty_like(w["k"]), torch.empty_like(w["v"])
+    ho = torch.empty_like(hq_).pin_memory()
+    hl = torch.empty((HQ, w["total"]), dtype=torch.float32).pin_memory()
+
+    def prefill_e2e():
+        dq.copy_(hq_, non_blocking=True)
+        dk.copy_(hk_, non_blocking=True)
+        dv_.copy_(hv_, non_blocking=True)
+        o, lse = ops.fmha_fwd_var_len(dq, dk, dv_, w["cu"], w["cu"], w["max_len"], causal=True, return_lse=True)
+        ho.copy_(o, non_blocking=True)
+        hl.copy_(lse, non_blocking=True)
+
+    e2e_steps = max(3, min(steps, 10))
+    ms_e2e = max_over_ranks(time_steps(prefill_e2e, e2e_steps, 3, barrier))
+    e2e_val = total_flops * e2e_steps / (ms_e2e * 1e-3) / 1e12
+    h2d = (hq_.numel() + hk_.numel() + hv_.numel()) * 2
+    d2h = ho.numel() * 2 + hl.numel() * 4
+    del hq_, hk_, hv_, dq, dk, dv_, ho, hl
+
+    line = {
+        "metric": "prefill_fmha_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": steps,
+        "warmup": warmup, "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "varlen causal batch prefill (BASELINE config 2): batch 16 per GPU, 32 q / 8 kv heads, "
+                               "hdim 128, L~U[512,4096], seed 1234+rank" + (" [--small]" if args.small else ""),
+                   "tokens_per_gpu": w["total"], "flops_per_gpu_step": w["flops"],
+                   "flop_count": "causal-effective 4*d*hq*sum L(L+1)/2",
+                   "l2": "inputs (q,k,v,o > 600 MB) larger than the 126 MB L2", "parallelism": f"dp{world}"},
+        "roofline": {"bound": "tensor", "achieved": kernel_tflops, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                     "frac": kernel_tflops / peaks["bf16_tflops"], "traffic": None,
+                     "peak_source": peaks["source"] + " (burst bf16 GEMM)"},
+        "e2e": {"value": e2e_val, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "gpu_launches": steps,
+        "clocks": clocks,
+    }
+    extra = {}
+
+    # ------------------------------------------------------------------ decode (config 3)
+    if not args.no_decode:
+        if args.small:
+            wd = make_decode(4321 + rank, device, batch=16, lo=1024, hi=16384)
+        else:
+            wd = make_decode(4321 + rank, device)
+        S = ops.default_num_splits(len(wd["lens"]))
+        ws = ops.splitkv_workspace(wd["q"], D, S)
+
+        def decode_step():
+            return ops.fmha_fwd_splitkv(wd["q"], wd["k"], wd["v"], seqlen_k=wd["seqlen"], block_table=wd["table"],
+                                        num_splits=S, workspace=ws, return_lse=True)
+
+        sampler = ClockSampler(local_rank)
+        sampler.start()
+        dsteps = max(steps, 20)
+        ms_d = max_over_ranks(time_steps(decode_step, dsteps, warmup, barrier))
+        dclocks = sampler.stop()
+        tot_bytes = sum_over_ranks(wd["bytes"])
+        gbs = tot_bytes * dsteps / (ms_d * 1e-3) / 1e9
+        gbs_gpu = wd["bytes"] * dsteps / (ms_d * 1e-3) / 1e9
+        # e2e decode step: the cache is resident state; the step's inputs are q, lengths and block table
+        hq2 = wd["q"].cpu().pin_memory()
+        hs, ht = wd["seqlen"].cpu().pin_memory(), wd["table"].cpu().pin_memory()
+        dq2, ds, dt_ = torch.empty_like(wd["q"]), torch.empty_like(wd["seqlen"]), torch.empty_like(wd["table"])
+        ho2 = torch.empty_like(hq2).pin_memory()
+
+        def decode_e2e():
+            dq2.copy_(hq2, non_blocking=True)
+            ds.copy_(hs, non_blocking=True)
+            dt_.copy_(ht, non_blocking=True)
+            o, _ = ops.fmha_fwd_splitkv(dq2, wd["k"], wd["v"], seqlen_k=ds, block_table=dt_, num_splits=S,
+                                        workspace=ws, return_lse=True)
+            ho2.copy_(o, non_blocking=True)
+
+        ms_de = max_over_ranks(time_steps(decode_e2e, dsteps, 3, barrier))
+        extra["decode"] = {
+            "metric": "paged_splitkv_decode_hbm_gbs", "value": gbs, "unit": "GB/s", "ms_per_step": ms_d / dsteps,
+            "steps": dsteps,
+            "config": {"workload": "paged split-KV decode (BASELINE config 3): batch 64 per GPU, seqlen_q 1, 32/8 heads, "
+                                   "hdim 128, ctx~U[1024,32768], page 16, shuffled block table"
+                                   + (" [--small]" if args.small else ""),
+                       "tokens_per_gpu": sum(wd["lens"]), "algorithmic_bytes_per_gpu_step": wd["bytes"],
+                       "num_splits": S, "l2": "K/V pool (GBs) larger than L2"},
+            "roofline": {"bound": "hbm", "achieved": gbs_gpu, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                         "frac": gbs_gpu / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"],
+                         "note": "split-KV kernel + combine kernel timed together"},
+            "e2e": {"value": tot_bytes * dsteps / (ms_de * 1e-3) / 1e9, "unit": "GB/s",
+                    "h2d_bytes_per_step": hq2.numel() * 2 + hs.numel() * 4 + ht.numel() * 4,
+                    "d2h_bytes_per_step": ho2.numel() * 2,
+                    "note": "KV cache is resident state; q, lengths and block table are the step's inputs"},
+            "gpu_launches": 2 * dsteps, "clocks": dclocks,
+        }
+        if rank == 0 and not args.no_cpu_baseline:
+            extra["decode"]["cpu_baseline"] = cpu_decode_sample(wd)
+        del wd, ws
+
+    if rank == 0 and not args.no_cpu_baseline:
+        cb = cpu_prefill_sample(w)
+        line["cpu_baseline"] = cb
+    line["extra"] = extra
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

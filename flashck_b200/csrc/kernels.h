@@ -1,0 +1,98 @@
+// Host-side launch interfaces of the flashck_b200 kernels (one per .cu file).
+#pragma once
+
+#include "common.cuh"
+
+namespace fck {
+
+// ---- split-KV combine (combine.cu) ------------------------------------------------------------
+struct CombineParams {
+    const float* lse_acc;  // [bs, hq, S, rows]
+    const float* o_acc;    // [bs, hq, S, rows, dv]
+    void* o;               // [bs, rows, hq, dv] in dtype
+    float* lse;            // [bs, hq, rows] or nullptr
+    int64_t bs, rows, hq, dv, num_splits;
+    int dtype;
+};
+int launch_combine(const CombineParams& p, cudaStream_t stream);
+
+// ---- append-KV (appendkv.cu) --------------------------------------------------------------------
+struct AppendKVParams {
+    void* q;
+    void* k_cache;
+    const void* knew;
+    void* v_cache;
+    const void* vnew;
+    const int32_t* seqlen_k;
+    const int64_t* seqstart_q;     // group mode or nullptr
+    const int64_t* seqstart_knew;  // group mode or nullptr
+    const void* rotary_cos;
+    const void* rotary_sin;
+    const int32_t* block_table;  // nullptr => contiguous cache
+    const int64_t* cache_batch_idx;
+    int64_t batch, seqlen_q, seqlen_k_cap, seqlen_knew;  // group mode: seqlen_q / seqlen_knew are totals
+    int64_t hq, hkv, d, dv, rotary_dim, bt_stride, page;
+    int rope_type;
+    int dtype;
+};
+int launch_appendkv(const AppendKVParams& p, cudaStream_t stream);
+
+// ---- split-KV decode over contiguous / paged K,V (splitkv_decode.cu) -----------------------------
+struct SplitKVParams {
+    const void* q;
+    const void* k;
+    const void* v;
+    float* o_acc;
+    float* lse_acc;  // may be nullptr when num_splits == 1
+    const int64_t* seqstart_q;
+    const int64_t* seqstart_k;
+    const int32_t* seqlen_k;
+    const int32_t* block_table;
+    const int64_t* cache_batch_idx;
+    int64_t batch, seqlen_q, seqlen_k_cap, hq, hkv, d, dv, max_seqlen_q, num_splits;
+    int64_t total_q;    // rows of the q token axis (batch mode: seqlen_q; group mode: seqstart_q[batch])
+    int64_t num_pages;  // paged: pool pages; contiguous: batch rows of the cache (or 0 if unknown)
+    int64_t bt_stride, page;
+    float scale;
+    int mask_type;
+    int64_t wl, wr;
+    int dtype;
+};
+int launch_splitkv_decode(const SplitKVParams& p, cudaStream_t stream);
+// instance parameters (see FlashckSetInstanceParam): "stages", "ctas_per_sm_x100" ...
+int splitkv_set_param(const char* key, int64_t value);
+int splitkv_get_param(const char* key, int64_t* value);
+
+// ---- generic forward / prefill (fmha_fwd_generic.cu): mma.sync tiles, any mask, varlen, paged ----
+struct FwdParams {
+    const void* q;
+    const void* k;
+    const void* v;
+    void* o;
+    float* lse;  // may be nullptr
+    const int64_t* seqstart_q;
+    const int64_t* seqstart_k;
+    const int64_t* seqlen_k64;   // FmhaFwd: int64 per-batch key lengths (optional)
+    const int32_t* seqlen_k32;   // paged prefill: int32 per-batch key lengths
+    const int32_t* block_table;  // [batch, bt_stride] page ids, or nullptr
+    const int32_t* kv_indptr;    // SGLang-style page table (batch prefill) or nullptr
+    const int32_t* kv_page_indices;
+    const int32_t* kv_last_page_len;
+    const int64_t* cache_batch_idx;
+    int64_t batch, seqlen_q, seqlen_k, hq, hkv, d, dv, max_seqlen_q;
+    int64_t total_q;
+    int64_t bt_stride, page;
+    float scale;
+    int mask_type;
+    int64_t wl, wr;
+    int dtype;
+};
+int launch_fwd_generic(const FwdParams& p, cudaStream_t stream);
+
+// ---- tcgen05 prefill (fmha_fwd_sm100.cu): hdim 128, contiguous K/V ------------------------------
+bool fwd_sm100_supported(const FwdParams& p);
+int launch_fwd_sm100(const FwdParams& p, cudaStream_t stream);
+int fwd_set_param(const char* key, int64_t value);
+int fwd_get_param(const char* key, int64_t* value);
+
+}  // namespace fck

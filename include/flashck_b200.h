@@ -1,0 +1,174 @@
+/*
+ * flashck_b200 -- C ABI of the B200-native attention path (libflashck_b200.so).
+ *
+ * Each entry point replaces one `extern "C"` function that FlashCK's generated
+ * `generated_kernel.so` exports and that `Kernel::KernelLauncher` binds with
+ * `dylib::get_function` (core/utils/dylib_utils.h:76-91).  Names and argument order
+ * follow the reference; three things differ and are the same for every function:
+ *   - `std::array<int64_t,2> window_size` is not expressible in C, so it is passed
+ *     as two scalars `window_left, window_right` (-1 = unbounded);
+ *   - `hipStream_t` becomes `void* stream` (a cudaStream_t);
+ *   - the reference bakes the element type into each generated instance; here it is
+ *     a trailing `int dtype` (3 = float16, 4 = bfloat16, the values of
+ *     flashck::DataType, core/utils/dtype.h:16-28), and functions return an int
+ *     status (0 = ok) instead of printing to stderr and returning void
+ *     (core/module/kernels/attention_kernels/fmha_common_jinja.h:5-12).
+ * Where the reference passes `nullptr` for the LSE (fmha_fwd/fmha_fwd_jinja.h:317),
+ * a trailing optional `lse_ptr` receives it.
+ *
+ * All data pointers are device pointers; the caller owns every buffer, including
+ * the split-KV workspaces, and the callee never allocates.  Calls are asynchronous
+ * enqueues on `stream` and re-entrant.  Layouts are BSHD: Q [b,sq,hq,d],
+ * K [b,sk,hkv,d], V [b,sk,hkv,dv], O [b,sq,hq,dv]; group (varlen) mode packs the
+ * sequences along the token axis ([total,h,d]) with int64 `seqstart` arrays [b+1].
+ * LSE is fp32: [b,hq,sq] in batch mode, [hq,total_q] in group mode.
+ * mask_type: 0 none, 1 top-left, 2 bottom-right, 3 generic (treated as top-left
+ * coordinates); causal = window (-1, 0).   scale == 0 means 1/sqrt(hdim_q).
+ */
+#ifndef FLASHCK_B200_H_
+#define FLASHCK_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* exported with default visibility, like FC_EXPORT in the reference
+ * (attention_kernels/fmha_common_jinja.h:14-17) */
+#if defined(__GNUC__)
+#define FLASHCK_API __attribute__((visibility("default")))
+#else
+#define FLASHCK_API
+#endif
+
+#define FLASHCK_DTYPE_FLOAT16 3
+#define FLASHCK_DTYPE_BFLOAT16 4
+
+/* status codes */
+#define FLASHCK_OK 0
+#define FLASHCK_ERR_INVALID_ARGUMENT 1   /* null pointer, bad shape, hq % hkv != 0 ... */
+#define FLASHCK_ERR_UNSUPPORTED 2        /* no kernel instance for this problem */
+#define FLASHCK_ERR_CUDA 3               /* a CUDA runtime / driver call failed */
+#define FLASHCK_ERR_DEVICE_TIMEOUT 4     /* a bounded device-side wait ran out */
+
+/* Human-readable text of the last error raised on the calling thread. */
+FLASHCK_API const char* FlashckGetLastError(void);
+/* Library version string. */
+FLASHCK_API const char* FlashckVersion(void);
+/* Reads and clears the device-side status word of the current device (0 = no bounded wait ran out).
+ * Synchronises the device. */
+FLASHCK_API int FlashckDeviceStatus(int* status_out);
+
+/*
+ * FmhaFwd -- dense or varlen forward attention.
+ * Replaces `FmhaFwd` (signature: core/module/kernels/attention_kernels/fmha_fwd/fmha_fwd_jinja.h:124-147;
+ * declaration fmha_fwd/fmha_fwd_call.h:34-53; launcher fmha_fwd/fmha_fwd_kernel.cc:79-107).
+ * Batch mode: the three seq pointers are NULL.  Group mode: q_seq_start / k_seq_start are int64 [batch+1]
+ * device arrays; k_seq_len_ptr (int64 [batch], optional) overrides the key length of each sequence.
+ * bias_buf_ptr must be NULL (no-bias instances only).
+ */
+FLASHCK_API int FmhaFwd(void* q_buf_ptr, void* k_buf_ptr, void* v_buf_ptr, void* bias_buf_ptr, void* o_buf_ptr,
+            int64_t* q_seq_start_ptr, int64_t* k_seq_start_ptr, int64_t* k_seq_len_ptr, int64_t batch,
+            int64_t q_seq_len, int64_t kv_seq_len, int64_t q_num_heads, int64_t kv_num_heads, int64_t qk_head_dim,
+            int64_t v_head_dim, int64_t q_max_seq_len, float scale, int64_t window_left, int64_t window_right,
+            uint32_t mask_type, void* stream, void* lse_ptr, int dtype);
+
+/*
+ * FmhaFwdBatchPrefill -- varlen prefill whose K/V sit behind an SGLang-style page table.
+ * The reference emits this family (core/profiling/attention/fmha_fwd_batch_prefill/
+ * fmha_fwd_batch_prefill_codegen.cc:93-162, problem ..._problem.h:20-99 `num_total_pages`) but its glue
+ * files (attention_kernels/fmha_fwd_batch_prefill/...) are empty, so the argument list is defined here:
+ * Q [total_q,hq,d] with q_seq_start int64 [batch+1] and q_seq_len = total_q; K/V pools [num_total_pages,page,hkv,d|dv];
+ * kv_indptr int32 [batch+1], kv_page_indices int32 [kv_indptr[batch]], kv_last_page_len int32 [batch].
+ */
+FLASHCK_API int FmhaFwdBatchPrefill(void* q_buf_ptr, void* k_buf_ptr, void* v_buf_ptr, void* bias_buf_ptr, void* o_buf_ptr,
+                        int64_t* q_seq_start_ptr, void* kv_indptr, void* kv_page_indices, void* kv_last_page_len,
+                        int64_t batch, int64_t q_seq_len, int64_t q_num_heads, int64_t kv_num_heads,
+                        int64_t qk_head_dim, int64_t v_head_dim, int64_t q_max_seq_len, int64_t num_total_pages,
+                        int64_t paged_block_size, float scale, int64_t window_left, int64_t window_right,
+                        uint32_t mask_type, void* stream, void* lse_ptr, int dtype);
+
+/*
+ * FmhaFwdPagedKVPrefill -- prefill reading K/V through a block table (same page layout as FmhaFwdSplitKV).
+ * Family emitted at core/profiling/attention/fmha_fwd_paged_kv_prefill/fmha_fwd_paged_kv_prefill_codegen.cc:85-144;
+ * glue files empty in the reference, argument list modelled on FmhaFwdSplitKV without the split workspaces.
+ * k_seq_len_ptr: int32 [batch]; block_table: int32 [batch, max_num_page_blocks / batch].
+ */
+FLASHCK_API int FmhaFwdPagedKVPrefill(void* q_buf_ptr, void* k_buf_ptr, void* v_buf_ptr, void* bias_buf_ptr, void* o_buf_ptr,
+                          int64_t* q_seq_start_ptr, void* k_seq_len_ptr, void* block_table_buf_ptr,
+                          int64_t* cache_batch_idx_buf_ptr, int64_t batch, int64_t q_seq_len, int64_t q_num_heads,
+                          int64_t kv_num_heads, int64_t qk_head_dim, int64_t v_head_dim, int64_t q_max_seq_len,
+                          int64_t max_num_page_blocks, int64_t paged_block_size, float scale, int64_t window_left,
+                          int64_t window_right, uint32_t mask_type, void* stream, void* lse_ptr, int dtype);
+
+/*
+ * FmhaFwdSplitKV -- per-split partial attention over contiguous or paged K/V.
+ * Replaces `FmhaFwdSplitKV` (signature: attention_kernels/fmha_fwd_split_kv/fmha_fwd_split_kv_jinja.h:155-184;
+ * launcher fmha_fwd_split_kv/fmha_fwd_split_kv_kernel.cc:90-123).
+ * Writes o_acc fp32 [b,hq,num_splits,sq,dv] (normalised within the split) and lse_acc fp32 [b,hq,num_splits,sq]
+ * (fmha_fwd_split_kv_jinja.h:543-547; group mode: b = 1, sq = total_q).  A split that received no keys gets
+ * lse_acc = -inf.  lse_acc may be NULL only when num_splits == 1.
+ * Paged: K/V pools [max_num_page_blocks, page, hkv, d|dv] (:512-519), block_table int32
+ * [batch, max_num_page_blocks / batch] (:318,550), k_seq_len_ptr int32 [batch] (required when paged).
+ * How the key range of a sequence is cut into splits is internal (balanced over the SMs); only
+ * "at most num_splits splits per sequence" is guaranteed.
+ */
+FLASHCK_API int FmhaFwdSplitKV(void* q_buf_ptr, void* k_buf_ptr, void* v_buf_ptr, void* bias_buf_ptr, void* lse_acc_buf_ptr,
+                   void* o_acc_buf_ptr, int64_t* q_seq_start_ptr, int64_t* kv_seq_start_ptr, void* k_seq_len_ptr,
+                   void* block_table_buf_ptr, int64_t* cache_batch_idx_buf_ptr, int64_t batch, int64_t q_seq_len,
+                   int64_t kv_seq_len, int64_t q_num_heads, int64_t kv_num_heads, int64_t qk_head_dim,
+                   int64_t v_head_dim, int64_t q_max_seq_len, int64_t num_splits, int64_t max_num_page_blocks,
+                   int64_t paged_block_size, float scale, int64_t window_left, int64_t window_right,
+                   uint32_t mask_type, void* stream, int dtype);
+
+/*
+ * FmhaFwdSplitKVCombine -- LSE-weighted merge of the split partials into O (and LSE).
+ * Replaces `FmhaFwdSplitKVCombine` (signature: attention_kernels/fmha_fwd_split_kv_combine/
+ * fmha_fwd_split_kv_combine_jinja.h:78-92; declaration ..._combine_call.h:26-36).  The reference's code
+ * generator names the symbol `FmhaSplitKVCombine` (..._combine_kernel.cc:16); both names are exported.
+ */
+FLASHCK_API int FmhaFwdSplitKVCombine(void* lse_acc_buf_ptr, void* o_acc_buf_ptr, void* o_buf_ptr, int64_t* q_seq_start_ptr,
+                          int64_t batch, int64_t q_seq_len, int64_t q_num_heads, int64_t v_head_dim,
+                          int64_t q_max_seq_len, int64_t num_splits, void* stream, void* lse_ptr, int dtype);
+FLASHCK_API int FmhaSplitKVCombine(void* lse_acc_buf_ptr, void* o_acc_buf_ptr, void* o_buf_ptr, int64_t* q_seq_start_ptr,
+                       int64_t batch, int64_t q_seq_len, int64_t q_num_heads, int64_t v_head_dim,
+                       int64_t q_max_seq_len, int64_t num_splits, void* stream, void* lse_ptr, int dtype);
+
+/*
+ * FmhaFwdAppendKV -- rotary embedding of Q and the new keys, and the K/V cache write.
+ * The reference names the kind (core/profiling/attention/fmha_library.h:19,41), the rotary modes
+ * (fmha_library.h:195-219: 0 none, 1 interleaved, 2 half-rotated) and the table generator
+ * (attention_kernels/fmha_common_jinja.h:192-227) but has no source for the function; the argument list is
+ * defined here in the reference's style.
+ *   q: [b,sq,hq,d] or group mode [total_q,hq,d] (q_seq_start), rotated IN PLACE at positions
+ *      seqlen_k[b] + n_new[b] - sq[b] + i.
+ *   knew/vnew: [b,n,hkv,d|dv] or group mode [total_new,hkv,*] (knew_seq_start int64 [b+1]).
+ *   k/v cache: paged pool [pages,page,hkv,*] + block_table int32 [b, max_num_page_blocks/b], or contiguous
+ *      [b_cache, kv_seq_len, hkv, *] when block_table is NULL.  New token j lands at seqlen_k[b] + j.
+ *   k_seq_len_ptr: int32 [b], cached length BEFORE the append (not updated by the call).
+ *   rotary_cos/sin: [positions, rotary_dim/2] in the element dtype, indexed by absolute position.
+ * Cache contents are bit-exact against the CPU statement of the same arithmetic: fp32 products and sums,
+ * each rounded separately (no FMA), round-to-nearest-even narrowing.
+ */
+FLASHCK_API int FmhaFwdAppendKV(void* q_buf_ptr, void* k_buf_ptr, void* knew_buf_ptr, void* v_buf_ptr, void* vnew_buf_ptr,
+                    void* k_seq_len_ptr, int64_t* q_seq_start_ptr, int64_t* knew_seq_start_ptr,
+                    void* rotary_cos_ptr, void* rotary_sin_ptr, void* block_table_buf_ptr,
+                    int64_t* cache_batch_idx_buf_ptr, int64_t batch, int64_t q_seq_len, int64_t kv_seq_len,
+                    int64_t knew_seq_len, int64_t q_num_heads, int64_t kv_num_heads, int64_t qk_head_dim,
+                    int64_t v_head_dim, int64_t rotary_dim, int rope_type, int64_t max_num_page_blocks,
+                    int64_t paged_block_size, void* stream, int dtype);
+
+/*
+ * Instance selection (the reference picks a tile instance per problem through its tuner,
+ * core/profiling/attention/fmha_fwd/fmha_fwd_emitter.cc:325-466).  `family`: 0 fmha_fwd, 2 fmha_fwd_split_kv
+ * (FmhaKind values, fmha_library.h:17-25).  `key`/`value` pairs are documented in the tuner; unknown keys
+ * return FLASHCK_ERR_INVALID_ARGUMENT.  Process-wide, set before launching; not thread-safe against launches.
+ */
+FLASHCK_API int FlashckSetInstanceParam(int family, const char* key, int64_t value);
+FLASHCK_API int FlashckGetInstanceParam(int family, const char* key, int64_t* value_out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FLASHCK_B200_H_ */

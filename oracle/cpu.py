@@ -1,0 +1,136 @@
+"""TEST INFRASTRUCTURE ONLY -- ctypes front end of the CPU oracle (``liboracle.so``).
+
+PARITY UNPINNED: the reference holds no golden vectors for its attention path (see the
+header of ``fmha_oracle.cpp``).  Only ``tests/``, ``__graft_entry__.smoke()`` and the
+``cpu_baseline`` / ``--impl reference`` legs of ``bench.py`` may import this module.
+All tensors are CPU torch tensors; fp16/bf16 payloads cross the boundary as raw 16-bit words.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import subprocess
+from typing import Optional
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB: Optional[ctypes.CDLL] = None
+
+FLOAT16, BFLOAT16 = 3, 4  # core/utils/dtype.h:16-28
+
+
+def build(force: bool = False) -> str:
+    """Compile the oracle with the Makefile beside this file; returns the library path."""
+    path = os.path.join(_HERE, "liboracle.so")
+    if force or not os.path.exists(path):
+        subprocess.run(["make", "-C", _HERE], check=True, capture_output=True)
+    return path
+
+
+def lib() -> ctypes.CDLL:
+    global _LIB
+    if _LIB is None:
+        _LIB = ctypes.CDLL(build())
+    return _LIB
+
+
+def _dt(t: torch.Tensor) -> int:
+    if t.dtype == torch.float16:
+        return FLOAT16
+    if t.dtype == torch.bfloat16:
+        return BFLOAT16
+    raise TypeError(f"oracle supports float16/bfloat16, got {t.dtype}")
+
+
+def _p(t: Optional[torch.Tensor]):
+    if t is None:
+        return ctypes.c_void_p(0)
+    assert t.device.type == "cpu" and t.is_contiguous()
+    return ctypes.c_void_p(t.data_ptr())
+
+
+def _i64(x):
+    return ctypes.c_int64(int(x))
+
+
+def fmha_fwd(q, k, v, *, seqstart_q=None, seqstart_k=None, seqlen_k=None, block_table=None,
+             cache_batch_idx=None, seqlen_q_shape=None, scale=0.0, window=(-1, -1), mask_type=0,
+             nthreads=0):
+    """Returns (O, LSE).  Batch mode: q [b,sq,hq,d]; group mode (seqstart_q given): q [total_q,hq,d].
+    LSE is [b,hq,sq] (batch) or [hq,total_q] (group)."""
+    dt = _dt(q)
+    group = seqstart_q is not None
+    paged = block_table is not None
+    if group:
+        batch = seqstart_q.numel() - 1
+        total_q, hq, d = q.shape
+        sq = 0
+    else:
+        batch, sq, hq, d = q.shape
+        total_q = batch * sq
+    hkv, dv = k.shape[-2], v.shape[-1]
+    if paged:
+        page = k.shape[1]
+        bt_stride = block_table.shape[1]
+        sk = 0
+    else:
+        page, bt_stride = 0, 0
+        sk = k.shape[1] if k.dim() == 4 else 0
+    o = torch.empty(q.shape[:-1] + (dv,), dtype=q.dtype)
+    lse = torch.empty((hq, total_q) if group else (batch, hq, sq), dtype=torch.float32)
+    if seqlen_k is not None:
+        seqlen_k = seqlen_k.to(torch.int32).contiguous()
+    rc = lib().oracle_fmha_fwd(
+        _p(q), _p(k), _p(v), _p(o), _p(lse), _p(seqstart_q), _p(seqstart_k), _p(seqlen_k), _p(block_table),
+        _p(cache_batch_idx), _i64(batch), _i64(sq), _i64(sk), _i64(hq), _i64(hkv), _i64(d), _i64(dv),
+        _i64(bt_stride), _i64(page), ctypes.c_float(scale), _i64(window[0]), _i64(window[1]),
+        ctypes.c_uint32(mask_type), ctypes.c_int(dt), ctypes.c_int(nthreads))
+    if rc != 0:
+        raise RuntimeError(f"oracle_fmha_fwd failed with status {rc}")
+    return o, lse
+
+
+def splitkv_combine(lse_acc, o_acc, dtype):
+    """lse_acc [bs,hq,S,rows], o_acc [bs,hq,S,rows,dv] fp32 -> (O [bs,rows,hq,dv] dtype, LSE [bs,hq,rows])."""
+    bs, hq, S, rows, dv = o_acc.shape
+    o = torch.empty((bs, rows, hq, dv), dtype=dtype)
+    lse = torch.empty((bs, hq, rows), dtype=torch.float32)
+    rc = lib().oracle_splitkv_combine(_p(lse_acc), _p(o_acc), _p(o), _p(lse), _i64(bs), _i64(rows), _i64(hq),
+                                      _i64(dv), _i64(S), ctypes.c_int(_dt(o)))
+    if rc != 0:
+        raise RuntimeError(f"oracle_splitkv_combine failed with status {rc}")
+    return o, lse
+
+
+def fmha_fwd_appendkv(q, k_cache, knew, v_cache, vnew, seqlen_k, rotary_cos, rotary_sin, *, rope_type=1,
+                      rotary_dim=None, block_table=None, cache_batch_idx=None, seqstart_q=None,
+                      seqstart_knew=None):
+    """In place: rotates ``q`` and writes rotated ``knew`` / ``vnew`` into the caches."""
+    dt = _dt(q)
+    group = seqstart_q is not None
+    if group:
+        batch = seqstart_q.numel() - 1
+        sq = n = 0
+    else:
+        batch, sq = q.shape[0], q.shape[1]
+        n = knew.shape[1]
+    hq, d = q.shape[-2], q.shape[-1]
+    hkv, dv = knew.shape[-2], vnew.shape[-1]
+    if rotary_dim is None:
+        rotary_dim = 2 * rotary_cos.shape[-1] if rope_type != 0 else 0
+    if block_table is not None:
+        page, bt_stride, cap = k_cache.shape[1], block_table.shape[1], 0
+    else:
+        page, bt_stride, cap = 0, 0, k_cache.shape[1]
+    rc = lib().oracle_fmha_fwd_appendkv(
+        _p(q), _p(k_cache), _p(knew), _p(v_cache), _p(vnew), _p(seqlen_k.to(torch.int32).contiguous()),
+        _p(seqstart_q), _p(seqstart_knew), _p(rotary_cos), _p(rotary_sin), _p(block_table), _p(cache_batch_idx),
+        _i64(batch), _i64(sq), _i64(cap), _i64(n), _i64(hq), _i64(hkv), _i64(d), _i64(dv), _i64(rotary_dim),
+        ctypes.c_int(rope_type), _i64(bt_stride), _i64(page), ctypes.c_int(dt))
+    if rc != 0:
+        raise RuntimeError(f"oracle_fmha_fwd_appendkv failed with status {rc}")
+
+
+def num_threads() -> int:
+    return int(lib().oracle_num_threads())

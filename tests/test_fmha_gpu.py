@@ -1,0 +1,296 @@
+"""GPU parity tests: the CUDA path (through the C ABI, via flashck_b200.ops) against the CPU oracle on the
+same seeded inputs."""
+import pytest
+import torch
+
+from flashck_b200 import ops
+from flashck_b200.utils import MaskEnum, RopeEnum
+from flashck_b200.utils.inputs import (make_paged_cache, normal_tensor, rotary_cos_sin, to_seqstarts,
+                                       uniform_seqlens)
+from helpers import assert_bits_equal, assert_lse_close, assert_o_close
+from oracle import cpu as oracle
+
+pytestmark = [pytest.mark.gpu, pytest.mark.usefixtures("device_ok")]
+DEV = "cuda:0"
+
+
+def _cu(t):
+    return None if t is None else t.to(DEV)
+
+
+# ------------------------------------------------------------------------------------------------
+# fmha_fwd, batch mode
+# ------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("causal", [False, True])
+def test_fmha_fwd_config1(dtype, causal):
+    # BASELINE config 1: b=2, h=8, sq=sk=128, hdim=64, scale=1/sqrt(64)
+    b, s, h, d = 2, 128, 8, 64
+    q, k, v = (normal_tensor((b, s, h, d), dtype, 100 + i) for i in range(3))
+    mt = 1 if causal else 0
+    o_ref, lse_ref = oracle.fmha_fwd(q, k, v, scale=0.125, mask_type=mt, window=(-1, 0) if causal else (-1, -1))
+    o, lse = ops.fmha_fwd(_cu(q), _cu(k), _cu(v), scale=0.125, causal=causal, return_lse=True)
+    assert_o_close(o, o_ref)
+    assert_lse_close(lse, lse_ref)
+
+
+@pytest.mark.parametrize("sq,sk", [(1, 1), (1, 77), (15, 15), (17, 63), (64, 64), (65, 129), (127, 300), (129, 129),
+                                   (200, 40)])
+@pytest.mark.parametrize("d", [64, 128])
+@pytest.mark.parametrize("mask", [(0, -1, -1), (1, -1, 0), (2, -1, 0), (2, 20, 0), (1, 5, 7), (3, 33, 0)])
+def test_fmha_fwd_shapes_and_masks(sq, sk, d, mask):
+    dtype = torch.bfloat16
+    b, hq, hkv = 2, 4, 2
+    q = normal_tensor((b, sq, hq, d), dtype, 1)
+    k = normal_tensor((b, sk, hkv, d), dtype, 2)
+    v = normal_tensor((b, sk, hkv, d), dtype, 3)
+    mt, wl, wr = mask
+    o_ref, lse_ref = oracle.fmha_fwd(q, k, v, mask_type=mt, window=(wl, wr))
+    o, lse = ops.fmha_fwd(_cu(q), _cu(k), _cu(v), window_size=(wl, wr), mask_type=mt, return_lse=True)
+    assert_o_close(o, o_ref)
+    assert_lse_close(lse, lse_ref)
+
+
+def test_fmha_fwd_var_len_gqa():
+    dtype = torch.bfloat16
+    lens = [1, 64, 65, 200, 0, 333]
+    cu = to_seqstarts(lens)
+    hq, hkv, d = 8, 2, 128
+    total = int(cu[-1])
+    q = normal_tensor((total, hq, d), dtype, 11)
+    k = normal_tensor((total, hkv, d), dtype, 12)
+    v = normal_tensor((total, hkv, d), dtype, 13)
+    o_ref, lse_ref = oracle.fmha_fwd(q, k, v, seqstart_q=cu, seqstart_k=cu, mask_type=1, window=(-1, 0))
+    o, lse = ops.fmha_fwd_var_len(_cu(q), _cu(k), _cu(v), _cu(cu), _cu(cu), max(lens), causal=True, return_lse=True)
+    assert_o_close(o, o_ref)
+    assert_lse_close(lse, lse_ref)
+
+
+def test_fmha_fwd_var_len_config2_small():
+    # BASELINE config 2 at reduced size: same head geometry (32/8, hdim 128), fewer and shorter sequences
+    dtype = torch.bfloat16
+    lens = uniform_seqlens(4, 512, 1024, seed=2)
+    cu = to_seqstarts(lens)
+    hq, hkv, d = 32, 8, 128
+    total = int(cu[-1])
+    q = normal_tensor((total, hq, d), dtype, 21)
+    k = normal_tensor((total, hkv, d), dtype, 22)
+    v = normal_tensor((total, hkv, d), dtype, 23)
+    o_ref, lse_ref = oracle.fmha_fwd(q, k, v, seqstart_q=cu, seqstart_k=cu, mask_type=1, window=(-1, 0))
+    o, lse = ops.fmha_fwd_var_len(_cu(q), _cu(k), _cu(v), _cu(cu), _cu(cu), max(lens), causal=True, return_lse=True)
+    assert_o_close(o, o_ref)
+    assert_lse_close(lse, lse_ref)
+
+
+def test_paged_prefill_variants():
+    dtype = torch.bfloat16
+    hq, hkv, d, page = 8, 2, 128, 16
+    lens_k = [40, 129, 16, 300]
+    lens_q = [40, 100, 3, 64]
+    cache = make_paged_cache(lens_k, hkv, d, d, page, dtype, seed=5)
+    cu_q = to_seqstarts(lens_q)
+    q = normal_tensor((int(cu_q[-1]), hq, d), dtype, 31)
+    o_ref, lse_ref = oracle.fmha_fwd(q, cache.k, cache.v, seqstart_q=cu_q, seqlen_k=cache.seqlen_k,
+                                     block_table=cache.block_table, mask_type=2, window=(-1, 0))
+    # block-table form
+    o, lse = ops.fmha_fwd_paged_kv_prefill(_cu(q), _cu(cache.k), _cu(cache.v), _cu(cache.block_table),
+                                           _cu(cache.seqlen_k), cu_seqlens_q=_cu(cu_q), max_seqlen_q=max(lens_q),
+                                           causal=True, return_lse=True)
+    assert_o_close(o, o_ref)
+    assert_lse_close(lse, lse_ref)
+    # SGLang-style page table form of the same cache
+    npages = [-(-l // page) for l in lens_k]
+    indptr = torch.tensor([0] + list(torch.tensor(npages).cumsum(0)), dtype=torch.int32)
+    indices = torch.cat([cache.block_table[b, :n] for b, n in enumerate(npages)]).to(torch.int32)
+    last = torch.tensor([l - (n - 1) * page for l, n in zip(lens_k, npages)], dtype=torch.int32)
+    o2, lse2 = ops.batch_prefill(_cu(q), _cu(cache.k), _cu(cache.v), _cu(cu_q), _cu(indptr), _cu(indices), _cu(last),
+                                 max(lens_q), causal=True, return_lse=True)
+    assert_o_close(o2, o_ref)
+    assert_lse_close(lse2, lse_ref)
+
+
+# ------------------------------------------------------------------------------------------------
+# split-KV decode + combine
+# ------------------------------------------------------------------------------------------------
+def test_combine_matches_oracle():
+    torch.manual_seed(0)
+    bs, hq, S, rows, dv = 3, 5, 7, 4, 128
+    lse_acc = torch.randn(bs, hq, S, rows) * 3
+    lse_acc[0, 0, 2] = float("-inf")
+    lse_acc[1, 1, :, 1] = float("-inf")  # a row no split saw
+    o_acc = torch.randn(bs, hq, S, rows, dv)
+    o_acc[0, 0, 2] = float("nan")  # the slot of an empty split is never read
+    o_ref, lse_ref = oracle.splitkv_combine(lse_acc, torch.nan_to_num(o_acc), torch.bfloat16)
+    o, lse = ops.fmha_fwd_splitkv_combine(_cu(lse_acc), _cu(o_acc), torch.bfloat16, return_lse=True)
+    assert_o_close(o, o_ref)
+    assert_lse_close(lse, lse_ref)
+
+
+@pytest.mark.parametrize("page", [16, 64])
+@pytest.mark.parametrize("hq,hkv", [(32, 8), (16, 8), (8, 4), (6, 2), (3, 1), (16, 16)])
+@pytest.mark.parametrize("num_splits", [1, 2, 5, 0])
+def test_splitkv_paged_decode(page, hq, hkv, num_splits):
+    dtype = torch.bfloat16
+    d = 128
+    lens = [1, 15, 16, 17, 127, 129, 1000, 0, 2049, 333]
+    cache = make_paged_cache(lens, hkv, d, d, page, dtype, seed=7)
+    q = normal_tensor((len(lens), 1, hq, d), dtype, 41)
+    o_ref, lse_ref = oracle.fmha_fwd(q, cache.k, cache.v, seqlen_k=cache.seqlen_k, block_table=cache.block_table)
+    o, lse = ops.fmha_fwd_splitkv(_cu(q), _cu(cache.k), _cu(cache.v), seqlen_k=_cu(cache.seqlen_k),
+                                  block_table=_cu(cache.block_table), num_splits=num_splits, return_lse=True)
+    assert_o_close(o, o_ref)
+    assert_lse_close(lse, lse_ref)
+
+
+@pytest.mark.parametrize("dtype,d", [(torch.float16, 64), (torch.float16, 128), (torch.bfloat16, 64)])
+def test_splitkv_dtypes_hdims(dtype, d):
+    hq, hkv, page = 8, 2, 16
+    lens = [100, 3, 777]
+    cache = make_paged_cache(lens, hkv, d, d, page, dtype, seed=8)
+    q = normal_tensor((len(lens), 1, hq, d), dtype, 42)
+    o_ref, lse_ref = oracle.fmha_fwd(q, cache.k, cache.v, seqlen_k=cache.seqlen_k, block_table=cache.block_table)
+    o, lse = ops.fmha_fwd_splitkv(_cu(q), _cu(cache.k), _cu(cache.v), seqlen_k=_cu(cache.seqlen_k),
+                                  block_table=_cu(cache.block_table), num_splits=4, return_lse=True)
+    assert_o_close(o, o_ref)
+    assert_lse_close(lse, lse_ref)
+
+
+def test_splitkv_contiguous_cache_and_batch_idx():
+    dtype = torch.bfloat16
+    b, cap, hq, hkv, d = 4, 200, 8, 2, 128
+    k = normal_tensor((b + 2, cap, hkv, d), dtype, 51)
+    v = normal_tensor((b + 2, cap, hkv, d), dtype, 52)
+    q = normal_tensor((b, 1, hq, d), dtype, 53)
+    sl = torch.tensor([200, 1, 57, 128], dtype=torch.int32)
+    idx = torch.tensor([5, 0, 3, 2], dtype=torch.int64)
+    o_ref, lse_ref = oracle.fmha_fwd(q, k, v, seqlen_k=sl, cache_batch_idx=idx)
+    o, lse = ops.fmha_fwd_splitkv(_cu(q), _cu(k), _cu(v), seqlen_k=_cu(sl), cache_batch_idx=_cu(idx), num_splits=3,
+                                  return_lse=True)
+    assert_o_close(o, o_ref)
+    assert_lse_close(lse, lse_ref)
+
+
+def test_splitkv_multi_token_queries_causal_and_window():
+    # seqlen_q > 1 (the append + decode case): ragged q rows, bottom-right causal, optional sliding window
+    dtype = torch.bfloat16
+    hq, hkv, d, page = 32, 8, 128, 16
+    lens_k = [300, 64, 1025, 17]
+    lens_q = [16, 1, 7, 17]
+    cache = make_paged_cache(lens_k, hkv, d, d, page, dtype, seed=9)
+    cu_q = to_seqstarts(lens_q)
+    q = normal_tensor((int(cu_q[-1]), hq, d), dtype, 61)
+    for wl in (-1, 100):
+        o_ref, lse_ref = oracle.fmha_fwd(q, cache.k, cache.v, seqstart_q=cu_q, seqlen_k=cache.seqlen_k,
+                                         block_table=cache.block_table, mask_type=2, window=(wl, 0))
+        o, lse = ops.fmha_fwd_splitkv(_cu(q), _cu(cache.k), _cu(cache.v), seqlen_k=_cu(cache.seqlen_k),
+                                      block_table=_cu(cache.block_table), cu_seqlens_q=_cu(cu_q),
+                                      max_seqlen_q=max(lens_q), num_splits=4, causal=True, window_size=(wl, 0),
+                                      return_lse=True)
+        assert_o_close(o, o_ref)
+        assert_lse_close(lse, lse_ref)
+
+
+def test_splitkv_config3_small():
+    # BASELINE config 3 geometry (32/8 heads, hdim 128, page 16, shuffled block table) at reduced batch/context
+    dtype = torch.bfloat16
+    lens = uniform_seqlens(8, 1024, 4096, seed=3)
+    cache = make_paged_cache(lens, 8, 128, 128, 16, dtype, seed=10)
+    q = normal_tensor((8, 1, 32, 128), dtype, 71)
+    o_ref, lse_ref = oracle.fmha_fwd(q, cache.k, cache.v, seqlen_k=cache.seqlen_k, block_table=cache.block_table)
+    o, lse = ops.fmha_fwd_splitkv(_cu(q), _cu(cache.k), _cu(cache.v), seqlen_k=_cu(cache.seqlen_k),
+                                  block_table=_cu(cache.block_table), return_lse=True)
+    assert_o_close(o, o_ref)
+    assert_lse_close(lse, lse_ref)
+
+
+# ------------------------------------------------------------------------------------------------
+# append-KV
+# ------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("rope,rotary_dim", [(RopeEnum.INTERLEAVED, 128), (RopeEnum.HALF_ROTATED, 128),
+                                             (RopeEnum.INTERLEAVED, 64), (RopeEnum.NONE, 0)])
+def test_appendkv_paged_bit_exact(dtype, rope, rotary_dim):
+    hq, hkv, d, page = 8, 2, 128, 16
+    lens = [0, 5, 16, 31, 100]
+    new = [3, 16, 1, 2, 9]
+    cap = [l + n for l, n in zip(lens, new)]
+    cache = make_paged_cache(lens, hkv, d, d, page, dtype, seed=12, capacity=cap)
+    cu_n = to_seqstarts(new)
+    total = int(cu_n[-1])
+    q = normal_tensor((total, hq, d), dtype, 81)
+    knew = normal_tensor((total, hkv, d), dtype, 82)
+    vnew = normal_tensor((total, hkv, d), dtype, 83)
+    cos, sin = rotary_cos_sin(max(cap) + 1, max(rotary_dim, 2), dtype)
+    # oracle (in place on CPU copies)
+    q_ref, k_ref, v_ref = q.clone(), cache.k.clone(), cache.v.clone()
+    oracle.fmha_fwd_appendkv(q_ref, k_ref, knew, v_ref, vnew, cache.seqlen_k, cos, sin, rope_type=int(rope),
+                             rotary_dim=rotary_dim, block_table=cache.block_table, seqstart_q=cu_n,
+                             seqstart_knew=cu_n)
+    qd, kd, vd = _cu(q), _cu(cache.k), _cu(cache.v)
+    ops.fmha_fwd_append_kv(qd, kd, vd, _cu(knew), _cu(vnew), _cu(cache.seqlen_k), _cu(cos), _cu(sin), rope=rope,
+                           rotary_dim=rotary_dim, block_table=_cu(cache.block_table), cu_seqlens_q=_cu(cu_n),
+                           cu_seqlens_knew=_cu(cu_n))
+    assert_bits_equal(kd, k_ref, "k cache")
+    assert_bits_equal(vd, v_ref, "v cache")
+    assert_bits_equal(qd, q_ref, "rotated q")
+
+
+def test_appendkv_contiguous_batch_mode():
+    dtype = torch.bfloat16
+    b, cap, hq, hkv, d, n = 3, 64, 4, 4, 64, 4
+    k = normal_tensor((b, cap, hkv, d), dtype, 91)
+    v = normal_tensor((b, cap, hkv, d), dtype, 92)
+    q = normal_tensor((b, n, hq, d), dtype, 93)
+    knew = normal_tensor((b, n, hkv, d), dtype, 94)
+    vnew = normal_tensor((b, n, hkv, d), dtype, 95)
+    sl = torch.tensor([0, 10, 60], dtype=torch.int32)
+    cos, sin = rotary_cos_sin(cap, d, dtype)
+    q_ref, k_ref, v_ref = q.clone(), k.clone(), v.clone()
+    oracle.fmha_fwd_appendkv(q_ref, k_ref, knew, v_ref, vnew, sl, cos, sin, rope_type=2)
+    qd, kd, vd = _cu(q), _cu(k), _cu(v)
+    ops.fmha_fwd_append_kv(qd, kd, vd, _cu(knew), _cu(vnew), _cu(sl), _cu(cos), _cu(sin), rope=RopeEnum.HALF_ROTATED)
+    assert_bits_equal(kd, k_ref, "k cache")
+    assert_bits_equal(vd, v_ref, "v cache")
+    assert_bits_equal(qd, q_ref, "rotated q")
+
+
+def test_append_then_decode_config4_small():
+    # BASELINE config 4 flow at reduced size: append 1..16 tokens with interleaved RoPE, then split-KV decode
+    dtype = torch.bfloat16
+    b, hq, hkv, d, page = 6, 32, 8, 128, 16
+    lens = uniform_seqlens(b, 200, 1500, seed=4)
+    new = uniform_seqlens(b, 1, 16, seed=5)
+    cap = [l + n for l, n in zip(lens, new)]
+    cache = make_paged_cache(lens, hkv, d, d, page, dtype, seed=13, capacity=cap)
+    cu_n = to_seqstarts(new)
+    total = int(cu_n[-1])
+    q = normal_tensor((total, hq, d), dtype, 101)
+    knew = normal_tensor((total, hkv, d), dtype, 102)
+    vnew = normal_tensor((total, hkv, d), dtype, 103)
+    cos, sin = rotary_cos_sin(max(cap) + 1, d, dtype)
+    q_ref, k_ref, v_ref = q.clone(), cache.k.clone(), cache.v.clone()
+    oracle.fmha_fwd_appendkv(q_ref, k_ref, knew, v_ref, vnew, cache.seqlen_k, cos, sin, rope_type=1,
+                             block_table=cache.block_table, seqstart_q=cu_n, seqstart_knew=cu_n)
+    new_len = torch.tensor(cap, dtype=torch.int32)
+    o_ref, lse_ref = oracle.fmha_fwd(q_ref, k_ref, v_ref, seqstart_q=cu_n, seqlen_k=new_len,
+                                     block_table=cache.block_table, mask_type=2, window=(-1, 0))
+    qd, kd, vd = _cu(q), _cu(cache.k), _cu(cache.v)
+    ops.fmha_fwd_append_kv(qd, kd, vd, _cu(knew), _cu(vnew), _cu(cache.seqlen_k), _cu(cos), _cu(sin),
+                           block_table=_cu(cache.block_table), cu_seqlens_q=_cu(cu_n), cu_seqlens_knew=_cu(cu_n))
+    assert_bits_equal(kd, k_ref, "k cache")
+    assert_bits_equal(vd, v_ref, "v cache")
+    o, lse = ops.fmha_fwd_splitkv(qd, kd, vd, seqlen_k=_cu(new_len), block_table=_cu(cache.block_table),
+                                  cu_seqlens_q=_cu(cu_n), max_seqlen_q=max(new), causal=True, return_lse=True)
+    assert_o_close(o, o_ref)
+    assert_lse_close(lse, lse_ref)
+
+
+def test_errors_are_loud():
+    q = torch.zeros(1, 1, 3, 128, dtype=torch.bfloat16, device=DEV)
+    k = torch.zeros(1, 16, 2, 128, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(RuntimeError, match="multiple"):
+        ops.fmha_fwd(q, k, k)  # 3 q heads over 2 kv heads
+    q = torch.zeros(1, 1, 2, 96, dtype=torch.bfloat16, device=DEV)
+    k = torch.zeros(1, 16, 2, 96, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(RuntimeError, match="hdim"):
+        ops.fmha_fwd(q, k, k)
