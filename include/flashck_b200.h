@@ -160,6 +160,29 @@ FLASHCK_API int FmhaFwdAppendKV(void* q_buf_ptr, void* k_buf_ptr, void* knew_buf
                     int64_t paged_block_size, void* stream, int dtype);
 
 /*
+ * FmhaFwdSplitKVStatic -- split-KV attention and combine in one call, for callers that cannot allocate.
+ * This entry point has no counterpart in the reference.  It exists for callers that may not call cudaMalloc
+ * (a serving loop with a fixed memory plan, code that must stay inside a framework allocator, threads barred
+ * from the allocator's locks): instead of caller-owned lse_acc / o_acc workspaces it uses a 16 MiB array that
+ * the library keeps in device memory on every GPU that loads it.  Arguments are those of FmhaFwdSplitKV with
+ * the two workspaces replaced by the final outputs o (element dtype, [b,sq,hq,dv]) and lse (fp32, optional).
+ *   - The workspaces of the call, (b*hq*num_splits*sq) * (dv + 1) floats, must fit 16 MiB; otherwise the call
+ *     returns FLASHCK_ERR_UNSUPPORTED and the error text gives both sizes.
+ *   - All calls on a device share the array and it keeps the previous call's contents (none of it has to be
+ *     zero).  Calls that overlap on the GPU race on it: run them one after another.
+ *   - The first call on each device looks up the array's device address; make that call before any stream
+ *     capture.  No call allocates or frees device memory.
+ */
+FLASHCK_API int FmhaFwdSplitKVStatic(void* q_buf_ptr, void* k_buf_ptr, void* v_buf_ptr, void* o_buf_ptr, void* lse_ptr,
+                                     int64_t* q_seq_start_ptr, int64_t* kv_seq_start_ptr, void* k_seq_len_ptr,
+                                     void* block_table_buf_ptr, int64_t* cache_batch_idx_buf_ptr, int64_t batch,
+                                     int64_t q_seq_len, int64_t kv_seq_len, int64_t q_num_heads, int64_t kv_num_heads,
+                                     int64_t qk_head_dim, int64_t v_head_dim, int64_t q_max_seq_len,
+                                     int64_t num_splits, int64_t max_num_page_blocks, int64_t paged_block_size,
+                                     float scale, int64_t window_left, int64_t window_right, uint32_t mask_type,
+                                     void* stream, int dtype);
+
+/*
  * Instance selection (the reference picks a tile instance per problem through its tuner,
  * core/profiling/attention/fmha_fwd/fmha_fwd_emitter.cc:325-466).  `family`: 0 fmha_fwd, 2 fmha_fwd_split_kv
  * (FmhaKind values, fmha_library.h:17-25).  `key`/`value` pairs are documented in the tuner; unknown keys
