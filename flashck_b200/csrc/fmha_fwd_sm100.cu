@@ -1,15 +1,485 @@
-// tcgen05 prefill instance (placeholder until the kernel lands): reports "not supported" so that the
-// dispatcher uses the general instance.
+// fmha_fwd / batch prefill -- the tcgen05 instance (hdim 128, contiguous K/V, no mask or causal).
+// Replaces ck_tile::FmhaFwdKernel<BlockFmhaPipelineQRKSVS...> as instantiated by the reference
+// (core/profiling/attention/fmha_fwd/fmha_fwd_codegen.cc:86-118) behind the C symbol FmhaFwd
+// (attention_kernels/fmha_fwd/fmha_fwd_jinja.h:124-147), batch and group mode, GQA, fp32 LSE.
+//
+// One CTA (384 threads, one per SM: it owns all 512 TMEM columns) computes 256 query rows of one head as two
+// 128-row tiles that ping-pong through the pipeline:
+//   warp 9      TMA producer: Q once (4 boxes of 64 x 128, 128-byte swizzle), then K and V tiles of 128 keys
+//               into two-slot rings, mbarrier expect-tx.
+//   warp 8      MMA issuer (one elected thread): S_i = Q_i K^T with tcgen05.mma (both operands in shared
+//               memory, K-major), O_i += P_i V with the A operand P_i read from tensor memory and V taken
+//               MN-major straight from its [key][hdim] tile.  Accumulators live in TMEM: S0,S1 (128 columns
+//               each, fp32) and O0,O1 (128 columns each).  tcgen05.commit signals the consumers.
+//   warps 0-3 / 4-7   softmax warpgroup of tile 0 / 1: thread r owns row r (TMEM lane r), so row max and row sum
+//               need no shuffles.  tcgen05.ld S -> registers, fp32 online softmax in base 2, P rounded to the
+//               element dtype and stored with tcgen05.st over the first 64 columns of S_i (the next QK^T of the
+//               tile is issued after the PV that reads P, and the tensor pipe runs in order).  The running max is
+//               only raised -- and O_i rescaled in TMEM -- when it grows by more than 2^8, so the correction
+//               is off the steady-state path; the final 1/l normalisation and the O / LSE stores are done by the
+//               same warpgroup.
+// K/V tiles hidden by the causal mask are skipped; only diagonal and tail tiles pay for masking.
+// The GQA group's q heads run in neighbouring CTAs and share K/V through L2 (no cluster multicast).
+// Every mbarrier wait is bounded; on expiry the CTA records a code in the device status word and drains.
+#include <atomic>
 #include <string.h>
 
 #include "kernels.h"
 
 namespace fck {
-bool fwd_sm100_supported(const FwdParams&) { return false; }
-int launch_fwd_sm100(const FwdParams&, cudaStream_t) {
-    set_last_error("fmha_fwd: the tcgen05 instance is not built");
-    return FLASHCK_ERR_UNSUPPORTED;
+
+namespace {
+
+constexpr int BM = 128;        // rows per Q tile
+constexpr int BN = 128;        // keys per K/V tile
+constexpr int HD = 128;        // head dim
+constexpr int KV_SLOTS = 2;
+constexpr int TILE_BYTES = BM * HD * 2;   // 32 KB: one Q, K or V tile
+constexpr int HALF_BYTES = TILE_BYTES / 2;  // one 64-column block (128 rows x 128 B)
+constexpr int NTHREADS = 384;
+constexpr float kRescaleThreshold = 8.f;  // log2 units
+
+std::atomic<int64_t> g_use_sm100{1};
+
+struct Sm100Dev {
+    void* o;
+    float* lse;
+    const int64_t* seqstart_q;
+    const int64_t* seqstart_k;
+    int* status;
+    int batch, seqlen_q, seqlen_k, hq, hkv, total_q;
+    int causal;       // 0 none, 1 top-left, 2 bottom-right
+    float scale_log2;
+};
+
+// ---- PTX wrappers ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3FFFF) >> 4);
+    d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
+    d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
+    d |= (uint64_t)1 << 46;  // descriptor version of sm_100
+    d |= (uint64_t)2 << 61;  // 128-byte swizzle
+    return d;
 }
-int fwd_set_param(const char*, int64_t) { return FLASHCK_ERR_INVALID_ARGUMENT; }
-int fwd_get_param(const char*, int64_t*) { return FLASHCK_ERR_INVALID_ARGUMENT; }
+__device__ __forceinline__ void umma_ss(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
+    asm volatile(
+        "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(d_tmem),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc)
+        : "memory");
+}
+__device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
+    asm volatile(
+        "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n" ::"r"(d_tmem),
+        "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(acc)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_u32(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,"
+        "%29,%30,%31}, [%32];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,"
+        "%30,%31,%32};\n" ::"r"(taddr),
+        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+        "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]),
+        "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]),
+        "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3,%4,%5}], [%2];\n" ::
+            "r"(smem_u32(smem_dst)),
+        "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
+        : "memory");
+}
+
+// Instruction descriptor of tcgen05.mma kind::f16: D = f32 (bits 4-5 = 1); A/B format at bits 7-9 / 10-12
+// (0 = f16, 1 = bf16); bit 16: B is MN-major; N >> 3 at bits 17-22; M >> 4 at bits 24-28.
+template <typename T> struct UmmaFmt;
+template <> struct UmmaFmt<__half> { static constexpr uint32_t v = 0u; };
+template <> struct UmmaFmt<__nv_bfloat16> { static constexpr uint32_t v = 1u; };
+template <typename T>
+__device__ __forceinline__ constexpr uint32_t make_idesc(bool b_mn_major) {
+    return (1u << 4) | (UmmaFmt<T>::v << 7) | (UmmaFmt<T>::v << 10) | ((b_mn_major ? 1u : 0u) << 16) |
+           ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
+
+// Shared-memory control block placed after the tiles.
+struct Ctrl {
+    uint64_t q_full;
+    uint64_t k_full[KV_SLOTS], k_empty[KV_SLOTS], v_full[KV_SLOTS], v_empty[KV_SLOTS];
+    uint64_t s_full[2], p_full[2], o_full[2];
+    uint32_t tmem_base;
+    int abort_flag;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(NTHREADS, 1)
+fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                      const __grid_constant__ CUtensorMap map_v, const Sm100Dev p) {
+    extern __shared__ uint8_t smem_raw[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int b = blockIdx.z, h = blockIdx.y;
+    const int mblk = gridDim.x - 1 - blockIdx.x;  // longest (causal) row blocks first
+    const int kh = h / (p.hq / p.hkv);
+
+    const int64_t q0 = p.seqstart_q ? p.seqstart_q[b] : (int64_t)b * p.seqlen_q;
+    const int sq = p.seqstart_q ? (int)(p.seqstart_q[b + 1] - p.seqstart_q[b]) : p.seqlen_q;
+    const int64_t k0 = p.seqstart_k ? p.seqstart_k[b] : (int64_t)b * p.seqlen_k;
+    const int sk = p.seqstart_k ? (int)(p.seqstart_k[b + 1] - p.seqstart_k[b]) : p.seqlen_k;
+    const int m0 = mblk * 2 * BM;
+    if (m0 >= sq) return;  // uniform for the CTA; nothing has been set up yet
+
+    // key tiles each Q tile needs: all of them, or up to its last row's diagonal
+    const int shift = (p.causal == 2) ? sk - sq : 0;
+    const int nk_all = (sk + BN - 1) / BN;
+    int ntile[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int first = m0 + i * BM;
+        if (first >= sq) { ntile[i] = 0; continue; }
+        const int last = min(sq, first + BM) - 1;
+        int n = nk_all;
+        if (p.causal) {
+            const int hi = last + shift;  // last visible key of the last row
+            n = hi < 0 ? 0 : min(nk_all, hi / BN + 1);
+        }
+        ntile[i] = n;
+    }
+    const int N0 = ntile[0], N1 = ntile[1];
+    const int N = max(N0, N1);
+
+    // ---- shared memory carve-up ----
+    const uint32_t raw = smem_u32(smem_raw);
+    uint8_t* base = smem_raw + (((raw + 1023u) & ~1023u) - raw);
+    uint8_t* sQ = base;                                  // 2 tiles
+    uint8_t* sK = base + 2 * TILE_BYTES;                 // KV_SLOTS tiles
+    uint8_t* sV = sK + KV_SLOTS * TILE_BYTES;            // KV_SLOTS tiles
+    Ctrl* ctrl = reinterpret_cast<Ctrl*>(sV + KV_SLOTS * TILE_BYTES);
+    volatile int* abort_flag = &ctrl->abort_flag;
+
+    if (threadIdx.x == 0) {
+        mbar_init(&ctrl->q_full, 1);
+        for (int s = 0; s < KV_SLOTS; ++s) {
+            mbar_init(&ctrl->k_full[s], 1);
+            mbar_init(&ctrl->k_empty[s], 1);
+            mbar_init(&ctrl->v_full[s], 1);
+            mbar_init(&ctrl->v_empty[s], 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&ctrl->s_full[i], 1);
+            mbar_init(&ctrl->p_full[i], 4);  // one arrival per softmax warp
+            mbar_init(&ctrl->o_full[i], 1);
+        }
+        ctrl->abort_flag = 0;
+        mbar_fence_init();
+    }
+    if (warp == 8) {  // TMEM: all 512 columns (S0 S1 O0 O1)
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;\n" ::"r"(
+            smem_u32(&ctrl->tmem_base)));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = ctrl->tmem_base;
+
+    if (warp >= 8) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 48;\n" ::);
+        if (warp == 9 && lane == 0) {
+            // ================================ TMA producer ================================
+            tma_prefetch_desc(&map_q);
+            tma_prefetch_desc(&map_k);
+            tma_prefetch_desc(&map_v);
+            const int q_tiles = (N1 > 0 || m0 + BM < sq) ? 2 : 1;
+            mbar_expect_tx(&ctrl->q_full, q_tiles * TILE_BYTES);
+            for (int i = 0; i < q_tiles; ++i)
+                for (int hb = 0; hb < 2; ++hb)
+                    tma_load_3d(sQ + i * TILE_BYTES + hb * HALF_BYTES, &map_q, &ctrl->q_full, hb * 64, h,
+                                (int)(q0 + m0 + i * BM));
+            for (int n = 0; n < N; ++n) {
+                const int s = n % KV_SLOTS;
+                const uint32_t ph = (n / KV_SLOTS) & 1u;
+                const int row = (int)(k0 + (int64_t)n * BN);
+                if (!mbar_wait_bounded(&ctrl->k_empty[s], ph ^ 1u, abort_flag, p.status, 0x10)) break;
+                mbar_expect_tx(&ctrl->k_full[s], TILE_BYTES);
+                for (int hb = 0; hb < 2; ++hb)
+                    tma_load_3d(sK + s * TILE_BYTES + hb * HALF_BYTES, &map_k, &ctrl->k_full[s], hb * 64, kh, row);
+                if (!mbar_wait_bounded(&ctrl->v_empty[s], ph ^ 1u, abort_flag, p.status, 0x20)) break;
+                mbar_expect_tx(&ctrl->v_full[s], TILE_BYTES);
+                for (int hb = 0; hb < 2; ++hb)
+                    tma_load_3d(sV + s * TILE_BYTES + hb * HALF_BYTES, &map_v, &ctrl->v_full[s], hb * 64, kh, row);
+            }
+        } else if (warp == 8 && lane == 0 && N > 0) {
+            // ================================ MMA issuer ================================
+            constexpr uint32_t idesc_qk = make_idesc<T>(false);
+            constexpr uint32_t idesc_pv = make_idesc<T>(true);
+            const uint32_t tS[2] = {tmem, tmem + 128};
+            const uint32_t tO[2] = {tmem + 256, tmem + 384};
+            auto issue_qk = [&](int i, int s) {  // S_i = Q_i K^T : 8 steps of 16 along the head dim
+                const uint32_t qa = smem_u32(sQ + i * TILE_BYTES), ka = smem_u32(sK + s * TILE_BYTES);
+#pragma unroll
+                for (int ks = 0; ks < HD / 16; ++ks) {
+                    const uint32_t off = (ks / 4) * HALF_BYTES + (ks % 4) * 32;
+                    umma_ss(tS[i], make_smem_desc(qa + off, 0, 1024), make_smem_desc(ka + off, 0, 1024), idesc_qk,
+                            ks > 0);
+                }
+            };
+            auto issue_pv = [&](int i, int s, bool accumulate) {  // O_i += P_i V : 8 steps of 16 keys
+                const uint32_t va = smem_u32(sV + s * TILE_BYTES);
+#pragma unroll
+                for (int ks = 0; ks < BN / 16; ++ks)
+                    umma_ts(tO[i], tS[i] + ks * 8, make_smem_desc(va + ks * 2048, HALF_BYTES, 1024), idesc_pv,
+                            (accumulate || ks > 0) ? 1u : 0u);
+            };
+            bool ok = mbar_wait_bounded(&ctrl->q_full, 0, abort_flag, p.status, 0x40) &&
+                      mbar_wait_bounded(&ctrl->k_full[0], 0, abort_flag, p.status, 0x41);
+            if (ok) {
+                tc_fence_after();
+                if (N0 > 0) { issue_qk(0, 0); umma_commit(&ctrl->s_full[0]); }
+                if (N1 > 0) { issue_qk(1, 0); umma_commit(&ctrl->s_full[1]); }
+                umma_commit(&ctrl->k_empty[0]);
+            }
+            for (int n = 0; ok && n < N; ++n) {
+                const int s = n % KV_SLOTS, s1 = (n + 1) % KV_SLOTS;
+                const uint32_t ph = (n / KV_SLOTS) & 1u, ph1 = ((n + 1) / KV_SLOTS) & 1u;
+                if (!(ok = mbar_wait_bounded(&ctrl->v_full[s], ph, abort_flag, p.status, 0x42))) break;
+                if (n < N0) {
+                    if (!(ok = mbar_wait_bounded(&ctrl->p_full[0], n & 1u, abort_flag, p.status, 0x43))) break;
+                    tc_fence_after();
+                    issue_pv(0, s, n > 0);
+                    if (n == N0 - 1) umma_commit(&ctrl->o_full[0]);
+                }
+                if (n + 1 < N) {
+                    if (!(ok = mbar_wait_bounded(&ctrl->k_full[s1], ph1, abort_flag, p.status, 0x44))) break;
+                    tc_fence_after();
+                }
+                if (n + 1 < N0) { issue_qk(0, s1); umma_commit(&ctrl->s_full[0]); }
+                if (n < N1) {
+                    if (!(ok = mbar_wait_bounded(&ctrl->p_full[1], n & 1u, abort_flag, p.status, 0x45))) break;
+                    tc_fence_after();
+                    issue_pv(1, s, n > 0);
+                    if (n == N1 - 1) umma_commit(&ctrl->o_full[1]);
+                }
+                umma_commit(&ctrl->v_empty[s]);
+                if (n + 1 < N1) { issue_qk(1, s1); umma_commit(&ctrl->s_full[1]); }
+                if (n + 1 < N) umma_commit(&ctrl->k_empty[s1]);
+            }
+        }
+    } else {
+        // ================================ softmax warpgroups ================================
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 224;\n" ::);
+        const int i = warp >> 2;                 // Q tile of this warpgroup
+        const int r = (warp & 3) * 32 + lane;    // row inside the tile == TMEM lane
+        const int Ni = ntile[i];
+        const int row = m0 + i * BM + r;         // row inside the sequence
+        const bool row_ok = row < sq;
+        const uint32_t lane_addr = tmem + ((uint32_t)((warp & 3) * 32) << 16);
+        const uint32_t tS = lane_addr + i * 128, tO = lane_addr + 256 + i * 128;
+        const int limit = p.causal ? min(sk - 1, row + shift) : sk - 1;  // last visible key of this row
+        const int tile_first_row = m0 + i * BM;
+
+        float m_used = -INFINITY;  // running max actually subtracted (scaled, base 2)
+        float l = 0.f;
+        bool ok = true;
+        for (int n = 0; n < Ni; ++n) {
+            if (!(ok = mbar_wait_bounded(&ctrl->s_full[i], n & 1u, abort_flag, p.status, 0x100 << i))) break;
+            tc_fence_after();
+            uint32_t sreg[128];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) tmem_ld32(tS + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&sreg[c * 32]));
+            tmem_wait_ld();
+            // mask the diagonal and tail tiles
+            const bool need_mask = (n * BN + BN > sk) || (p.causal && n * BN + BN - 1 > tile_first_row + shift);
+            if (need_mask) {
+#pragma unroll
+                for (int j = 0; j < 128; ++j)
+                    if (n * BN + j > limit) sreg[j] = 0xff800000u;  // -inf
+            }
+            float mx = -INFINITY;
+#pragma unroll
+            for (int j = 0; j < 128; ++j) mx = fmaxf(mx, __uint_as_float(sreg[j]));
+            mx *= p.scale_log2;  // scale > 0: max commutes with scaling
+            // raise the running max only on a jump of more than 2^8; rescale O in TMEM when that happens
+            const bool grow = mx > m_used + kRescaleThreshold;
+            if (n > 0 && __any_sync(0xffffffffu, grow)) {
+                const float alpha = grow ? fast_exp2(m_used - mx) : 1.f;  // exp2(-inf) = 0
+                l *= alpha;
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t t[32];
+                    tmem_ld32(tO + c * 32, t);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) t[j] = __float_as_uint(__uint_as_float(t[j]) * alpha);
+                    tmem_st32(tO + c * 32, t);
+                }
+                tmem_wait_st();
+            }
+            if (grow) m_used = mx;
+            const float msub = (m_used == -INFINITY) ? 0.f : m_used;
+            float psum = 0.f;
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                uint32_t pk[32];
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    const float p0 = fast_exp2(fmaf(__uint_as_float(sreg[c * 64 + 2 * j]), p.scale_log2, -msub));
+                    const float p1 = fast_exp2(fmaf(__uint_as_float(sreg[c * 64 + 2 * j + 1]), p.scale_log2, -msub));
+                    psum += p0 + p1;
+                    pk[j] = Elem<T>::pack2(p0, p1);
+                }
+                tmem_st32(tS + c * 32, pk);
+            }
+            l += psum;
+            tmem_wait_st();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&ctrl->p_full[i]);
+        }
+        // ---- epilogue: O / l and LSE ----
+        if (ok && Ni > 0) ok = mbar_wait_bounded(&ctrl->o_full[i], 0, abort_flag, p.status, 0x400 << i);
+        if (ok && tile_first_row < sq) {
+            tc_fence_after();
+            const float inv = l > 0.f ? 1.f / l : 0.f;
+            T* orow = (T*)p.o + ((q0 + row) * p.hq + h) * HD;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                uint32_t t[32];
+                if (Ni > 0) {
+                    tmem_ld32(tO + c * 32, t);
+                    tmem_wait_ld();
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) t[j] = 0u;
+                }
+                if (row_ok) {
+#pragma unroll
+                    for (int v4 = 0; v4 < 4; ++v4) {
+                        uint4 pk;
+                        pk.x = Elem<T>::pack2(__uint_as_float(t[v4 * 8 + 0]) * inv, __uint_as_float(t[v4 * 8 + 1]) * inv);
+                        pk.y = Elem<T>::pack2(__uint_as_float(t[v4 * 8 + 2]) * inv, __uint_as_float(t[v4 * 8 + 3]) * inv);
+                        pk.z = Elem<T>::pack2(__uint_as_float(t[v4 * 8 + 4]) * inv, __uint_as_float(t[v4 * 8 + 5]) * inv);
+                        pk.w = Elem<T>::pack2(__uint_as_float(t[v4 * 8 + 6]) * inv, __uint_as_float(t[v4 * 8 + 7]) * inv);
+                        *reinterpret_cast<uint4*>(orow + c * 32 + v4 * 8) = pk;
+                    }
+                }
+            }
+            if (p.lse && row_ok) {
+                float* lp = p.seqstart_q ? p.lse + (int64_t)h * p.total_q + q0 + row
+                                         : p.lse + ((int64_t)b * p.hq + h) * p.seqlen_q + row;
+                *lp = l > 0.f ? (m_used + log2f(l)) * 0.6931471805599453f : -INFINITY;
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 8) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;\n" ::"r"(tmem));
+    }
+}
+
+int make_map_3d(CUtensorMap* map, const void* base, int dtype, int64_t rows, int64_t heads) {
+    PFN_encodeTiled enc = get_encode_tiled();
+    FCK_REQUIRE(enc != nullptr, FLASHCK_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    const cuuint64_t dims[3] = {(cuuint64_t)HD, (cuuint64_t)heads, (cuuint64_t)(rows > 0 ? rows : 1)};
+    const cuuint64_t strides[2] = {(cuuint64_t)(HD * 2), (cuuint64_t)(heads * HD * 2)};
+    const cuuint32_t box[3] = {64, 1, (cuuint32_t)BM};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    const CUtensorMapDataType dt =
+        dtype == FLASHCK_DTYPE_BFLOAT16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    const CUresult r = enc(map, dt, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    FCK_REQUIRE(r == CUDA_SUCCESS, FLASHCK_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d) rows=%lld heads=%lld", (int)r,
+                (long long)rows, (long long)heads);
+    return FLASHCK_OK;
+}
+
+template <typename T>
+int launch_t(const FwdParams& p, const Sm100Dev& dev, cudaStream_t stream) {
+    const int64_t rows_q = p.seqstart_q ? p.total_q : p.batch * p.seqlen_q;
+    const int64_t rows_k = p.seqstart_k ? p.seqlen_k : p.batch * p.seqlen_k;  // group mode: packed total
+    CUtensorMap mq, mk, mv;
+    int rc;
+    if ((rc = make_map_3d(&mq, p.q, p.dtype, rows_q, p.hq))) return rc;
+    if ((rc = make_map_3d(&mk, p.k, p.dtype, rows_k, p.hkv))) return rc;
+    if ((rc = make_map_3d(&mv, p.v, p.dtype, rows_k, p.hkv))) return rc;
+    auto kern = fmha_fwd_sm100_kernel<T>;
+    const size_t smem = 1024 + (size_t)(2 + 2 * KV_SLOTS) * TILE_BYTES + sizeof(Ctrl);
+    static thread_local int configured_device = -1;
+    int devid = 0;
+    FCK_CUDA(cudaGetDevice(&devid));
+    if (configured_device != devid) {
+        FCK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        configured_device = devid;
+    }
+    const int mblocks = (int)((p.max_seqlen_q + 2 * BM - 1) / (2 * BM));
+    if (mblocks == 0 || p.batch == 0) return FLASHCK_OK;
+    dim3 grid(mblocks, (unsigned)p.hq, (unsigned)p.batch);
+    kern<<<grid, NTHREADS, smem, stream>>>(mq, mk, mv, dev);
+    FCK_CUDA(cudaGetLastError());
+    return FLASHCK_OK;
+}
+
+}  // namespace
+
+bool fwd_sm100_supported(const FwdParams& p) {
+    if (!g_use_sm100.load()) return false;
+    if (p.d != HD || p.dv != HD) return false;
+    if (p.block_table || p.kv_indptr || p.cache_batch_idx || p.seqlen_k64 || p.seqlen_k32) return false;
+    if ((p.seqstart_q == nullptr) != (p.seqstart_k == nullptr)) return false;
+    if (p.mask_type != 0 && !(p.mask_type <= 2 && p.wl < 0 && p.wr == 0)) return false;  // none or causal
+    if (p.hq > 65535 || p.batch > 65535) return false;
+    if (p.total_q >= (1ll << 31) || p.batch * p.seqlen_k >= (1ll << 31)) return false;
+    return true;
+}
+
+int launch_fwd_sm100(const FwdParams& p, cudaStream_t stream) {
+    int* status = device_status_ptr();
+    if (!status) return FLASHCK_ERR_CUDA;
+    Sm100Dev dev;
+    dev.o = p.o; dev.lse = p.lse; dev.seqstart_q = p.seqstart_q; dev.seqstart_k = p.seqstart_k; dev.status = status;
+    dev.batch = (int)p.batch; dev.seqlen_q = (int)p.seqlen_q; dev.seqlen_k = (int)p.seqlen_k;
+    dev.hq = (int)p.hq; dev.hkv = (int)p.hkv; dev.total_q = (int)p.total_q;
+    dev.causal = p.mask_type;
+    dev.scale_log2 = p.scale * 1.4426950408889634f;
+    if (p.dtype == FLASHCK_DTYPE_BFLOAT16) return launch_t<__nv_bfloat16>(p, dev, stream);
+    return launch_t<__half>(p, dev, stream);
+}
+
+int fwd_set_param(const char* key, int64_t value) {
+    if (!strcmp(key, "use_sm100")) { g_use_sm100 = value; return FLASHCK_OK; }
+    return FLASHCK_ERR_INVALID_ARGUMENT;
+}
+int fwd_get_param(const char* key, int64_t* value) {
+    if (!strcmp(key, "use_sm100")) { *value = g_use_sm100; return FLASHCK_OK; }
+    return FLASHCK_ERR_INVALID_ARGUMENT;
+}
+
 }  // namespace fck

@@ -51,6 +51,43 @@ def test_fmha_fwd_shapes_and_masks(sq, sk, d, mask):
     assert_lse_close(lse, lse_ref)
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("sq,sk,mt", [(384, 384, 1), (1000, 1000, 1), (300, 777, 0), (513, 1024, 2), (700, 300, 2),
+                                      (257, 257, 0), (128, 128, 1), (256, 2048, 2), (1, 500, 0)])
+def test_fmha_fwd_hdim128_many_tiles(dtype, sq, sk, mt):
+    # hdim 128 with no mask / causal goes to the tcgen05 instance: several 128-key tiles, both Q tiles of a CTA,
+    # ragged tails, bottom-right alignment with sq != sk
+    b, hq, hkv, d = 2, 4, 2, 128
+    q = normal_tensor((b, sq, hq, d), dtype, 1)
+    k = normal_tensor((b, sk, hkv, d), dtype, 2)
+    v = normal_tensor((b, sk, hkv, d), dtype, 3)
+    win = (-1, 0) if mt else (-1, -1)
+    o_ref, lse_ref = oracle.fmha_fwd(q, k, v, mask_type=mt, window=win)
+    o, lse = ops.fmha_fwd(_cu(q), _cu(k), _cu(v), window_size=win, mask_type=mt, return_lse=True)
+    assert_o_close(o, o_ref)
+    assert_lse_close(lse, lse_ref)
+
+
+def test_fmha_fwd_instances_agree():
+    # the tcgen05 instance and the general instance on the same problem
+    from flashck_b200 import _lib
+    dtype = torch.bfloat16
+    lens = [700, 130, 1025]
+    cu = to_seqstarts(lens)
+    q = normal_tensor((sum(lens), 8, 128), dtype, 5).to(DEV)
+    k = normal_tensor((sum(lens), 2, 128), dtype, 6).to(DEV)
+    v = normal_tensor((sum(lens), 2, 128), dtype, 7).to(DEV)
+    outs = []
+    for use in (1, 0):
+        _lib.set_instance_param(0, "use_sm100", use)
+        try:
+            outs.append(ops.fmha_fwd_var_len(q, k, v, cu.to(DEV), cu.to(DEV), max(lens), causal=True, return_lse=True))
+        finally:
+            _lib.set_instance_param(0, "use_sm100", 1)
+    assert_o_close(outs[0][0], outs[1][0])
+    assert_lse_close(outs[0][1], outs[1][1])
+
+
 def test_fmha_fwd_var_len_gqa():
     dtype = torch.bfloat16
     lens = [1, 64, 65, 200, 0, 333]
