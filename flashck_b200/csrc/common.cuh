@@ -156,20 +156,40 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// Bounded wait: gives up after ~`limit_cycles` SM cycles, ORs `code` into the device status word and into
+// try_wait with a suspend-time hint: the hardware parks the thread (no issue slots used) until the phase
+// completes or about `ns` nanoseconds have passed.
+__device__ __forceinline__ bool mbar_try_wait_hint(uint64_t* bar, uint32_t parity, uint32_t ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(ns)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait: gives up after about `kWaitLimitCycles` SM cycles, ORs `code` into the device status word and into
 // the CTA-wide abort flag, and returns false.  Once the abort flag is set every later wait returns at once.
+// The loop is kept to a few instructions per (hardware-suspended) probe so that waiting warps do not take issue
+// slots from the warps that compute; the clock and the abort flag are only looked at every 32 probes.
 constexpr long long kWaitLimitCycles = 2000000000LL;  // about one second
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
                                                   int* status, int code) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
+    uint32_t probes = 0;
     while (true) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if (*abort_flag) return false;
-        if (clock64() - t0 > kWaitLimitCycles) {
-            *abort_flag = code;
-            atomicOr(status, code);
-            return false;
+        if (mbar_try_wait_hint(bar, parity, 2000u)) return true;
+        if ((++probes & 31u) == 0u) {
+            if (*abort_flag) return false;
+            if (clock64() - t0 > kWaitLimitCycles) {
+                *abort_flag = code;
+                atomicOr(status, code);
+                return false;
+            }
         }
     }
 }

@@ -23,6 +23,7 @@
 // Every mbarrier wait is bounded; on expiry the CTA records a code in the device status word and drains.
 #include <atomic>
 #include <string.h>
+#include <type_traits>
 
 #include "kernels.h"
 
@@ -40,6 +41,7 @@ constexpr int NTHREADS = 384;
 constexpr float kRescaleThreshold = 8.f;  // log2 units
 
 std::atomic<int64_t> g_use_sm100{1};
+std::atomic<int64_t> g_poly8{3};  // column pairs of every 8 whose exp2 runs on the FMA pipe (0, 2, 3 or 4)
 
 struct Sm100Dev {
     void* o;
@@ -127,6 +129,35 @@ __device__ __forceinline__ constexpr uint32_t make_idesc(bool b_mn_major) {
            ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
 }
 
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float r;
+    asm("max.f32 %0, %1, %2, %3;\n" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+    return r;
+}
+__device__ __forceinline__ float ex2_fast(float x) {  // not volatile: the compiler may schedule it freely
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
+// 2^x for two values on the FMA pipe with packed f32x2 arithmetic: round-to-nearest split x = n + f,
+// f in [-0.5, 0.5], cubic for 2^f (max relative error 7.5e-5, far below the rounding of P to 16 bits), then n is
+// added to the exponent field.  The exp2 unit delivers 16 results per clock per SM -- as many cycles per
+// 128x128 tile as the two MMAs take -- so a share of the elements goes this way instead.
+__device__ __forceinline__ float2 exp2_poly2(float2 x) {
+    x.x = fmaxf(x.x, -126.f);
+    x.y = fmaxf(x.y, -126.f);
+    const float2 t = __fadd2_rn(x, make_float2(12582912.f, 12582912.f));  // 1.5 * 2^23: n lands in the low mantissa bits
+    const float2 nf = __fadd2_rn(t, make_float2(-12582912.f, -12582912.f));
+    const float2 f = __ffma2_rn(nf, make_float2(-1.f, -1.f), x);
+    float2 pl = __ffma2_rn(make_float2(0.055171605f, 0.055171605f), f, make_float2(0.24261111f, 0.24261111f));
+    pl = __ffma2_rn(pl, f, make_float2(0.69326097f, 0.69326097f));
+    pl = __ffma2_rn(pl, f, make_float2(0.99992806f, 0.99992806f));
+    float2 r;
+    r.x = __int_as_float(__float_as_int(pl.x) + (__float_as_int(t.x) << 23));
+    r.y = __int_as_float(__float_as_int(pl.y) + (__float_as_int(t.y) << 23));
+    return r;
+}
+
 // Shared-memory control block placed after the tiles.
 struct Ctrl {
     uint64_t q_full;
@@ -136,7 +167,7 @@ struct Ctrl {
     int abort_flag;
 };
 
-template <typename T>
+template <typename T, int NPOLY8>
 __global__ void __launch_bounds__(NTHREADS, 1)
 fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                       const __grid_constant__ CUtensorMap map_v, const Sm100Dev p) {
@@ -208,7 +239,10 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     const uint32_t tmem = ctrl->tmem_base;
 
     if (warp >= 8) {
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 48;\n" ::);
+        // Register budget.  The CTA is launched with 384 x 168 = 64512 registers; setmaxnreg.dec returns registers
+        // to the CTA's pool and setmaxnreg.inc waits -- without a bound -- until the pool can serve it, so the sum
+        // after the moves must stay below the launch allocation: 256 x 208 + 128 x 80 = 63488.
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 80;\n" ::);
         if (warp == 9 && lane == 0) {
             // ================================ TMA producer ================================
             tma_prefetch_desc(&map_q);
@@ -239,21 +273,29 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
             constexpr uint32_t idesc_pv = make_idesc<T>(true);
             const uint32_t tS[2] = {tmem, tmem + 128};
             const uint32_t tO[2] = {tmem + 256, tmem + 384};
+            // Descriptors are built once; per MMA only the 14-bit start-address field (16-byte units) advances,
+            // by compile-time offsets, so the issuing thread spends a few integer adds per instruction.
+            const uint64_t dQ0 = make_smem_desc(smem_u32(sQ), 0, 1024);
+            const uint64_t dQ1 = make_smem_desc(smem_u32(sQ + TILE_BYTES), 0, 1024);
+            const uint64_t dK0 = make_smem_desc(smem_u32(sK), 0, 1024);
+            const uint64_t dK1 = make_smem_desc(smem_u32(sK + TILE_BYTES), 0, 1024);
+            const uint64_t dV0 = make_smem_desc(smem_u32(sV), HALF_BYTES, 1024);
+            const uint64_t dV1 = make_smem_desc(smem_u32(sV + TILE_BYTES), HALF_BYTES, 1024);
             auto issue_qk = [&](int i, int s) {  // S_i = Q_i K^T : 8 steps of 16 along the head dim
-                const uint32_t qa = smem_u32(sQ + i * TILE_BYTES), ka = smem_u32(sK + s * TILE_BYTES);
+                const uint64_t qd = i ? dQ1 : dQ0, kd = s ? dK1 : dK0;
+                const uint32_t d = tS[i];
 #pragma unroll
                 for (int ks = 0; ks < HD / 16; ++ks) {
-                    const uint32_t off = (ks / 4) * HALF_BYTES + (ks % 4) * 32;
-                    umma_ss(tS[i], make_smem_desc(qa + off, 0, 1024), make_smem_desc(ka + off, 0, 1024), idesc_qk,
-                            ks > 0);
+                    const uint64_t off = (uint64_t)(((ks / 4) * HALF_BYTES + (ks % 4) * 32) >> 4);
+                    umma_ss(d, qd + off, kd + off, idesc_qk, ks > 0 ? 1u : 0u);
                 }
             };
             auto issue_pv = [&](int i, int s, bool accumulate) {  // O_i += P_i V : 8 steps of 16 keys
-                const uint32_t va = smem_u32(sV + s * TILE_BYTES);
+                const uint64_t vd = s ? dV1 : dV0;
+                const uint32_t d = tO[i], a = tS[i];
 #pragma unroll
                 for (int ks = 0; ks < BN / 16; ++ks)
-                    umma_ts(tO[i], tS[i] + ks * 8, make_smem_desc(va + ks * 2048, HALF_BYTES, 1024), idesc_pv,
-                            (accumulate || ks > 0) ? 1u : 0u);
+                    umma_ts(d, a + ks * 8, vd + (uint64_t)((ks * 2048) >> 4), idesc_pv, (accumulate || ks > 0) ? 1u : 0u);
             };
             bool ok = mbar_wait_bounded(&ctrl->q_full, 0, abort_flag, p.status, 0x40) &&
                       mbar_wait_bounded(&ctrl->k_full[0], 0, abort_flag, p.status, 0x41);
@@ -291,7 +333,7 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         }
     } else {
         // ================================ softmax warpgroups ================================
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 224;\n" ::);
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 208;\n" ::);
         const int i = warp >> 2;                 // Q tile of this warpgroup
         const int r = (warp & 3) * 32 + lane;    // row inside the tile == TMEM lane
         const int Ni = ntile[i];
@@ -319,9 +361,18 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                 for (int j = 0; j < 128; ++j)
                     if (n * BN + j > limit) sreg[j] = 0xff800000u;  // -inf
             }
-            float mx = -INFINITY;
+            float mx;
+            {
+                float a0 = -INFINITY, a1 = -INFINITY, a2 = -INFINITY, a3 = -INFINITY;  // four independent chains
 #pragma unroll
-            for (int j = 0; j < 128; ++j) mx = fmaxf(mx, __uint_as_float(sreg[j]));
+                for (int j = 0; j < 128; j += 8) {
+                    a0 = max3(a0, __uint_as_float(sreg[j]), __uint_as_float(sreg[j + 1]));
+                    a1 = max3(a1, __uint_as_float(sreg[j + 2]), __uint_as_float(sreg[j + 3]));
+                    a2 = max3(a2, __uint_as_float(sreg[j + 4]), __uint_as_float(sreg[j + 5]));
+                    a3 = max3(a3, __uint_as_float(sreg[j + 6]), __uint_as_float(sreg[j + 7]));
+                }
+                mx = fmaxf(max3(a0, a1, a2), a3);
+            }
             mx *= p.scale_log2;  // scale > 0: max commutes with scaling
             // raise the running max only on a jump of more than 2^8; rescale O in TMEM when that happens
             const bool grow = mx > m_used + kRescaleThreshold;
@@ -341,19 +392,35 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
             }
             if (grow) m_used = mx;
             const float msub = (m_used == -INFINITY) ? 0.f : m_used;
-            float psum = 0.f;
-#pragma unroll
-            for (int c = 0; c < 2; ++c) {
+            const float2 sc2 = make_float2(p.scale_log2, p.scale_log2), nm2 = make_float2(-msub, -msub);
+            float2 psa = make_float2(0.f, 0.f), psb = make_float2(0.f, 0.f);
+            // P = 2^(S * scale - max) for the 128 columns of the row, 64 at a time.  NPOLY8 of every 8 column pairs
+            // take the polynomial; tiles with masked (-inf) entries use the exp2 unit only, which returns exact
+            // zeros for them.  The two variants are separate straight-line loops so that the scheduler can
+            // interleave exp2-unit and FMA-pipe work across column pairs.
+            auto exp_half = [&](int c, auto use_poly_tag) {
+                constexpr int NP = decltype(use_poly_tag)::value;
                 uint32_t pk[32];
 #pragma unroll
                 for (int j = 0; j < 32; ++j) {
-                    const float p0 = fast_exp2(fmaf(__uint_as_float(sreg[c * 64 + 2 * j]), p.scale_log2, -msub));
-                    const float p1 = fast_exp2(fmaf(__uint_as_float(sreg[c * 64 + 2 * j + 1]), p.scale_log2, -msub));
-                    psum += p0 + p1;
-                    pk[j] = Elem<T>::pack2(p0, p1);
+                    const int e = c * 64 + 2 * j;
+                    const float2 x = __ffma2_rn(make_float2(__uint_as_float(sreg[e]), __uint_as_float(sreg[e + 1])), sc2, nm2);
+                    float2 pr;
+                    if (NP > 0 && ((j * NP) & 7) < NP) pr = exp2_poly2(x);
+                    else { pr.x = ex2_fast(x.x); pr.y = ex2_fast(x.y); }
+                    if (j & 1) psb = __fadd2_rn(psb, pr); else psa = __fadd2_rn(psa, pr);
+                    pk[j] = Elem<T>::pack2(pr.x, pr.y);
                 }
                 tmem_st32(tS + c * 32, pk);
+            };
+            if (need_mask) {
+                exp_half(0, std::integral_constant<int, 0>{});
+                exp_half(1, std::integral_constant<int, 0>{});
+            } else {
+                exp_half(0, std::integral_constant<int, NPOLY8>{});
+                exp_half(1, std::integral_constant<int, NPOLY8>{});
             }
+            const float psum = (psa.x + psa.y) + (psb.x + psb.y);
             l += psum;
             tmem_wait_st();
             tc_fence_before();
@@ -421,7 +488,7 @@ int make_map_3d(CUtensorMap* map, const void* base, int dtype, int64_t rows, int
     return FLASHCK_OK;
 }
 
-template <typename T>
+template <typename T, int NPOLY8>
 int launch_t(const FwdParams& p, const Sm100Dev& dev, cudaStream_t stream) {
     const int64_t rows_q = p.seqstart_q ? p.total_q : p.batch * p.seqlen_q;
     const int64_t rows_k = p.seqstart_k ? p.seqlen_k : p.batch * p.seqlen_k;  // group mode: packed total
@@ -430,7 +497,7 @@ int launch_t(const FwdParams& p, const Sm100Dev& dev, cudaStream_t stream) {
     if ((rc = make_map_3d(&mq, p.q, p.dtype, rows_q, p.hq))) return rc;
     if ((rc = make_map_3d(&mk, p.k, p.dtype, rows_k, p.hkv))) return rc;
     if ((rc = make_map_3d(&mv, p.v, p.dtype, rows_k, p.hkv))) return rc;
-    auto kern = fmha_fwd_sm100_kernel<T>;
+    auto kern = fmha_fwd_sm100_kernel<T, NPOLY8>;
     const size_t smem = 1024 + (size_t)(2 + 2 * KV_SLOTS) * TILE_BYTES + sizeof(Ctrl);
     static thread_local int configured_device = -1;
     int devid = 0;
@@ -469,16 +536,27 @@ int launch_fwd_sm100(const FwdParams& p, cudaStream_t stream) {
     dev.hq = (int)p.hq; dev.hkv = (int)p.hkv; dev.total_q = (int)p.total_q;
     dev.causal = p.mask_type;
     dev.scale_log2 = p.scale * 1.4426950408889634f;
-    if (p.dtype == FLASHCK_DTYPE_BFLOAT16) return launch_t<__nv_bfloat16>(p, dev, stream);
-    return launch_t<__half>(p, dev, stream);
+    const bool bf16 = p.dtype == FLASHCK_DTYPE_BFLOAT16;
+    switch ((int)g_poly8.load()) {
+        case 0: return bf16 ? launch_t<__nv_bfloat16, 0>(p, dev, stream) : launch_t<__half, 0>(p, dev, stream);
+        case 2: return bf16 ? launch_t<__nv_bfloat16, 2>(p, dev, stream) : launch_t<__half, 2>(p, dev, stream);
+        case 4: return bf16 ? launch_t<__nv_bfloat16, 4>(p, dev, stream) : launch_t<__half, 4>(p, dev, stream);
+        default: return bf16 ? launch_t<__nv_bfloat16, 3>(p, dev, stream) : launch_t<__half, 3>(p, dev, stream);
+    }
 }
 
 int fwd_set_param(const char* key, int64_t value) {
     if (!strcmp(key, "use_sm100")) { g_use_sm100 = value; return FLASHCK_OK; }
+    if (!strcmp(key, "poly8")) {
+        if (value != 0 && value != 2 && value != 3 && value != 4) return FLASHCK_ERR_INVALID_ARGUMENT;
+        g_poly8 = value;
+        return FLASHCK_OK;
+    }
     return FLASHCK_ERR_INVALID_ARGUMENT;
 }
 int fwd_get_param(const char* key, int64_t* value) {
     if (!strcmp(key, "use_sm100")) { *value = g_use_sm100; return FLASHCK_OK; }
+    if (!strcmp(key, "poly8")) { *value = g_poly8; return FLASHCK_OK; }
     return FLASHCK_ERR_INVALID_ARGUMENT;
 }
 
