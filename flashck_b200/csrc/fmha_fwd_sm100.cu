@@ -51,6 +51,8 @@ struct Sm100Dev {
     int* status;
     int batch, seqlen_q, seqlen_k, hq, hkv, total_q;
     int causal;       // 0 none, 1 top-left, 2 bottom-right
+    int num_levels;   // row blocks of the longest sequence (128 rows when heads are paired, else 256)
+    int pair_heads;   // the two Q tiles of a work item are two q heads of one kv group
     float scale_log2;
 };
 
@@ -158,14 +160,112 @@ __device__ __forceinline__ float2 exp2_poly2(float2 x) {
     return r;
 }
 
+constexpr int kMaxBatch = 1024;   // sequences the on-chip schedule can hold
+constexpr int kMaxLevels = 1024;  // row blocks per sequence the on-chip schedule can hold
+constexpr int kMaxRounds = 96;    // work items per CTA decoded up front (later ones are decoded on the fly)
+
+// One work item = two 128-row Q tiles that share their K/V tiles.  With an even GQA ratio the tiles are the same
+// 128 rows of two neighbouring q heads of one kv group: both see the same keys, so they run the same number of
+// steps and hit the diagonal together.  Otherwise they are two consecutive row tiles of one head.
+struct Item {
+    int valid;
+    int b, kh, sq, sk, shift, N;
+    int h[2];     // q head of each tile
+    int row0[2];  // first row (inside the sequence) of each tile
+    int nt[2];    // key tiles each Q tile needs (0: the tile does not exist or sees nothing)
+    int q0, k0;   // first row of the sequence in the packed Q / K buffers
+};
+
 // Shared-memory control block placed after the tiles.
 struct Ctrl {
-    uint64_t q_full;
+    uint64_t q_full, q_empty;
     uint64_t k_full[KV_SLOTS], k_empty[KV_SLOTS], v_full[KV_SLOTS], v_empty[KV_SLOTS];
     uint64_t s_full[2], p_full[2], o_full[2];
     uint32_t tmem_base;
     int abort_flag;
+    int num_levels;                     // row-block indices 0 .. num_levels-1
+    int level_start[kMaxLevels + 1];    // first work item of each level; level 0 = highest block index
+    int nblk[kMaxBatch];                // row blocks of each sequence
+    int seq_q0[kMaxBatch], seq_sq[kMaxBatch], seq_k0[kMaxBatch], seq_sk[kMaxBatch];  // first row / length, Q and K
+    Item items[kMaxRounds];             // this CTA's work list
 };
+
+// Item taken by CTA `cta` in round `rnd` of a grid of `g` CTAs: rounds alternate direction (snake order), so that
+// with items sorted by decreasing cost no CTA collects the most expensive item of every round.
+__device__ __forceinline__ int item_of_round(int rnd, int cta, int g) {
+    return rnd * g + ((rnd & 1) ? (g - 1 - cta) : cta);
+}
+
+// Work items are ordered by decreasing row-block index (under a causal mask: decreasing cost), then by sequence,
+// then by head, so that the q heads of a GQA group -- which read the same K/V -- run at the same time on
+// neighbouring SMs and share those tiles through L2.  Warp-collective.
+__device__ __forceinline__ void decode_item(const Ctrl* ctrl, const Sm100Dev& p, int w, int lane, Item& it) {
+    int lo = 0, hi = ctrl->num_levels;  // last level whose start is <= w
+    while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (ctrl->level_start[mid] <= w) lo = mid; else hi = mid;
+    }
+    const int blk = ctrl->num_levels - 1 - lo;
+    const int per_seq = p.pair_heads ? p.hq / 2 : p.hq;  // items per (sequence, row block)
+    const int j = w - ctrl->level_start[lo];
+    int bj = j / per_seq;
+    const int hj = j - bj * per_seq;
+    int b = 0;
+    for (int base = 0; base < p.batch; base += 32) {  // the bj-th sequence that has a block `blk`
+        const bool has = (base + lane < p.batch) && ctrl->nblk[base + lane] > blk;
+        const uint32_t m = __ballot_sync(0xffffffffu, has);
+        const int c = __popc(m);
+        if (bj < c) {
+            b = base + __fns(m, 0, bj + 1);
+            break;
+        }
+        bj -= c;
+    }
+    it.valid = 1;
+    it.b = b;
+    it.q0 = ctrl->seq_q0[b];
+    it.sq = ctrl->seq_sq[b];
+    it.k0 = ctrl->seq_k0[b];
+    it.sk = ctrl->seq_sk[b];
+    if (p.pair_heads) {
+        it.h[0] = 2 * hj;
+        it.h[1] = 2 * hj + 1;
+        it.row0[0] = it.row0[1] = blk * BM;
+    } else {
+        it.h[0] = it.h[1] = hj;
+        it.row0[0] = blk * 2 * BM;
+        it.row0[1] = blk * 2 * BM + BM;
+    }
+    it.kh = it.h[0] / (p.hq / p.hkv);
+    // key tiles each Q tile needs: all of them, or up to its last row's diagonal
+    it.shift = (p.causal == 2) ? it.sk - it.sq : 0;
+    const int nk_all = (it.sk + BN - 1) / BN;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int first = it.row0[i];
+        int n = 0;
+        if (first < it.sq) {
+            n = nk_all;
+            if (p.causal) {
+                const int hi_key = min(it.sq, first + BM) - 1 + it.shift;  // last visible key of the tile's last row
+                n = hi_key < 0 ? 0 : min(nk_all, hi_key / BN + 1);
+            }
+        }
+        it.nt[i] = n;
+    }
+    it.N = max(it.nt[0], it.nt[1]);
+}
+
+// The work item of round `rnd`: from the table filled at start-up, or decoded on the fly.  Warp-collective.
+__device__ __forceinline__ void get_item(const Ctrl* ctrl, const Sm100Dev& p, int rnd, int total_items, int lane, Item& it) {
+    if (rnd < kMaxRounds) {
+        it = ctrl->items[rnd];
+        return;
+    }
+    const int w = item_of_round(rnd, blockIdx.x, gridDim.x);
+    it.valid = 0;
+    if (w < total_items) decode_item(ctrl, p, w, lane, it);
+}
 
 template <typename T, int NPOLY8>
 __global__ void __launch_bounds__(NTHREADS, 1)
@@ -173,35 +273,6 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                       const __grid_constant__ CUtensorMap map_v, const Sm100Dev p) {
     extern __shared__ uint8_t smem_raw[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int b = blockIdx.z, h = blockIdx.y;
-    const int mblk = gridDim.x - 1 - blockIdx.x;  // longest (causal) row blocks first
-    const int kh = h / (p.hq / p.hkv);
-
-    const int64_t q0 = p.seqstart_q ? p.seqstart_q[b] : (int64_t)b * p.seqlen_q;
-    const int sq = p.seqstart_q ? (int)(p.seqstart_q[b + 1] - p.seqstart_q[b]) : p.seqlen_q;
-    const int64_t k0 = p.seqstart_k ? p.seqstart_k[b] : (int64_t)b * p.seqlen_k;
-    const int sk = p.seqstart_k ? (int)(p.seqstart_k[b + 1] - p.seqstart_k[b]) : p.seqlen_k;
-    const int m0 = mblk * 2 * BM;
-    if (m0 >= sq) return;  // uniform for the CTA; nothing has been set up yet
-
-    // key tiles each Q tile needs: all of them, or up to its last row's diagonal
-    const int shift = (p.causal == 2) ? sk - sq : 0;
-    const int nk_all = (sk + BN - 1) / BN;
-    int ntile[2];
-#pragma unroll
-    for (int i = 0; i < 2; ++i) {
-        const int first = m0 + i * BM;
-        if (first >= sq) { ntile[i] = 0; continue; }
-        const int last = min(sq, first + BM) - 1;
-        int n = nk_all;
-        if (p.causal) {
-            const int hi = last + shift;  // last visible key of the last row
-            n = hi < 0 ? 0 : min(nk_all, hi / BN + 1);
-        }
-        ntile[i] = n;
-    }
-    const int N0 = ntile[0], N1 = ntile[1];
-    const int N = max(N0, N1);
 
     // ---- shared memory carve-up ----
     const uint32_t raw = smem_u32(smem_raw);
@@ -214,6 +285,7 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
 
     if (threadIdx.x == 0) {
         mbar_init(&ctrl->q_full, 1);
+        mbar_init(&ctrl->q_empty, 1);
         for (int s = 0; s < KV_SLOTS; ++s) {
             mbar_init(&ctrl->k_full[s], 1);
             mbar_init(&ctrl->k_empty[s], 1);
@@ -226,6 +298,7 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
             mbar_init(&ctrl->o_full[i], 1);
         }
         ctrl->abort_flag = 0;
+        ctrl->num_levels = p.num_levels;
         mbar_fence_init();
     }
     if (warp == 8) {  // TMEM: all 512 columns (S0 S1 O0 O1)
@@ -233,41 +306,97 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
             smem_u32(&ctrl->tmem_base)));
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
     }
+    // ---- schedule: blocks per sequence, then the first work item of every level ----
+    for (int b = threadIdx.x; b < p.batch; b += NTHREADS) {
+        const int64_t q0 = p.seqstart_q ? p.seqstart_q[b] : (int64_t)b * p.seqlen_q;
+        const int64_t k0 = p.seqstart_k ? p.seqstart_k[b] : (int64_t)b * p.seqlen_k;
+        const int sq = p.seqstart_q ? (int)(p.seqstart_q[b + 1] - q0) : p.seqlen_q;
+        const int sk = p.seqstart_k ? (int)(p.seqstart_k[b + 1] - k0) : p.seqlen_k;
+        ctrl->seq_q0[b] = (int)q0;  // row indices fit 31 bits (checked on the host)
+        ctrl->seq_sq[b] = sq;
+        ctrl->seq_k0[b] = (int)k0;
+        ctrl->seq_sk[b] = sk;
+        const int rows_per_block = p.pair_heads ? BM : 2 * BM;
+        ctrl->nblk[b] = min(p.num_levels, (sq + rows_per_block - 1) / rows_per_block);
+    }
+    __syncthreads();
+    for (int lv = threadIdx.x; lv < p.num_levels; lv += NTHREADS) {  // count of sequences that have block index lv
+        int c = 0;
+        for (int b = 0; b < p.batch; ++b) c += ctrl->nblk[b] > lv;
+        ctrl->level_start[p.num_levels - lv] = c * (p.pair_heads ? p.hq / 2 : p.hq);  // summed up below
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int run = 0;
+        ctrl->level_start[0] = 0;
+        for (int lv = 1; lv <= p.num_levels; ++lv) {
+            run += ctrl->level_start[lv];
+            ctrl->level_start[lv] = run;
+        }
+    }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = ctrl->tmem_base;
+    const int total_items = ctrl->level_start[p.num_levels];
+    const int rounds = (total_items + (int)gridDim.x - 1) / (int)gridDim.x;
+    for (int rnd = warp; rnd < min(rounds, kMaxRounds); rnd += NTHREADS / 32) {  // this CTA's work list
+        const int w = item_of_round(rnd, blockIdx.x, gridDim.x);
+        Item it;
+        it.valid = 0;
+        if (w < total_items) decode_item(ctrl, p, w, lane, it);
+        if (lane == 0) ctrl->items[rnd] = it;
+    }
+    __syncthreads();
 
     if (warp >= 8) {
         // Register budget.  The CTA is launched with 384 x 168 = 64512 registers; setmaxnreg.dec returns registers
         // to the CTA's pool and setmaxnreg.inc waits -- without a bound -- until the pool can serve it, so the sum
         // after the moves must stay below the launch allocation: 256 x 208 + 128 x 80 = 63488.
         asm volatile("setmaxnreg.dec.sync.aligned.u32 80;\n" ::);
-        if (warp == 9 && lane == 0) {
+        if (warp == 9) {
             // ================================ TMA producer ================================
-            tma_prefetch_desc(&map_q);
-            tma_prefetch_desc(&map_k);
-            tma_prefetch_desc(&map_v);
-            const int q_tiles = (N1 > 0 || m0 + BM < sq) ? 2 : 1;
-            mbar_expect_tx(&ctrl->q_full, q_tiles * TILE_BYTES);
-            for (int i = 0; i < q_tiles; ++i)
-                for (int hb = 0; hb < 2; ++hb)
-                    tma_load_3d(sQ + i * TILE_BYTES + hb * HALF_BYTES, &map_q, &ctrl->q_full, hb * 64, h,
-                                (int)(q0 + m0 + i * BM));
-            for (int n = 0; n < N; ++n) {
-                const int s = n % KV_SLOTS;
-                const uint32_t ph = (n / KV_SLOTS) & 1u;
-                const int row = (int)(k0 + (int64_t)n * BN);
-                if (!mbar_wait_bounded(&ctrl->k_empty[s], ph ^ 1u, abort_flag, p.status, 0x10)) break;
-                mbar_expect_tx(&ctrl->k_full[s], TILE_BYTES);
-                for (int hb = 0; hb < 2; ++hb)
-                    tma_load_3d(sK + s * TILE_BYTES + hb * HALF_BYTES, &map_k, &ctrl->k_full[s], hb * 64, kh, row);
-                if (!mbar_wait_bounded(&ctrl->v_empty[s], ph ^ 1u, abort_flag, p.status, 0x20)) break;
-                mbar_expect_tx(&ctrl->v_full[s], TILE_BYTES);
-                for (int hb = 0; hb < 2; ++hb)
-                    tma_load_3d(sV + s * TILE_BYTES + hb * HALF_BYTES, &map_v, &ctrl->v_full[s], hb * 64, kh, row);
+            if (lane == 0) {
+                tma_prefetch_desc(&map_q);
+                tma_prefetch_desc(&map_k);
+                tma_prefetch_desc(&map_v);
             }
-        } else if (warp == 8 && lane == 0 && N > 0) {
+            uint32_t kv_cnt = 0, q_cnt = 0;  // K/V tiles and Q loads issued so far (ring positions)
+            for (int rnd = 0; rnd < rounds; ++rnd) {
+                Item it;
+                get_item(ctrl, p, rnd, total_items, lane, it);
+                if (!it.valid || it.N == 0) continue;
+                bool ok = true;
+                if (lane == 0) {
+                    ok = mbar_wait_bounded(&ctrl->q_empty, (q_cnt & 1u) ^ 1u, abort_flag, p.status, 0x08);
+                    if (ok) {
+                        const int q_tiles = (it.row0[1] < it.sq) ? 2 : 1;
+                        mbar_expect_tx(&ctrl->q_full, q_tiles * TILE_BYTES);
+                        for (int hb = 0; hb < 2; ++hb)
+                            tma_load_3d(sQ + hb * HALF_BYTES, &map_q, &ctrl->q_full, hb * 64, it.h[0], it.q0 + it.row0[0]);
+                        if (q_tiles == 2)
+                            for (int hb = 0; hb < 2; ++hb)
+                                tma_load_3d(sQ + TILE_BYTES + hb * HALF_BYTES, &map_q, &ctrl->q_full, hb * 64, it.h[1],
+                                            it.q0 + it.row0[1]);
+                    }
+                    for (int n = 0; ok && n < it.N; ++n, ++kv_cnt) {
+                        const int s = kv_cnt % KV_SLOTS;
+                        const uint32_t ph = (kv_cnt / KV_SLOTS) & 1u;
+                        const int row = it.k0 + n * BN;
+                        if (!(ok = mbar_wait_bounded(&ctrl->k_empty[s], ph ^ 1u, abort_flag, p.status, 0x10))) break;
+                        mbar_expect_tx(&ctrl->k_full[s], TILE_BYTES);
+                        for (int hb = 0; hb < 2; ++hb)
+                            tma_load_3d(sK + s * TILE_BYTES + hb * HALF_BYTES, &map_k, &ctrl->k_full[s], hb * 64, it.kh, row);
+                        if (!(ok = mbar_wait_bounded(&ctrl->v_empty[s], ph ^ 1u, abort_flag, p.status, 0x20))) break;
+                        mbar_expect_tx(&ctrl->v_full[s], TILE_BYTES);
+                        for (int hb = 0; hb < 2; ++hb)
+                            tma_load_3d(sV + s * TILE_BYTES + hb * HALF_BYTES, &map_v, &ctrl->v_full[s], hb * 64, it.kh, row);
+                    }
+                }
+                ++q_cnt;
+                if (!__shfl_sync(0xffffffffu, ok, 0)) break;
+            }
+        } else if (warp == 8) {
             // ================================ MMA issuer ================================
             constexpr uint32_t idesc_qk = make_idesc<T>(false);
             constexpr uint32_t idesc_pv = make_idesc<T>(true);
@@ -297,38 +426,58 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                 for (int ks = 0; ks < BN / 16; ++ks)
                     umma_ts(d, a + ks * 8, vd + (uint64_t)((ks * 2048) >> 4), idesc_pv, (accumulate || ks > 0) ? 1u : 0u);
             };
-            bool ok = mbar_wait_bounded(&ctrl->q_full, 0, abort_flag, p.status, 0x40) &&
-                      mbar_wait_bounded(&ctrl->k_full[0], 0, abort_flag, p.status, 0x41);
-            if (ok) {
-                tc_fence_after();
-                if (N0 > 0) { issue_qk(0, 0); umma_commit(&ctrl->s_full[0]); }
-                if (N1 > 0) { issue_qk(1, 0); umma_commit(&ctrl->s_full[1]); }
-                umma_commit(&ctrl->k_empty[0]);
-            }
-            for (int n = 0; ok && n < N; ++n) {
-                const int s = n % KV_SLOTS, s1 = (n + 1) % KV_SLOTS;
-                const uint32_t ph = (n / KV_SLOTS) & 1u, ph1 = ((n + 1) / KV_SLOTS) & 1u;
-                if (!(ok = mbar_wait_bounded(&ctrl->v_full[s], ph, abort_flag, p.status, 0x42))) break;
-                if (n < N0) {
-                    if (!(ok = mbar_wait_bounded(&ctrl->p_full[0], n & 1u, abort_flag, p.status, 0x43))) break;
-                    tc_fence_after();
-                    issue_pv(0, s, n > 0);
-                    if (n == N0 - 1) umma_commit(&ctrl->o_full[0]);
+            // running counts give ring slots and barrier parities across work items
+            uint32_t kv_cnt = 0, q_cnt = 0, sc0 = 0, sc1 = 0;
+            for (int rnd = 0; rnd < rounds; ++rnd) {
+                Item it;
+                get_item(ctrl, p, rnd, total_items, lane, it);
+                if (!it.valid || it.N == 0) continue;
+                bool ok = true;
+                if (lane == 0) {
+                    const int N = it.N, N0 = it.nt[0], N1 = it.nt[1];
+                    const int s0 = kv_cnt % KV_SLOTS;
+                    ok = mbar_wait_bounded(&ctrl->q_full, q_cnt & 1u, abort_flag, p.status, 0x40) &&
+                         mbar_wait_bounded(&ctrl->k_full[s0], (kv_cnt / KV_SLOTS) & 1u, abort_flag, p.status, 0x41);
+                    if (ok) {
+                        tc_fence_after();
+                        if (N0 > 0) { issue_qk(0, s0); umma_commit(&ctrl->s_full[0]); }
+                        if (N1 > 0) { issue_qk(1, s0); umma_commit(&ctrl->s_full[1]); }
+                        umma_commit(&ctrl->k_empty[s0]);
+                        if (N == 1) umma_commit(&ctrl->q_empty);  // Q may be replaced once these MMAs are done
+                    }
+                    for (int n = 0; ok && n < N; ++n) {
+                        const uint32_t kc = kv_cnt + n;
+                        const int s = kc % KV_SLOTS, s1 = (kc + 1) % KV_SLOTS;
+                        const uint32_t ph = (kc / KV_SLOTS) & 1u, ph1 = ((kc + 1) / KV_SLOTS) & 1u;
+                        if (!(ok = mbar_wait_bounded(&ctrl->v_full[s], ph, abort_flag, p.status, 0x42))) break;
+                        if (n < N0) {
+                            if (!(ok = mbar_wait_bounded(&ctrl->p_full[0], (sc0 + n) & 1u, abort_flag, p.status, 0x43))) break;
+                            tc_fence_after();
+                            issue_pv(0, s, n > 0);
+                            if (n == N0 - 1) umma_commit(&ctrl->o_full[0]);
+                        }
+                        if (n + 1 < N) {
+                            if (!(ok = mbar_wait_bounded(&ctrl->k_full[s1], ph1, abort_flag, p.status, 0x44))) break;
+                            tc_fence_after();
+                        }
+                        if (n + 1 < N0) { issue_qk(0, s1); umma_commit(&ctrl->s_full[0]); }
+                        if (n < N1) {
+                            if (!(ok = mbar_wait_bounded(&ctrl->p_full[1], (sc1 + n) & 1u, abort_flag, p.status, 0x45))) break;
+                            tc_fence_after();
+                            issue_pv(1, s, n > 0);
+                            if (n == N1 - 1) umma_commit(&ctrl->o_full[1]);
+                        }
+                        umma_commit(&ctrl->v_empty[s]);
+                        if (n + 1 < N1) { issue_qk(1, s1); umma_commit(&ctrl->s_full[1]); }
+                        if (n + 1 < N) umma_commit(&ctrl->k_empty[s1]);
+                        if (n + 2 == N) umma_commit(&ctrl->q_empty);  // the last QK^T of the item has been issued
+                    }
                 }
-                if (n + 1 < N) {
-                    if (!(ok = mbar_wait_bounded(&ctrl->k_full[s1], ph1, abort_flag, p.status, 0x44))) break;
-                    tc_fence_after();
-                }
-                if (n + 1 < N0) { issue_qk(0, s1); umma_commit(&ctrl->s_full[0]); }
-                if (n < N1) {
-                    if (!(ok = mbar_wait_bounded(&ctrl->p_full[1], n & 1u, abort_flag, p.status, 0x45))) break;
-                    tc_fence_after();
-                    issue_pv(1, s, n > 0);
-                    if (n == N1 - 1) umma_commit(&ctrl->o_full[1]);
-                }
-                umma_commit(&ctrl->v_empty[s]);
-                if (n + 1 < N1) { issue_qk(1, s1); umma_commit(&ctrl->s_full[1]); }
-                if (n + 1 < N) umma_commit(&ctrl->k_empty[s1]);
+                kv_cnt += it.N;
+                sc0 += it.nt[0];
+                sc1 += it.nt[1];
+                ++q_cnt;
+                if (!__shfl_sync(0xffffffffu, ok, 0)) break;
             }
         }
     } else {
@@ -336,129 +485,144 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         asm volatile("setmaxnreg.inc.sync.aligned.u32 208;\n" ::);
         const int i = warp >> 2;                 // Q tile of this warpgroup
         const int r = (warp & 3) * 32 + lane;    // row inside the tile == TMEM lane
-        const int Ni = ntile[i];
-        const int row = m0 + i * BM + r;         // row inside the sequence
-        const bool row_ok = row < sq;
         const uint32_t lane_addr = tmem + ((uint32_t)((warp & 3) * 32) << 16);
         const uint32_t tS = lane_addr + i * 128, tO = lane_addr + 256 + i * 128;
-        const int limit = p.causal ? min(sk - 1, row + shift) : sk - 1;  // last visible key of this row
-        const int tile_first_row = m0 + i * BM;
-
-        float m_used = -INFINITY;  // running max actually subtracted (scaled, base 2)
-        float l = 0.f;
+        uint32_t sc = 0, oc = 0;  // S tiles and O accumulators consumed so far (barrier parities)
         bool ok = true;
-        for (int n = 0; n < Ni; ++n) {
-            if (!(ok = mbar_wait_bounded(&ctrl->s_full[i], n & 1u, abort_flag, p.status, 0x100 << i))) break;
-            tc_fence_after();
-            uint32_t sreg[128];
+        for (int rnd = 0; ok && rnd < rounds; ++rnd) {
+            Item it;
+            get_item(ctrl, p, rnd, total_items, lane, it);
+            if (!it.valid) continue;
+            const int Ni = i ? it.nt[1] : it.nt[0], head = i ? it.h[1] : it.h[0];
+            const int sq = it.sq, sk = it.sk, shift = it.shift;
+            const int tile_first_row = i ? it.row0[1] : it.row0[0];
+            const int row = tile_first_row + r;      // row inside the sequence
+            const bool row_ok = row < sq;
+            const int limit = p.causal ? min(sk - 1, row + shift) : sk - 1;  // last visible key of this row
+
+            float m_used = -INFINITY;  // running max actually subtracted (scaled, base 2)
+            float l = 0.f;
+            for (int n = 0; n < Ni; ++n) {
+                // warp-uniform outcome: the loads, votes and stores below are warp-collective
+                ok = __all_sync(0xffffffffu, mbar_wait_bounded(&ctrl->s_full[i], (sc + n) & 1u, abort_flag, p.status, 0x100 << i));
+                if (!ok) break;
+                tc_fence_after();
+                uint32_t sreg[128];
 #pragma unroll
-            for (int c = 0; c < 4; ++c) tmem_ld32(tS + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&sreg[c * 32]));
-            tmem_wait_ld();
-            // mask the diagonal and tail tiles
-            const bool need_mask = (n * BN + BN > sk) || (p.causal && n * BN + BN - 1 > tile_first_row + shift);
-            if (need_mask) {
+                for (int c = 0; c < 4; ++c) tmem_ld32(tS + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&sreg[c * 32]));
+                tmem_wait_ld();
+                // mask the diagonal and tail tiles
+                const bool need_mask = (n * BN + BN > sk) || (p.causal && n * BN + BN - 1 > tile_first_row + shift);
+                if (need_mask) {
 #pragma unroll
-                for (int j = 0; j < 128; ++j)
-                    if (n * BN + j > limit) sreg[j] = 0xff800000u;  // -inf
-            }
-            float mx;
-            {
-                float a0 = -INFINITY, a1 = -INFINITY, a2 = -INFINITY, a3 = -INFINITY;  // four independent chains
-#pragma unroll
-                for (int j = 0; j < 128; j += 8) {
-                    a0 = max3(a0, __uint_as_float(sreg[j]), __uint_as_float(sreg[j + 1]));
-                    a1 = max3(a1, __uint_as_float(sreg[j + 2]), __uint_as_float(sreg[j + 3]));
-                    a2 = max3(a2, __uint_as_float(sreg[j + 4]), __uint_as_float(sreg[j + 5]));
-                    a3 = max3(a3, __uint_as_float(sreg[j + 6]), __uint_as_float(sreg[j + 7]));
+                    for (int j = 0; j < 128; ++j)
+                        if (n * BN + j > limit) sreg[j] = 0xff800000u;  // -inf
                 }
-                mx = fmaxf(max3(a0, a1, a2), a3);
+                float mx;
+                {
+                    float a0 = -INFINITY, a1 = -INFINITY, a2 = -INFINITY, a3 = -INFINITY;  // four independent chains
+#pragma unroll
+                    for (int j = 0; j < 128; j += 8) {
+                        a0 = max3(a0, __uint_as_float(sreg[j]), __uint_as_float(sreg[j + 1]));
+                        a1 = max3(a1, __uint_as_float(sreg[j + 2]), __uint_as_float(sreg[j + 3]));
+                        a2 = max3(a2, __uint_as_float(sreg[j + 4]), __uint_as_float(sreg[j + 5]));
+                        a3 = max3(a3, __uint_as_float(sreg[j + 6]), __uint_as_float(sreg[j + 7]));
+                    }
+                    mx = fmaxf(max3(a0, a1, a2), a3);
+                }
+                mx *= p.scale_log2;  // scale > 0: max commutes with scaling
+                // raise the running max only on a jump of more than 2^8; rescale O in TMEM when that happens
+                const bool grow = mx > m_used + kRescaleThreshold;
+                if (n > 0 && __any_sync(0xffffffffu, grow)) {
+                    const float alpha = grow ? fast_exp2(m_used - mx) : 1.f;  // exp2(-inf) = 0
+                    l *= alpha;
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        uint32_t t[32];
+                        tmem_ld32(tO + c * 32, t);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) t[j] = __float_as_uint(__uint_as_float(t[j]) * alpha);
+                        tmem_st32(tO + c * 32, t);
+                    }
+                    tmem_wait_st();
+                }
+                if (grow) m_used = mx;
+                const float msub = (m_used == -INFINITY) ? 0.f : m_used;
+                const float2 sc2 = make_float2(p.scale_log2, p.scale_log2), nm2 = make_float2(-msub, -msub);
+                float2 psa = make_float2(0.f, 0.f), psb = make_float2(0.f, 0.f);
+                // P = 2^(S * scale - max) for the 128 columns of the row, 64 at a time.  NPOLY8 of every 8 column
+                // pairs take the polynomial; tiles with masked (-inf) entries use the exp2 unit only, which returns
+                // exact zeros for them.  The two variants are separate straight-line loops so that the scheduler
+                // can interleave exp2-unit and FMA-pipe work across column pairs.
+                auto exp_half = [&](int c, auto use_poly_tag) {
+                    constexpr int NP = decltype(use_poly_tag)::value;
+                    uint32_t pk[32];
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const int e = c * 64 + 2 * j;
+                        const float2 x = __ffma2_rn(make_float2(__uint_as_float(sreg[e]), __uint_as_float(sreg[e + 1])), sc2, nm2);
+                        float2 pr;
+                        if (NP > 0 && ((j * NP) & 7) < NP) pr = exp2_poly2(x);
+                        else { pr.x = ex2_fast(x.x); pr.y = ex2_fast(x.y); }
+                        if (j & 1) psb = __fadd2_rn(psb, pr); else psa = __fadd2_rn(psa, pr);
+                        pk[j] = Elem<T>::pack2(pr.x, pr.y);
+                    }
+                    tmem_st32(tS + c * 32, pk);
+                };
+                if (need_mask) {
+                    exp_half(0, std::integral_constant<int, 0>{});
+                    exp_half(1, std::integral_constant<int, 0>{});
+                } else {
+                    exp_half(0, std::integral_constant<int, NPOLY8>{});
+                    exp_half(1, std::integral_constant<int, NPOLY8>{});
+                }
+                l += (psa.x + psa.y) + (psb.x + psb.y);
+                tmem_wait_st();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&ctrl->p_full[i]);
             }
-            mx *= p.scale_log2;  // scale > 0: max commutes with scaling
-            // raise the running max only on a jump of more than 2^8; rescale O in TMEM when that happens
-            const bool grow = mx > m_used + kRescaleThreshold;
-            if (n > 0 && __any_sync(0xffffffffu, grow)) {
-                const float alpha = grow ? fast_exp2(m_used - mx) : 1.f;  // exp2(-inf) = 0
-                l *= alpha;
+            if (!ok) break;
+            sc += Ni;
+            // ---- epilogue: O / l and LSE ----
+            if (Ni > 0) {
+                ok = __all_sync(0xffffffffu, mbar_wait_bounded(&ctrl->o_full[i], oc & 1u, abort_flag, p.status, 0x400 << i));
+                if (!ok) break;
+                ++oc;
+                tc_fence_after();
+            }
+            if (tile_first_row < sq) {
+                const float inv = l > 0.f ? 1.f / l : 0.f;
+                T* orow = (T*)p.o + ((int64_t)(it.q0 + row) * p.hq + head) * HD;
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
                     uint32_t t[32];
-                    tmem_ld32(tO + c * 32, t);
-                    tmem_wait_ld();
+                    if (Ni > 0) {
+                        tmem_ld32(tO + c * 32, t);
+                        tmem_wait_ld();
+                    } else {
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) t[j] = __float_as_uint(__uint_as_float(t[j]) * alpha);
-                    tmem_st32(tO + c * 32, t);
-                }
-                tmem_wait_st();
-            }
-            if (grow) m_used = mx;
-            const float msub = (m_used == -INFINITY) ? 0.f : m_used;
-            const float2 sc2 = make_float2(p.scale_log2, p.scale_log2), nm2 = make_float2(-msub, -msub);
-            float2 psa = make_float2(0.f, 0.f), psb = make_float2(0.f, 0.f);
-            // P = 2^(S * scale - max) for the 128 columns of the row, 64 at a time.  NPOLY8 of every 8 column pairs
-            // take the polynomial; tiles with masked (-inf) entries use the exp2 unit only, which returns exact
-            // zeros for them.  The two variants are separate straight-line loops so that the scheduler can
-            // interleave exp2-unit and FMA-pipe work across column pairs.
-            auto exp_half = [&](int c, auto use_poly_tag) {
-                constexpr int NP = decltype(use_poly_tag)::value;
-                uint32_t pk[32];
+                        for (int j = 0; j < 32; ++j) t[j] = 0u;
+                    }
+                    if (row_ok) {
 #pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    const int e = c * 64 + 2 * j;
-                    const float2 x = __ffma2_rn(make_float2(__uint_as_float(sreg[e]), __uint_as_float(sreg[e + 1])), sc2, nm2);
-                    float2 pr;
-                    if (NP > 0 && ((j * NP) & 7) < NP) pr = exp2_poly2(x);
-                    else { pr.x = ex2_fast(x.x); pr.y = ex2_fast(x.y); }
-                    if (j & 1) psb = __fadd2_rn(psb, pr); else psa = __fadd2_rn(psa, pr);
-                    pk[j] = Elem<T>::pack2(pr.x, pr.y);
-                }
-                tmem_st32(tS + c * 32, pk);
-            };
-            if (need_mask) {
-                exp_half(0, std::integral_constant<int, 0>{});
-                exp_half(1, std::integral_constant<int, 0>{});
-            } else {
-                exp_half(0, std::integral_constant<int, NPOLY8>{});
-                exp_half(1, std::integral_constant<int, NPOLY8>{});
-            }
-            const float psum = (psa.x + psa.y) + (psb.x + psb.y);
-            l += psum;
-            tmem_wait_st();
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&ctrl->p_full[i]);
-        }
-        // ---- epilogue: O / l and LSE ----
-        if (ok && Ni > 0) ok = mbar_wait_bounded(&ctrl->o_full[i], 0, abort_flag, p.status, 0x400 << i);
-        if (ok && tile_first_row < sq) {
-            tc_fence_after();
-            const float inv = l > 0.f ? 1.f / l : 0.f;
-            T* orow = (T*)p.o + ((q0 + row) * p.hq + h) * HD;
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                uint32_t t[32];
-                if (Ni > 0) {
-                    tmem_ld32(tO + c * 32, t);
-                    tmem_wait_ld();
-                } else {
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) t[j] = 0u;
-                }
-                if (row_ok) {
-#pragma unroll
-                    for (int v4 = 0; v4 < 4; ++v4) {
-                        uint4 pk;
-                        pk.x = Elem<T>::pack2(__uint_as_float(t[v4 * 8 + 0]) * inv, __uint_as_float(t[v4 * 8 + 1]) * inv);
-                        pk.y = Elem<T>::pack2(__uint_as_float(t[v4 * 8 + 2]) * inv, __uint_as_float(t[v4 * 8 + 3]) * inv);
-                        pk.z = Elem<T>::pack2(__uint_as_float(t[v4 * 8 + 4]) * inv, __uint_as_float(t[v4 * 8 + 5]) * inv);
-                        pk.w = Elem<T>::pack2(__uint_as_float(t[v4 * 8 + 6]) * inv, __uint_as_float(t[v4 * 8 + 7]) * inv);
-                        *reinterpret_cast<uint4*>(orow + c * 32 + v4 * 8) = pk;
+                        for (int v4 = 0; v4 < 4; ++v4) {
+                            uint4 pk;
+                            pk.x = Elem<T>::pack2(__uint_as_float(t[v4 * 8 + 0]) * inv, __uint_as_float(t[v4 * 8 + 1]) * inv);
+                            pk.y = Elem<T>::pack2(__uint_as_float(t[v4 * 8 + 2]) * inv, __uint_as_float(t[v4 * 8 + 3]) * inv);
+                            pk.z = Elem<T>::pack2(__uint_as_float(t[v4 * 8 + 4]) * inv, __uint_as_float(t[v4 * 8 + 5]) * inv);
+                            pk.w = Elem<T>::pack2(__uint_as_float(t[v4 * 8 + 6]) * inv, __uint_as_float(t[v4 * 8 + 7]) * inv);
+                            *reinterpret_cast<uint4*>(orow + c * 32 + v4 * 8) = pk;
+                        }
                     }
                 }
-            }
-            if (p.lse && row_ok) {
-                float* lp = p.seqstart_q ? p.lse + (int64_t)h * p.total_q + q0 + row
-                                         : p.lse + ((int64_t)b * p.hq + h) * p.seqlen_q + row;
-                *lp = l > 0.f ? (m_used + log2f(l)) * 0.6931471805599453f : -INFINITY;
+                if (p.lse && row_ok) {
+                    float* lp = p.seqstart_q ? p.lse + (int64_t)head * p.total_q + it.q0 + row
+                                             : p.lse + ((int64_t)it.b * p.hq + head) * p.seqlen_q + row;
+                    *lp = l > 0.f ? (m_used + log2f(l)) * 0.6931471805599453f : -INFINITY;
+                }
+                // the O reads above are complete (wait::ld) before this warp's next P store releases the next PV
             }
         }
     }
@@ -506,10 +670,9 @@ int launch_t(const FwdParams& p, const Sm100Dev& dev, cudaStream_t stream) {
         FCK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         configured_device = devid;
     }
-    const int mblocks = (int)((p.max_seqlen_q + 2 * BM - 1) / (2 * BM));
-    if (mblocks == 0 || p.batch == 0) return FLASHCK_OK;
-    dim3 grid(mblocks, (unsigned)p.hq, (unsigned)p.batch);
-    kern<<<grid, NTHREADS, smem, stream>>>(mq, mk, mv, dev);
+    if (p.max_seqlen_q == 0 || p.batch == 0) return FLASHCK_OK;
+    // persistent: one CTA per SM walks the device-side work list
+    kern<<<sm_count(), NTHREADS, smem, stream>>>(mq, mk, mv, dev);
     FCK_CUDA(cudaGetLastError());
     return FLASHCK_OK;
 }
@@ -522,7 +685,7 @@ bool fwd_sm100_supported(const FwdParams& p) {
     if (p.block_table || p.kv_indptr || p.cache_batch_idx || p.seqlen_k64 || p.seqlen_k32) return false;
     if ((p.seqstart_q == nullptr) != (p.seqstart_k == nullptr)) return false;
     if (p.mask_type != 0 && !(p.mask_type <= 2 && p.wl < 0 && p.wr == 0)) return false;  // none or causal
-    if (p.hq > 65535 || p.batch > 65535) return false;
+    if (p.batch > kMaxBatch || (p.max_seqlen_q + BM - 1) / BM > kMaxLevels) return false;  // on-chip schedule
     if (p.total_q >= (1ll << 31) || p.batch * p.seqlen_k >= (1ll << 31)) return false;
     return true;
 }
@@ -535,6 +698,8 @@ int launch_fwd_sm100(const FwdParams& p, cudaStream_t stream) {
     dev.batch = (int)p.batch; dev.seqlen_q = (int)p.seqlen_q; dev.seqlen_k = (int)p.seqlen_k;
     dev.hq = (int)p.hq; dev.hkv = (int)p.hkv; dev.total_q = (int)p.total_q;
     dev.causal = p.mask_type;
+    dev.pair_heads = ((p.hq / p.hkv) % 2 == 0) ? 1 : 0;
+    dev.num_levels = (int)((p.max_seqlen_q + (dev.pair_heads ? BM : 2 * BM) - 1) / (dev.pair_heads ? BM : 2 * BM));
     dev.scale_log2 = p.scale * 1.4426950408889634f;
     const bool bf16 = p.dtype == FLASHCK_DTYPE_BFLOAT16;
     switch ((int)g_poly8.load()) {
