@@ -139,6 +139,31 @@ def make_decode(seed: int, device, batch=64, lo=1024, hi=32768, page=16, hq=HQ, 
             "page": page, "hq": hq, "hkv": hkv}
 
 
+def make_append_decode(seed: int, device, batch=32, lo=2048, hi=16384, page=16):
+    """BASELINE config 4: a paged cache holding `ctx` tokens per sequence with room for 1..16 appended ones."""
+    from flashck_b200.utils.inputs import rotary_cos_sin
+    ctx = uniform_seqlens(batch, lo, hi, seed)
+    new = uniform_seqlens(batch, 1, 16, seed + 1)
+    cap = [c + n for c, n in zip(ctx, new)]
+    w = make_decode(seed + 2, device, lens=cap, page=page)
+    total = sum(new)
+    g = torch.Generator(device=device).manual_seed(seed + 3)
+    mk = lambda h: torch.randn(total, h, D, generator=g, device=device, dtype=torch.float32).to(torch.bfloat16)
+    cos, sin = rotary_cos_sin(max(cap) + 1, D, torch.bfloat16)
+    w.update({"ctx": ctx, "new": new, "qn": mk(HQ), "kn": mk(HKV), "vn": mk(HKV), "cu_new": to_seqstarts(new).to(device),
+              "ctx_len": torch.tensor(ctx, dtype=torch.int32, device=device), "cos": cos.to(device), "sin": sin.to(device),
+              "append_bytes": float(total * (2 * HKV * D * 2 * 2 + 2 * HQ * D * 2))})
+    return w
+
+
+def make_long_decode(seed: int, device, world: int, batch=4, ctx=524288, page=64, hq=64, hkv=8):
+    """BASELINE config 5: this rank's contiguous page shard of `batch` contexts of `ctx` tokens (1/world of each)."""
+    local = ctx // world
+    w = make_decode(seed, device, lens=[local] * batch, page=page, hq=hq, hkv=hkv)
+    w["total_bytes"] = float(batch * ctx * hkv * 2 * D * 2)
+    return w
+
+
 def time_steps(fn, steps, warmup, barrier=None):
     """Device time of `steps` calls of fn, in ms (CUDA events on the current stream)."""
     for _ in range(warmup):
@@ -184,7 +209,7 @@ def cpu_prefill_sample(w, budget_flops=1.5e12):
                       f"{fl:.3g} FLOP) in {dt:.2f} s", "seconds": dt}
 
 
-def cpu_decode_sample(w, nseq=8):
+def cpu_decode_sample(w, nseq=48):
     from oracle import cpu as oracle
     lens = w["lens"][:nseq]
     page = w["page"]
@@ -406,6 +431,68 @@ def main():
         if rank == 0 and not args.no_cpu_baseline:
             extra["decode"]["cpu_baseline"] = cpu_decode_sample(wd)
         del wd, ws
+
+    # ------------------------------------------------------------------ append + decode (config 4)
+    if not args.no_decode and not args.small:
+        wa = make_append_decode(777 + rank, device)
+        S4 = ops.default_num_splits(len(wa["lens"]))
+        cu_n, max_new = wa["cu_new"], max(wa["new"])
+        ws4 = ops.splitkv_workspace(wa["qn"], D, S4, cu_n)
+
+        def append_decode_step():
+            ops.fmha_fwd_append_kv(wa["qn"], wa["k"], wa["v"], wa["kn"], wa["vn"], wa["ctx_len"], wa["cos"], wa["sin"],
+                                   block_table=wa["table"], cu_seqlens_q=cu_n, cu_seqlens_knew=cu_n)
+            return ops.fmha_fwd_splitkv(wa["qn"], wa["k"], wa["v"], seqlen_k=wa["seqlen"], block_table=wa["table"],
+                                        cu_seqlens_q=cu_n, max_seqlen_q=max_new, num_splits=S4, causal=True,
+                                        workspace=ws4, return_lse=True)
+
+        asteps = max(steps, 20)
+        ms_a = max_over_ranks(time_steps(append_decode_step, asteps, warmup, barrier))
+        a_bytes = wa["bytes"] + wa["append_bytes"]
+        extra["append_decode"] = {
+            "metric": "appendkv_plus_splitkv_decode_hbm_gbs", "value": sum_over_ranks(a_bytes) * asteps / (ms_a * 1e-3) / 1e9,
+            "unit": "GB/s", "ms_per_step": ms_a / asteps, "steps": asteps,
+            "config": {"workload": "append 1-16 tokens with interleaved RoPE, then split-KV decode (BASELINE config 4): batch 32 "
+                                   "per GPU, 32/8 heads, hdim 128, ctx~U[2048,16384], page 16",
+                       "tokens_per_gpu": sum(wa["lens"]), "new_tokens_per_gpu": sum(wa["new"]),
+                       "algorithmic_bytes_per_gpu_step": a_bytes, "num_splits": S4},
+            "roofline": {"bound": "hbm", "achieved": a_bytes * asteps / (ms_a * 1e-3) / 1e9, "peak": peaks["hbm_gbs"],
+                         "unit": "GB/s", "frac": a_bytes * asteps / (ms_a * 1e-3) / 1e9 / peaks["hbm_gbs"], "traffic": None,
+                         "peak_source": peaks["source"], "note": "append-KV + split-KV + combine kernels timed together"},
+            "gpu_launches": 3 * asteps,
+        }
+        del wa, ws4
+
+    # ------------------------------------------------------------------ sequence-sharded long-context decode (config 5)
+    if not args.no_decode and not args.small:
+        from flashck_b200 import dist as fdist
+        wl = make_long_decode(999 + rank, device, world)
+        S5 = ops.default_num_splits(len(wl["lens"]))
+        ws5 = ops.splitkv_workspace(wl["q"], D, S5)
+        if dist is not None:  # q is replicated
+            dist.broadcast(wl["q"], src=0)
+
+        def long_decode_step():
+            return fdist.sequence_sharded_decode(wl["q"], wl["k"], wl["v"], wl["table"], wl["seqlen"], num_splits=S5,
+                                                 workspace=ws5, return_lse=True)
+
+        lsteps = max(steps, 20)
+        ms_l = max_over_ranks(time_steps(long_decode_step, lsteps, warmup, barrier))
+        gbs_l = wl["total_bytes"] * lsteps / (ms_l * 1e-3) / 1e9
+        extra["long_decode"] = {
+            "metric": "sequence_sharded_decode_hbm_gbs", "value": gbs_l, "unit": "GB/s", "ms_per_step": ms_l / lsteps,
+            "steps": lsteps, "scaling": "strong",
+            "config": {"workload": "long-context decode (BASELINE config 5): batch 4, seqlen_q 1, 64/8 heads, hdim 128, "
+                                   "ctx 524288 per sequence, page 64, KV pages sharded contiguously over the GPUs; "
+                                   "local split-KV + fp32 merge, one all-gather of the partials, final merge",
+                       "total_kv_bytes": wl["total_bytes"], "num_splits": S5,
+                       "gather_bytes_per_rank": 4 * fdist.partial_numel(4, 1, 64, D), "parallelism": f"sp{world}"},
+            "roofline": {"bound": "hbm", "achieved": gbs_l / world, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                         "frac": gbs_l / world / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"],
+                         "note": "per GPU; split-KV, two merges and the all-gather timed together"},
+            "gpu_launches": 3 * lsteps,
+        }
+        del wl, ws5
 
     if rank == 0 and not args.no_cpu_baseline:
         cb = cpu_prefill_sample(w)

@@ -27,6 +27,7 @@ SIGNATURES = {
     "FmhaFwdSplitKV": ([_P] * 11 + [_I64] * 11 + [_F, _I64, _I64, _U32, _P, _I], _I),
     "FmhaFwdSplitKVCombine": ([_P] * 4 + [_I64] * 6 + [_P, _P, _I], _I),
     "FmhaSplitKVCombine": ([_P] * 4 + [_I64] * 6 + [_P, _P, _I], _I),
+    "FmhaFwdSplitKVCombineStrided": ([_P] * 4 + [_I64] * 5 + [ctypes.POINTER(_I64), ctypes.POINTER(_I64), _I, _P], _I),
     "FmhaFwdSplitKVStatic": ([_P] * 10 + [_I64] * 11 + [_F, _I64, _I64, _U32, _P, _I], _I),
     "FmhaFwdAppendKV": ([_P] * 12 + [_I64] * 9 + [_I, _I64, _I64, _P, _I], _I),
     "FlashckSetInstanceParam": ([_I, ctypes.c_char_p, _I64], _I),

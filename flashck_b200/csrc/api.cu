@@ -255,6 +255,21 @@ int FmhaFwdSplitKVCombine(void* lse_acc, void* o_acc, void* o, int64_t* q_seq_st
     return launch_combine(p, (cudaStream_t)stream);
 }
 
+int FmhaFwdSplitKVCombineStrided(void* lse_acc, void* o_acc, void* o, void* lse, int64_t batch, int64_t rows, int64_t hq,
+                                 int64_t dv, int64_t num_splits, const int64_t* lse_strides, const int64_t* o_strides,
+                                 int out_dtype, void* stream) {
+    FCK_REQUIRE(lse_acc && o_acc && o && lse_strides && o_strides, FLASHCK_ERR_INVALID_ARGUMENT,
+                "FmhaFwdSplitKVCombineStrided: null pointer argument");
+    FCK_REQUIRE(batch >= 0 && rows >= 0 && hq > 0 && dv > 0, FLASHCK_ERR_INVALID_ARGUMENT,
+                "FmhaFwdSplitKVCombineStrided: bad sizes");
+    CombineParams p{};
+    p.lse_acc = (const float*)lse_acc; p.o_acc = (const float*)o_acc; p.o = o; p.lse = (float*)lse;
+    p.bs = batch; p.rows = rows; p.hq = hq; p.dv = dv; p.num_splits = num_splits; p.dtype = out_dtype;
+    p.strided = true;
+    for (int i = 0; i < 4; ++i) { p.lse_strides[i] = lse_strides[i]; p.o_strides[i] = o_strides[i]; }
+    return launch_combine(p, (cudaStream_t)stream);
+}
+
 int FmhaSplitKVCombine(void* lse_acc, void* o_acc, void* o, int64_t* q_seq_start, int64_t batch, int64_t q_seq_len,
                        int64_t hq, int64_t dv, int64_t q_max_seq_len, int64_t num_splits, void* stream, void* lse,
                        int dtype) {

@@ -3,21 +3,26 @@
 // (core/profiling/attention/fmha_fwd/fmha_fwd_codegen.cc:86-118) behind the C symbol FmhaFwd
 // (attention_kernels/fmha_fwd/fmha_fwd_jinja.h:124-147), batch and group mode, GQA, fp32 LSE.
 //
-// One CTA (384 threads, one per SM: it owns all 512 TMEM columns) computes 256 query rows of one head as two
-// 128-row tiles that ping-pong through the pipeline:
-//   warp 9      TMA producer: Q once (4 boxes of 64 x 128, 128-byte swizzle), then K and V tiles of 128 keys
-//               into two-slot rings, mbarrier expect-tx.
+// Persistent kernel: one CTA per SM (384 threads; it owns all 512 TMEM columns) walks a work list that every CTA
+// derives on chip from the sequence lengths: items sorted by decreasing row-block index (decreasing cost under a
+// causal mask), dealt to the CTAs in snake order.  A work item is two 128-row Q tiles that share their K/V tiles:
+// the same rows of two neighbouring q heads of a GQA group when the group size is even (both tiles then run the
+// same number of steps and meet the diagonal together), else two consecutive row tiles of one head.  The two
+// tiles ping-pong through the pipeline:
+//   warp 9      TMA producer: Q tiles of the item (4 boxes of 64 x 128, 128-byte swizzle), then K and V tiles of
+//               128 keys into two-slot rings that run on across work items; mbarrier expect-tx.
 //   warp 8      MMA issuer (one elected thread): S_i = Q_i K^T with tcgen05.mma (both operands in shared
 //               memory, K-major), O_i += P_i V with the A operand P_i read from tensor memory and V taken
 //               MN-major straight from its [key][hdim] tile.  Accumulators live in TMEM: S0,S1 (128 columns
-//               each, fp32) and O0,O1 (128 columns each).  tcgen05.commit signals the consumers.
+//               each, fp32) and O0,O1 (128 columns each).  tcgen05.commit signals the consumers.  Shared-memory
+//               descriptors are built once; per instruction only the start-address field advances.
 //   warps 0-3 / 4-7   softmax warpgroup of tile 0 / 1: thread r owns row r (TMEM lane r), so row max and row sum
-//               need no shuffles.  tcgen05.ld S -> registers, fp32 online softmax in base 2, P rounded to the
-//               element dtype and stored with tcgen05.st over the first 64 columns of S_i (the next QK^T of the
-//               tile is issued after the PV that reads P, and the tensor pipe runs in order).  The running max is
-//               only raised -- and O_i rescaled in TMEM -- when it grows by more than 2^8, so the correction
-//               is off the steady-state path; the final 1/l normalisation and the O / LSE stores are done by the
-//               same warpgroup.
+//               need no shuffles.  tcgen05.ld S -> registers, fp32 online softmax in base 2 with packed f32x2
+//               arithmetic, P rounded to the element dtype and stored with tcgen05.st over the first 64 columns
+//               of S_i (the next QK^T of the tile is issued after the PV that reads P, and the tensor pipe runs
+//               in order).  The running max is only raised -- and O_i rescaled in TMEM -- when it grows by more
+//               than 2^8, so the correction is off the steady-state path; the final 1/l normalisation and the
+//               O / LSE stores are done by the same warpgroup while the MMA warp already starts the next item.
 // K/V tiles hidden by the causal mask are skipped; only diagonal and tail tiles pay for masking.
 // The GQA group's q heads run in neighbouring CTAs and share K/V through L2 (no cluster multicast).
 // Every mbarrier wait is bounded; on expiry the CTA records a code in the device status word and drains.
@@ -41,7 +46,7 @@ constexpr int NTHREADS = 384;
 constexpr float kRescaleThreshold = 8.f;  // log2 units
 
 std::atomic<int64_t> g_use_sm100{1};
-std::atomic<int64_t> g_poly8{3};  // column pairs of every 8 whose exp2 runs on the FMA pipe (0, 2, 3 or 4)
+std::atomic<int64_t> g_poly8{0};  // column pairs of every 8 whose exp2 runs on the FMA pipe (0, 2, 3 or 4)
 
 struct Sm100Dev {
     void* o;
@@ -703,10 +708,10 @@ int launch_fwd_sm100(const FwdParams& p, cudaStream_t stream) {
     dev.scale_log2 = p.scale * 1.4426950408889634f;
     const bool bf16 = p.dtype == FLASHCK_DTYPE_BFLOAT16;
     switch ((int)g_poly8.load()) {
-        case 0: return bf16 ? launch_t<__nv_bfloat16, 0>(p, dev, stream) : launch_t<__half, 0>(p, dev, stream);
         case 2: return bf16 ? launch_t<__nv_bfloat16, 2>(p, dev, stream) : launch_t<__half, 2>(p, dev, stream);
         case 4: return bf16 ? launch_t<__nv_bfloat16, 4>(p, dev, stream) : launch_t<__half, 4>(p, dev, stream);
-        default: return bf16 ? launch_t<__nv_bfloat16, 3>(p, dev, stream) : launch_t<__half, 3>(p, dev, stream);
+        case 3: return bf16 ? launch_t<__nv_bfloat16, 3>(p, dev, stream) : launch_t<__half, 3>(p, dev, stream);
+        default: return bf16 ? launch_t<__nv_bfloat16, 0>(p, dev, stream) : launch_t<__half, 0>(p, dev, stream);
     }
 }
 

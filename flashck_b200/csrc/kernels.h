@@ -12,7 +12,10 @@ struct CombineParams {
     void* o;               // [bs, rows, hq, dv] in dtype
     float* lse;            // [bs, hq, rows] or nullptr
     int64_t bs, rows, hq, dv, num_splits;
-    int dtype;
+    int dtype;              // output element type: 3 float16, 4 bfloat16, 7 float32
+    bool strided;           // use the strides below instead of the reference layout
+    int64_t lse_strides[4]; // lse_acc strides in elements: batch, head, split, row
+    int64_t o_strides[4];   // o_acc strides in elements: batch, head, split, row (hdim is contiguous)
 };
 int launch_combine(const CombineParams& p, cudaStream_t stream);
 

@@ -69,8 +69,8 @@ struct Sched {
     bool per_batch;  // mode B: one piece per sequence (num_splits == 1)
 };
 
-template <typename T, int D, int HK>
-__global__ void __launch_bounds__((HK + 1) * 32, 1)
+template <typename T, int D, int HK, int MT>
+__global__ void __launch_bounds__((HK * MT + 1) * 32, 1)
 splitkv_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                       const DecodeDev p) {
     constexpr int DH = D / 64;                       // 128-byte column groups per row
@@ -98,7 +98,7 @@ splitkv_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
         for (int s = 0; s < stages; ++s) {
             mbar_init(&full_k[s], 1);
             mbar_init(&full_v[s], 1);
-            mbar_init(&empty[s], HK);
+            mbar_init(&empty[s], HK * MT);
         }
         *abort_flag = 0;
         mbar_fence_init();
@@ -178,7 +178,7 @@ splitkv_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
 
     const int hgroup = blockIdx.z;  // kv heads [hgroup*HK, hgroup*HK + HK)
 
-    if (warp == HK) {
+    if (warp == HK * MT) {
         // =========================== producer warp ===========================================
         if (lane == 0) {
             tma_prefetch_desc(&map_k);
@@ -206,7 +206,7 @@ splitkv_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
                 const int tb = min(g_hi, sm_prefix[b + 1]) - sm_prefix[b];
                 if (tb <= ta) continue;
                 // rows of this m-tile exist in this sequence?  (the consumers skip the same segments)
-                if ((int)blockIdx.y * 16 >= seq_len_q(p, b) * G) continue;
+                if ((int)blockIdx.y * MT * 16 >= seq_len_q(p, b) * G) continue;
                 const int64_t bphys = p.cache_batch_idx ? p.cache_batch_idx[b] : b;
                 const int64_t kstart = p.seqstart_k ? p.seqstart_k[b] : 0;
                 const int t0 = sm_tile0[b];
@@ -257,8 +257,11 @@ splitkv_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
     }
 
     // =============================== consumer warps =============================================
-    const int kh = hgroup * HK + warp;  // kv head of this warp
-    const int mt = blockIdx.y;          // 16-row tile of the (token, group-head) rows
+    // MT warps share one kv head: warp w works on head w / MT and on 16-row tile w % MT of the (token, group-head)
+    // rows, so that up to 16*MT query rows per kv head are served by one pass over the K/V tiles in shared memory
+    const int hw = warp / MT;
+    const int kh = hgroup * HK + hw;
+    const int mt = blockIdx.y * MT + warp % MT;
     const int quad = lane >> 2, qlane = lane & 3;
     const int lm = lane >> 3, lr = lane & 7;  // ldmatrix: matrix id / row within the 8x8 matrix
     uint32_t it = 0;
@@ -285,7 +288,20 @@ splitkv_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
             if (tb <= ta) continue;
             const int sq = seq_len_q(p, b);
             const int rows = sq * G;
-            if (mt * 16 >= rows) continue;
+            if ((int)blockIdx.y * MT * 16 >= rows) continue;  // no row tile of this CTA exists here (the producer skips too)
+            if (MT > 1 && mt * 16 >= rows) {
+                // this warp's row tile does not exist in this sequence, but its partners use the tiles: keep the
+                // stage accounting in step
+                for (int t = ta; t < tb; ++t, ++it) {
+                    const int s = it % stages;
+                    const uint32_t ph = (it / stages) & 1u;
+                    if (!mbar_wait_bounded(&full_k[s], ph, abort_flag, p.status, 2)) return;
+                    if (!mbar_wait_bounded(&full_v[s], ph, abort_flag, p.status, 4)) return;
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&empty[s]);
+                }
+                continue;
+            }
             const int len = seq_len_k(p, b);
             const int split = sc.per_batch ? 0 : piece - sm_prefix[b] / sc.piece;
             const int64_t q0 = p.seqstart_q ? p.seqstart_q[b] : (int64_t)b * p.seqlen_q;
@@ -337,7 +353,7 @@ splitkv_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
                         const int dh = ks / 4;
                         const int c = 2 * (ks % 4) + (lm & 1);
                         uint32_t bfr[4];
-                        ldmatrix_x4(bfr, kbase + (dh * HK + warp) * HEAD_BYTES + key * 128 + ((c ^ (key & 7)) << 4));
+                        ldmatrix_x4(bfr, kbase + (dh * HK + hw) * HEAD_BYTES + key * 128 + ((c ^ (key & 7)) << 4));
                         mma_16816<T>(sacc[0], qa[ks], bfr[0], bfr[1]);
                         mma_16816<T>(sacc[1], qa[ks], bfr[2], bfr[3]);
                     }
@@ -405,7 +421,7 @@ splitkv_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
                         const int dh = g / 8, c = g % 8;
                         uint32_t bfr[4];
                         ldmatrix_x4_trans(bfr,
-                                          vbase + (dh * HK + warp) * HEAD_BYTES + key * 128 + ((c ^ (key & 7)) << 4));
+                                          vbase + (dh * HK + hw) * HEAD_BYTES + key * 128 + ((c ^ (key & 7)) << 4));
                         mma_16816<T>(o[2 * j], pa, bfr[0], bfr[1]);
                         mma_16816<T>(o[2 * j + 1], pa, bfr[2], bfr[3]);
                     }
@@ -467,7 +483,7 @@ int make_pool_map(CUtensorMap* map, const void* base, int dtype, int64_t pages, 
     return FLASHCK_OK;
 }
 
-template <typename T, int D, int HK>
+template <typename T, int D, int HK, int MT>
 int launch_inst(const SplitKVParams& p, const DecodeDev& dev_in, cudaStream_t stream) {
     DecodeDev dev = dev_in;
     constexpr int TILE_BYTES = kTok * HK * D * 2;
@@ -493,7 +509,7 @@ int launch_inst(const SplitKVParams& p, const DecodeDev& dev_in, cudaStream_t st
     rc = make_pool_map(&mv, p.v, p.dtype, pages, page_tokens, p.hkv, D, HK);
     if (rc) return rc;
 
-    auto kern = splitkv_decode_kernel<T, D, HK>;
+    auto kern = splitkv_decode_kernel<T, D, HK, MT>;
     static thread_local int configured_device = -1;  // per instantiation
     int devid = 0;
     FCK_CUDA(cudaGetDevice(&devid));
@@ -502,22 +518,40 @@ int launch_inst(const SplitKVParams& p, const DecodeDev& dev_in, cudaStream_t st
         configured_device = devid;
     }
     const int G = (int)(p.hq / p.hkv);
-    const int mtiles = (int)((p.max_seqlen_q * G + 15) / 16);
+    const int mtiles = (int)((p.max_seqlen_q * G + 16 * MT - 1) / (16 * MT));
     int gx = (int)((int64_t)sm_count() * g_ctas_per_sm_x100.load() / 100);
     if (gx < 1) gx = 1;
     dim3 grid(gx, mtiles, (unsigned)(p.hkv / HK));
-    kern<<<grid, (HK + 1) * 32, smem, stream>>>(mk, mv, dev);
+    kern<<<grid, (HK * MT + 1) * 32, smem, stream>>>(mk, mv, dev);
     FCK_CUDA(cudaGetLastError());
     return FLASHCK_OK;
 }
 
-template <typename T, int D>
+// Instance choice: MT = row tiles (of 16 query rows x group heads) served per pass, HK = kv heads per CTA;
+// HK * MT <= 8 consumer warps.  Decode (one token, group <= 16) uses MT = 1 and all 8 heads of a page per CTA;
+// multi-token queries (append + decode) trade heads per CTA for row tiles so that K/V still cross HBM once.
+template <typename T, int D, int MT>
 int launch_hk(const SplitKVParams& p, const DecodeDev& dev, cudaStream_t stream) {
     const int64_t hkv = p.hkv;
-    if (hkv % 8 == 0) return launch_inst<T, D, 8>(p, dev, stream);
-    if (hkv % 4 == 0) return launch_inst<T, D, 4>(p, dev, stream);
-    if (hkv % 2 == 0) return launch_inst<T, D, 2>(p, dev, stream);
-    return launch_inst<T, D, 1>(p, dev, stream);
+    constexpr int kMaxHK = 8 / MT;
+    if constexpr (kMaxHK >= 8) {
+        if (hkv % 8 == 0) return launch_inst<T, D, 8, MT>(p, dev, stream);
+    }
+    if constexpr (kMaxHK >= 4) {
+        if (hkv % 4 == 0) return launch_inst<T, D, 4, MT>(p, dev, stream);
+    }
+    if constexpr (kMaxHK >= 2) {
+        if (hkv % 2 == 0) return launch_inst<T, D, 2, MT>(p, dev, stream);
+    }
+    return launch_inst<T, D, 1, MT>(p, dev, stream);
+}
+
+template <typename T, int D>
+int launch_mt(const SplitKVParams& p, const DecodeDev& dev, cudaStream_t stream) {
+    const int64_t row_tiles = (p.max_seqlen_q * (p.hq / p.hkv) + 15) / 16;
+    if (row_tiles <= 1) return launch_hk<T, D, 1>(p, dev, stream);
+    if (row_tiles <= 2) return launch_hk<T, D, 2>(p, dev, stream);
+    return launch_hk<T, D, 4>(p, dev, stream);
 }
 
 }  // namespace
@@ -556,8 +590,8 @@ int launch_splitkv_decode(const SplitKVParams& p, cudaStream_t stream) {
     dev.stages = 0;
     dev.scale_log2 = p.scale * 1.4426950408889634f;
     if (p.dtype == FLASHCK_DTYPE_BFLOAT16)
-        return p.d == 128 ? launch_hk<__nv_bfloat16, 128>(p, dev, stream) : launch_hk<__nv_bfloat16, 64>(p, dev, stream);
-    return p.d == 128 ? launch_hk<__half, 128>(p, dev, stream) : launch_hk<__half, 64>(p, dev, stream);
+        return p.d == 128 ? launch_mt<__nv_bfloat16, 128>(p, dev, stream) : launch_mt<__nv_bfloat16, 64>(p, dev, stream);
+    return p.d == 128 ? launch_mt<__half, 128>(p, dev, stream) : launch_mt<__half, 64>(p, dev, stream);
 }
 
 }  // namespace fck

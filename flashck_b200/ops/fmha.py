@@ -28,6 +28,7 @@ __all__ = [
     "fmha_fwd_paged_kv_prefill",
     "fmha_fwd_splitkv",
     "fmha_fwd_splitkv_combine",
+    "fmha_fwd_splitkv_combine_strided",
     "fmha_fwd_append_kv",
     "splitkv_workspace",
     "default_num_splits",
@@ -264,12 +265,18 @@ def splitkv_workspace(q: torch.Tensor, dv: int, num_splits: int, cu_seqlens_q: O
     return lse_acc, o_acc
 
 
+_OUT_CODES = {torch.float16: 3, torch.bfloat16: 4, torch.float32: 7}
+
+
 def fmha_fwd_splitkv_combine(lse_acc: torch.Tensor, o_acc: torch.Tensor, dtype: torch.dtype, *,
-                             varlen: bool = False, return_lse: bool = False, out: Optional[torch.Tensor] = None):
+                             varlen: bool = False, return_lse: bool = False, out: Optional[torch.Tensor] = None,
+                             lse_out: Optional[torch.Tensor] = None):
     """LSE-weighted merge of split partials (C symbol ``FmhaFwdSplitKVCombine``).
 
     ``lse_acc [bs, hq, S, rows]``, ``o_acc [bs, hq, S, rows, dv]`` fp32 -> o ``[bs, rows, hq, dv]``
-    (``[rows, hq, dv]`` when ``varlen``) in ``dtype`` and LSE ``[bs, hq, rows]`` (``[hq, rows]``)."""
+    (``[rows, hq, dv]`` when ``varlen``) in ``dtype`` and LSE ``[bs, hq, rows]`` (``[hq, rows]``).
+    ``dtype=torch.float32`` keeps the merged partial in fp32 (what one rank contributes when the KV sequence is
+    sharded over GPUs); ``out`` / ``lse_out`` receive the results in place."""
     _check_cuda("lse_acc", lse_acc, torch.float32)
     _check_cuda("o_acc", o_acc, torch.float32)
     if o_acc.dim() != 5 or lse_acc.shape != o_acc.shape[:4]:
@@ -277,20 +284,52 @@ def fmha_fwd_splitkv_combine(lse_acc: torch.Tensor, o_acc: torch.Tensor, dtype: 
     bs, hq, S, rows, dv = o_acc.shape
     if varlen and bs != 1:
         raise ValueError("varlen workspaces have a single batch row")
-    code = _lib.FLOAT16 if dtype == torch.float16 else _lib.BFLOAT16 if dtype == torch.bfloat16 else None
+    code = _OUT_CODES.get(dtype)
     if code is None:
-        raise TypeError(f"output dtype must be float16 or bfloat16, got {dtype}")
+        raise TypeError(f"output dtype must be float16, bfloat16 or float32, got {dtype}")
     o = out if out is not None else torch.empty((bs, rows, hq, dv), dtype=dtype, device=o_acc.device)
-    lse = torch.empty((bs, hq, rows), dtype=torch.float32, device=o_acc.device) if return_lse else None
-    # group mode is signalled by a non-null seqstart pointer; its contents are not needed by the combine
-    marker = torch.zeros(1, dtype=torch.int64, device=o_acc.device) if varlen else None
+    _check_cuda("out", o, dtype)
+    lse = lse_out if lse_out is not None else (
+        torch.empty((bs, hq, rows), dtype=torch.float32, device=o_acc.device) if return_lse else None)
+    _check_cuda("lse_out", lse, torch.float32)
     with torch.cuda.device(o_acc.device):
-        rc = _lib.lib().FmhaFwdSplitKVCombine(_ptr(lse_acc), _ptr(o_acc), _ptr(o), _ptr(marker), bs, rows, hq, dv,
-                                              rows, S, _stream(), _ptr(lse), code)
+        if dtype == torch.float32:
+            ls = (ctypes.c_int64 * 4)(hq * S * rows, S * rows, rows, 1)
+            os_ = (ctypes.c_int64 * 4)(hq * S * rows * dv, S * rows * dv, rows * dv, dv)
+            rc = _lib.lib().FmhaFwdSplitKVCombineStrided(_ptr(lse_acc), _ptr(o_acc), _ptr(o), _ptr(lse), bs, rows, hq, dv,
+                                                         S, ls, os_, code, _stream())
+        else:
+            # group mode is signalled by a non-null seqstart pointer; its contents are not needed by the combine
+            marker = torch.zeros(1, dtype=torch.int64, device=o_acc.device) if varlen else None
+            rc = _lib.lib().FmhaFwdSplitKVCombine(_ptr(lse_acc), _ptr(o_acc), _ptr(o), _ptr(marker), bs, rows, hq, dv,
+                                                  rows, S, _stream(), _ptr(lse), code)
     _lib.check(rc, "FmhaFwdSplitKVCombine")
     if varlen and out is None:
         o = o[0]
         lse = lse[0] if lse is not None else None
+    return (o, lse) if (return_lse or lse_out is not None) else o
+
+
+def fmha_fwd_splitkv_combine_strided(buf: torch.Tensor, batch: int, rows: int, hq: int, dv: int, num_splits: int, *,
+                                     lse_offset: int, lse_strides: Sequence[int], o_strides: Sequence[int],
+                                     dtype: torch.dtype, return_lse: bool = False):
+    """Merge of partials that sit in one fp32 buffer with arbitrary strides (C symbol
+    ``FmhaFwdSplitKVCombineStrided``): the O partials start at element 0 of ``buf``, the LSE partials at element
+    ``lse_offset``; strides are in elements for (batch, head, split, row).  Returns o ``[batch, rows, hq, dv]`` in
+    ``dtype`` (and LSE ``[batch, hq, rows]``)."""
+    _check_cuda("buf", buf, torch.float32)
+    code = _OUT_CODES.get(dtype)
+    if code is None:
+        raise TypeError(f"output dtype must be float16, bfloat16 or float32, got {dtype}")
+    o = torch.empty((batch, rows, hq, dv), dtype=dtype, device=buf.device)
+    lse = torch.empty((batch, hq, rows), dtype=torch.float32, device=buf.device) if return_lse else None
+    ls = (ctypes.c_int64 * 4)(*[int(x) for x in lse_strides])
+    os_ = (ctypes.c_int64 * 4)(*[int(x) for x in o_strides])
+    with torch.cuda.device(buf.device):
+        rc = _lib.lib().FmhaFwdSplitKVCombineStrided(ctypes.c_void_p(buf.data_ptr() + 4 * int(lse_offset)), _ptr(buf),
+                                                     _ptr(o), _ptr(lse), batch, rows, hq, dv, num_splits, ls, os_, code,
+                                                     _stream())
+    _lib.check(rc, "FmhaFwdSplitKVCombineStrided")
     return (o, lse) if return_lse else o
 
 

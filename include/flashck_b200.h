@@ -44,6 +44,7 @@ extern "C" {
 
 #define FLASHCK_DTYPE_FLOAT16 3
 #define FLASHCK_DTYPE_BFLOAT16 4
+#define FLASHCK_DTYPE_FLOAT32 7 /* only as the output type of FmhaFwdSplitKVCombineStrided */
 
 /* status codes */
 #define FLASHCK_OK 0
@@ -134,6 +135,21 @@ FLASHCK_API int FmhaFwdSplitKVCombine(void* lse_acc_buf_ptr, void* o_acc_buf_ptr
 FLASHCK_API int FmhaSplitKVCombine(void* lse_acc_buf_ptr, void* o_acc_buf_ptr, void* o_buf_ptr, int64_t* q_seq_start_ptr,
                        int64_t batch, int64_t q_seq_len, int64_t q_num_heads, int64_t v_head_dim,
                        int64_t q_max_seq_len, int64_t num_splits, void* stream, void* lse_ptr, int dtype);
+
+/*
+ * FmhaFwdSplitKVCombineStrided -- the same LSE-weighted merge with explicit strides and an optional fp32 result.
+ * The reference is single-GPU and has no counterpart; its combine kernel takes exactly these strides as kernel
+ * arguments (MakeKargs, fmha_fwd_split_kv_combine_jinja.h:176-215), the C symbol just fixes them.  Used when the
+ * KV sequence of one request is sharded over several GPUs: every rank merges its local splits into fp32
+ * (out_dtype = 7), the ranks all-gather those partials, and one more merge over the gathered [rank][...] buffer
+ * (num_splits = world size) gives O.  lse_strides / o_acc_strides: 4 int64 each, in elements, for
+ * (batch, head, split, row); hdim is contiguous and o_acc strides must be multiples of 4.
+ * Output o is [batch, rows, hq, dv] in out_dtype, lse (optional) fp32 [batch, hq, rows].
+ */
+FLASHCK_API int FmhaFwdSplitKVCombineStrided(void* lse_acc_buf_ptr, void* o_acc_buf_ptr, void* o_buf_ptr, void* lse_ptr,
+                                             int64_t batch, int64_t rows, int64_t q_num_heads, int64_t v_head_dim,
+                                             int64_t num_splits, const int64_t* lse_strides,
+                                             const int64_t* o_acc_strides, int out_dtype, void* stream);
 
 /*
  * FmhaFwdAppendKV -- rotary embedding of Q and the new keys, and the K/V cache write.

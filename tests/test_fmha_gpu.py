@@ -240,6 +240,51 @@ def test_splitkv_config3_small():
     assert_lse_close(lse, lse_ref)
 
 
+def test_combine_fp32_output_and_strided_form():
+    torch.manual_seed(1)
+    bs, hq, S, rows, dv = 2, 4, 3, 2, 128
+    lse_acc = torch.randn(bs, hq, S, rows) * 2
+    lse_acc[1, 2, 1] = float("-inf")
+    o_acc = torch.randn(bs, hq, S, rows, dv)
+    o_ref, lse_ref = oracle.splitkv_combine(lse_acc, o_acc, torch.bfloat16)
+    o32, lse = ops.fmha_fwd_splitkv_combine(_cu(lse_acc), _cu(o_acc), torch.float32, return_lse=True)
+    assert o32.dtype == torch.float32
+    assert_o_close(o32, o_ref)
+    assert_lse_close(lse, lse_ref)
+
+
+@pytest.mark.parametrize("world", [1, 2, 4, 8])
+def test_sequence_sharded_decode_ranks_emulated_on_one_gpu(world):
+    # BASELINE config 5 geometry (64/8 heads, page 64) at reduced context; the ranks run one after the other on this
+    # GPU and their fp32 partials are stacked where the all-gather would put them
+    from flashck_b200 import dist as fdist
+    dtype = torch.bfloat16
+    lens = [5000, 130, 64, 0]
+    hq, hkv, d, page = 64, 8, 128, 64
+    cache = make_paged_cache(lens, hkv, d, d, page, dtype, seed=14)
+    q = normal_tensor((len(lens), 1, hq, d), dtype, 111)
+    o_ref, lse_ref = oracle.fmha_fwd(q, cache.k, cache.v, seqlen_k=cache.seqlen_k, block_table=cache.block_table)
+    qd, kd, vd = _cu(q), _cu(cache.k), _cu(cache.v)
+    slots = []
+
+    def capture(slot, group):
+        slots.append(slot.clone())
+        return slot.view(1, -1)
+
+    for rank in range(world):
+        table, local = fdist.shard_pages(lens, cache.block_table, page, rank, world)
+        fdist.sequence_sharded_decode(qd, kd, vd, _cu(table), _cu(local), gather=capture)
+    stacked = torch.stack(slots)
+
+    def replay(slot, group):
+        return stacked
+
+    table, local = fdist.shard_pages(lens, cache.block_table, page, 0, world)
+    o, lse = fdist.sequence_sharded_decode(qd, kd, vd, _cu(table), _cu(local), gather=replay, return_lse=True)
+    assert_o_close(o, o_ref)
+    assert_lse_close(lse, lse_ref)
+
+
 # ------------------------------------------------------------------------------------------------
 # append-KV
 # ------------------------------------------------------------------------------------------------
