@@ -49,3 +49,15 @@ def test_version_and_argument_errors_without_gpu():
     _lib.set_instance_param(2, "stages", 3)
     assert _lib.get_instance_param(2, "stages") == 3
     _lib.set_instance_param(2, "stages", 0)
+
+
+def test_cpp_operator_api_compiles_links_and_throws(tmp_path):
+    import shutil
+    import subprocess
+    gxx = "/usr/bin/g++" if os.path.exists("/usr/bin/g++") else shutil.which("g++")
+    exe = str(tmp_path / "cpp_api_check")
+    libdir = os.path.dirname(_lib.LIB_PATH)
+    subprocess.run([gxx, "-std=c++17", "-I", os.path.join(ROOT, "include"), os.path.join(ROOT, "tests", "cpp_api_check.cpp"),
+                    "-L", libdir, "-lflashck_b200", f"-Wl,-rpath,{libdir}", "-o", exe], check=True, capture_output=True)
+    out = subprocess.run([exe], capture_output=True, text=True)
+    assert out.returncode == 0 and "OK" in out.stdout, out.stdout + out.stderr
