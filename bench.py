@@ -34,6 +34,8 @@ sys.path.insert(0, ROOT)
 from flashck_b200.utils.inputs import iota_shuffle, to_seqstarts, uniform_seqlens  # noqa: E402
 
 HQ, HKV, D = 32, 8, 128
+# threads of the CPU baseline: all host cores, set explicitly (torchrun exports OMP_NUM_THREADS=1)
+HOST_THREADS = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
 
 
 def load_peaks():
@@ -202,9 +204,9 @@ def cpu_prefill_sample(w, budget_flops=1.5e12):
     v = torch.cat([w["v"][s] for s in parts]).cpu()
     cu_s = to_seqstarts([lens[b] for b in chosen])
     t0 = time.perf_counter()
-    oracle.fmha_fwd(q, k, v, seqstart_q=cu_s, seqstart_k=cu_s, mask_type=1, window=(-1, 0))
+    oracle.fmha_fwd(q, k, v, seqstart_q=cu_s, seqstart_k=cu_s, mask_type=1, window=(-1, 0), nthreads=HOST_THREADS)
     dt = time.perf_counter() - t0
-    return {"value": fl / dt / 1e12, "unit": "TFLOP/s", "cores": oracle.num_threads(), "kind": "port",
+    return {"value": fl / dt / 1e12, "unit": "TFLOP/s", "cores": HOST_THREADS, "kind": "port",
             "sample": f"{len(chosen)} shortest of {len(lens)} sequences ({sum(lens[b] for b in chosen)} tokens, "
                       f"{fl:.3g} FLOP) in {dt:.2f} s", "seconds": dt}
 
@@ -226,10 +228,10 @@ def cpu_decode_sample(w, nseq=48):
     q = w["q"][:nseq].cpu()
     sl = torch.tensor(lens, dtype=torch.int32)
     t0 = time.perf_counter()
-    oracle.fmha_fwd(q, kpool, vpool, seqlen_k=sl, block_table=new_table)
+    oracle.fmha_fwd(q, kpool, vpool, seqlen_k=sl, block_table=new_table, nthreads=HOST_THREADS)
     dt = time.perf_counter() - t0
     nbytes = sum(lens) * w["hkv"] * 2 * D * 2
-    return {"value": nbytes / dt / 1e9, "unit": "GB/s", "cores": oracle.num_threads(), "kind": "port",
+    return {"value": nbytes / dt / 1e9, "unit": "GB/s", "cores": HOST_THREADS, "kind": "port",
             "sample": f"first {nseq} of {len(w['lens'])} sequences ({sum(lens)} tokens) in {dt:.2f} s", "seconds": dt}
 
 
@@ -259,7 +261,7 @@ def run_reference(args, rank):
         "config": {"workload": "varlen causal batch prefill (BASELINE config 2): batch 16, 32/8 heads, hdim 128, "
                                "L~U[512,4096] seed 1234", "note": "CPU statement of the path (oracle port); the "
                                "reference's own kernels need ROCm + ck_tile"},
-        "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": oracle.num_threads(), "kind": "port",
+        "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": HOST_THREADS, "kind": "port",
                          "sample": samples[-1]["sample"]},
         "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
