@@ -369,7 +369,10 @@ def main():
                    "flop_count": "causal-effective 4*d*hq*sum L(L+1)/2",
                    "l2": "inputs (q,k,v,o > 600 MB) larger than the 126 MB L2", "parallelism": f"dp{world}"},
         "roofline": {"bound": "tensor", "achieved": kernel_tflops, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
-                     "frac": kernel_tflops / peaks["bf16_tflops"], "traffic": None,
+                     "frac": kernel_tflops / peaks["bf16_tflops"],
+                     # DRAM bytes per launch from the ncu capture summarised in profiles/fmha_fwd_sm100_prefill_bf16.md
+                     "traffic": None if args.small else 1.352e9,
+                     "algorithmic_bytes": 2.0 * w["total"] * (2 * HQ * D + 2 * HKV * D) + 4.0 * w["total"] * HQ,
                      "peak_source": peaks["source"] + " (burst bf16 GEMM)"},
         "e2e": {"value": e2e_val, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
         "gpu_launches": steps,
@@ -422,7 +425,9 @@ def main():
                        "tokens_per_gpu": sum(wd["lens"]), "algorithmic_bytes_per_gpu_step": wd["bytes"],
                        "num_splits": S, "l2": "K/V pool (GBs) larger than L2"},
             "roofline": {"bound": "hbm", "achieved": gbs_gpu, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                         "frac": gbs_gpu / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"],
+                         "frac": gbs_gpu / peaks["hbm_gbs"],
+                         # DRAM bytes of the split-KV launch from the ncu capture in profiles/fmha_fwd_sm100_prefill_bf16.md
+                         "traffic": None if args.small else 4.247e9, "peak_source": peaks["source"],
                          "note": "split-KV kernel + combine kernel timed together"},
             "e2e": {"value": tot_bytes * dsteps / (ms_de * 1e-3) / 1e9, "unit": "GB/s",
                     "h2d_bytes_per_step": hq2.numel() * 2 + hs.numel() * 4 + ht.numel() * 4,
