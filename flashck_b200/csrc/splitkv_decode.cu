@@ -24,6 +24,7 @@
 
 #include <atomic>
 #include <string.h>
+#include <type_traits>
 
 namespace fck {
 
@@ -334,34 +335,57 @@ splitkv_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
             for (int n = 0; n < D / 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
             float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
 
-            for (int t = ta; t < tb; ++t, ++it) {
-                const int s = it % stages;
-                const uint32_t ph = (it / stages) & 1u;
-                const uint32_t kbase = smem_u32(tiles + (size_t)s * 2 * TILE_BYTES);
-                const uint32_t vbase = kbase + TILE_BYTES;
-                const int tok0 = (t0 + t) * kTok;
-
-                if (!mbar_wait_bounded(&full_k[s], ph, abort_flag, p.status, 2)) return;
-                // ---- S = Q K^T ----
-                float sacc[2][4];
+            // tiles whose keys all lie at or before `mask_from` and inside the sequence need no masking
+            int mask_from = len;  // first key index that some row may not see
+            if (p.mask_type != 0) {
+                const int shift = (p.mask_type == 2) ? len - sq : 0;
+                if (p.wr >= 0) mask_from = min(mask_from, shift + p.wr + 1);
+                if (p.wl >= 0) mask_from = 0;
+            }
+            bool failed = false;
+            int tcur = ta;  // next tile of the segment
+            // One or two 16-token tiles per step.  Two tiles share the row maxima, the O rescale and the shuffles, and
+            // give the dependent mma chains twice the independent work; the steps of a segment are taken in pairs
+            // while at least two tiles remain.
+            auto step = [&](auto nt_tag) {
+                constexpr int NT = decltype(nt_tag)::value;
+                uint32_t kbase[NT], vbase[NT], ph[NT];
+                int st[NT];
 #pragma unroll
-                for (int n = 0; n < 2; ++n) sacc[n][0] = sacc[n][1] = sacc[n][2] = sacc[n][3] = 0.f;
+                for (int u = 0; u < NT; ++u) {
+                    st[u] = (it + u) % stages;
+                    ph[u] = ((it + u) / stages) & 1u;
+                    kbase[u] = smem_u32(tiles + (size_t)st[u] * 2 * TILE_BYTES);
+                    vbase[u] = kbase[u] + TILE_BYTES;
+                }
+                const int tok0 = (t0 + tcur) * kTok;
+                // ---- S = Q K^T ----
+                float sacc[2 * NT][4];
+#pragma unroll
+                for (int n = 0; n < 2 * NT; ++n) sacc[n][0] = sacc[n][1] = sacc[n][2] = sacc[n][3] = 0.f;
+#pragma unroll
+                for (int u = 0; u < NT; ++u) {
+                    if (!mbar_wait_bounded(&full_k[st[u]], ph[u], abort_flag, p.status, 2)) { failed = true; return; }
+                }
                 {
                     const int key = (lm >> 1) * 8 + lr;  // token row this lane addresses
 #pragma unroll
                     for (int ks = 0; ks < D / 16; ++ks) {
                         const int dh = ks / 4;
                         const int c = 2 * (ks % 4) + (lm & 1);
-                        uint32_t bfr[4];
-                        ldmatrix_x4(bfr, kbase + (dh * HK + hw) * HEAD_BYTES + key * 128 + ((c ^ (key & 7)) << 4));
-                        mma_16816<T>(sacc[0], qa[ks], bfr[0], bfr[1]);
-                        mma_16816<T>(sacc[1], qa[ks], bfr[2], bfr[3]);
+#pragma unroll
+                        for (int u = 0; u < NT; ++u) {
+                            uint32_t bfr[4];
+                            ldmatrix_x4(bfr, kbase[u] + (dh * HK + hw) * HEAD_BYTES + key * 128 + ((c ^ (key & 7)) << 4));
+                            mma_16816<T>(sacc[2 * u], qa[ks], bfr[0], bfr[1]);
+                            mma_16816<T>(sacc[2 * u + 1], qa[ks], bfr[2], bfr[3]);
+                        }
                     }
                 }
                 // ---- scale, mask, online softmax (base 2) ----
-                const bool need_mask = (tok0 + kTok > len) || (p.mask_type != 0);
+                const bool need_mask = tok0 + NT * kTok > mask_from;
 #pragma unroll
-                for (int n = 0; n < 2; ++n) {
+                for (int n = 0; n < 2 * NT; ++n) {
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
                         float x = sacc[n][e] * p.scale_log2;
@@ -373,8 +397,12 @@ splitkv_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
                         sacc[n][e] = x;
                     }
                 }
-                float mx0 = fmaxf(fmaxf(sacc[0][0], sacc[0][1]), fmaxf(sacc[1][0], sacc[1][1]));
-                float mx1 = fmaxf(fmaxf(sacc[0][2], sacc[0][3]), fmaxf(sacc[1][2], sacc[1][3]));
+                float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+                for (int n = 0; n < 2 * NT; ++n) {
+                    mx0 = fmaxf(mx0, fmaxf(sacc[n][0], sacc[n][1]));
+                    mx1 = fmaxf(mx1, fmaxf(sacc[n][2], sacc[n][3]));
+                }
                 mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
                 mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
                 mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
@@ -386,7 +414,7 @@ splitkv_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
                 m1 = mn1;
                 float ps0 = 0.f, ps1 = 0.f;
 #pragma unroll
-                for (int n = 0; n < 2; ++n) {
+                for (int n = 0; n < 2 * NT; ++n) {
                     sacc[n][0] = fast_exp2(sacc[n][0] - ms0);
                     sacc[n][1] = fast_exp2(sacc[n][1] - ms0);
                     sacc[n][2] = fast_exp2(sacc[n][2] - ms1);
@@ -405,15 +433,15 @@ splitkv_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
                         o[n][3] *= a1;
                     }
                 }
-                uint32_t pa[4];
-                pa[0] = Elem<T>::pack2(sacc[0][0], sacc[0][1]);
-                pa[1] = Elem<T>::pack2(sacc[0][2], sacc[0][3]);
-                pa[2] = Elem<T>::pack2(sacc[1][0], sacc[1][1]);
-                pa[3] = Elem<T>::pack2(sacc[1][2], sacc[1][3]);
-
                 // ---- O += P V ----
-                if (!mbar_wait_bounded(&full_v[s], ph, abort_flag, p.status, 4)) return;
-                {
+#pragma unroll
+                for (int u = 0; u < NT; ++u) {
+                    uint32_t pa[4];
+                    pa[0] = Elem<T>::pack2(sacc[2 * u][0], sacc[2 * u][1]);
+                    pa[1] = Elem<T>::pack2(sacc[2 * u][2], sacc[2 * u][3]);
+                    pa[2] = Elem<T>::pack2(sacc[2 * u + 1][0], sacc[2 * u + 1][1]);
+                    pa[3] = Elem<T>::pack2(sacc[2 * u + 1][2], sacc[2 * u + 1][3]);
+                    if (!mbar_wait_bounded(&full_v[st[u]], ph[u], abort_flag, p.status, 4)) { failed = true; return; }
                     const int key = (lm & 1) * 8 + lr;
 #pragma unroll
                     for (int j = 0; j < D / 16; ++j) {
@@ -421,14 +449,21 @@ splitkv_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
                         const int dh = g / 8, c = g % 8;
                         uint32_t bfr[4];
                         ldmatrix_x4_trans(bfr,
-                                          vbase + (dh * HK + hw) * HEAD_BYTES + key * 128 + ((c ^ (key & 7)) << 4));
+                                          vbase[u] + (dh * HK + hw) * HEAD_BYTES + key * 128 + ((c ^ (key & 7)) << 4));
                         mma_16816<T>(o[2 * j], pa, bfr[0], bfr[1]);
                         mma_16816<T>(o[2 * j + 1], pa, bfr[2], bfr[3]);
                     }
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&empty[st[u]]);
                 }
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&empty[s]);
+                it += NT;
+                tcur += NT;
+            };
+            while (tcur < tb && !failed) {
+                if (tb - tcur >= 2) step(std::integral_constant<int, 2>{});
+                else step(std::integral_constant<int, 1>{});
             }
+            if (failed) return;
 
             // ---- epilogue: normalise within the split, store fp32 partials ----
             l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
