@@ -125,6 +125,15 @@ __device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* m
         : "memory");
 }
 
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, const void* smem_src, int c0, int c1, int c2) {
+    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2,%3,%4}], [%1];\n" ::"l"(map),
+                 "r"(smem_u32(smem_src)), "r"(c0), "r"(c1), "r"(c2)
+                 : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;\n" ::: "memory"); }
+__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;\n" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
+
 // Instruction descriptor of tcgen05.mma kind::f16: D = f32 (bits 4-5 = 1); A/B format at bits 7-9 / 10-12
 // (0 = f16, 1 = bf16); bit 16: B is MN-major; N >> 3 at bits 17-22; M >> 4 at bits 24-28.
 template <typename T> struct UmmaFmt;
@@ -165,8 +174,9 @@ __device__ __forceinline__ float2 exp2_poly2(float2 x) {
     return r;
 }
 
-constexpr int kMaxBatch = 1024;   // sequences the on-chip schedule can hold
-constexpr int kMaxLevels = 1024;  // row blocks per sequence the on-chip schedule can hold
+constexpr int kMaxBatch = 256;    // sequences the on-chip schedule can hold (larger batches use the general instance)
+constexpr int kMaxLevels = 512;   // row blocks per sequence the on-chip schedule can hold
+constexpr int STAGE_BYTES = 32 * 32 * 2;  // per softmax warp: 32 rows x 32 columns of O on their way to a TMA store
 constexpr int kMaxRounds = 96;    // work items per CTA decoded up front (later ones are decoded on the fly)
 
 // One work item = two 128-row Q tiles that share their K/V tiles.  With an even GQA ratio the tiles are the same
@@ -275,7 +285,8 @@ __device__ __forceinline__ void get_item(const Ctrl* ctrl, const Sm100Dev& p, in
 template <typename T, int NPOLY8>
 __global__ void __launch_bounds__(NTHREADS, 1)
 fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                      const __grid_constant__ CUtensorMap map_v, const Sm100Dev p) {
+                      const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_o,
+                      const Sm100Dev p) {
     extern __shared__ uint8_t smem_raw[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -285,7 +296,8 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     uint8_t* sQ = base;                                  // 2 tiles
     uint8_t* sK = base + 2 * TILE_BYTES;                 // KV_SLOTS tiles
     uint8_t* sV = sK + KV_SLOTS * TILE_BYTES;            // KV_SLOTS tiles
-    Ctrl* ctrl = reinterpret_cast<Ctrl*>(sV + KV_SLOTS * TILE_BYTES);
+    uint8_t* sStage = sV + KV_SLOTS * TILE_BYTES;        // 8 x STAGE_BYTES: O chunks of the softmax warps
+    Ctrl* ctrl = reinterpret_cast<Ctrl*>(sStage + 8 * STAGE_BYTES);
     volatile int* abort_flag = &ctrl->abort_flag;
 
     if (threadIdx.x == 0) {
@@ -599,6 +611,11 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
             }
             if (tile_first_row < sq) {
                 const float inv = l > 0.f ? 1.f / l : 0.f;
+                // Whole tiles leave through shared memory and TMA stores (32 rows x 32 columns per warp and store), which
+                // keeps the load/store unit free for the other warps; a tile that reaches past the end of its sequence
+                // is written row by row, because its surplus rows belong to the next sequence of the packed buffer.
+                const bool whole_tile = tile_first_row + BM <= sq;
+                uint8_t* stage = sStage + warp * STAGE_BYTES;
                 T* orow = (T*)p.o + ((int64_t)(it.q0 + row) * p.hq + head) * HD;
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
@@ -610,16 +627,29 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
 #pragma unroll
                         for (int j = 0; j < 32; ++j) t[j] = 0u;
                     }
-                    if (row_ok) {
+                    uint4 pk[4];
 #pragma unroll
-                        for (int v4 = 0; v4 < 4; ++v4) {
-                            uint4 pk;
-                            pk.x = Elem<T>::pack2(__uint_as_float(t[v4 * 8 + 0]) * inv, __uint_as_float(t[v4 * 8 + 1]) * inv);
-                            pk.y = Elem<T>::pack2(__uint_as_float(t[v4 * 8 + 2]) * inv, __uint_as_float(t[v4 * 8 + 3]) * inv);
-                            pk.z = Elem<T>::pack2(__uint_as_float(t[v4 * 8 + 4]) * inv, __uint_as_float(t[v4 * 8 + 5]) * inv);
-                            pk.w = Elem<T>::pack2(__uint_as_float(t[v4 * 8 + 6]) * inv, __uint_as_float(t[v4 * 8 + 7]) * inv);
-                            *reinterpret_cast<uint4*>(orow + c * 32 + v4 * 8) = pk;
+                    for (int v4 = 0; v4 < 4; ++v4) {
+                        pk[v4].x = Elem<T>::pack2(__uint_as_float(t[v4 * 8 + 0]) * inv, __uint_as_float(t[v4 * 8 + 1]) * inv);
+                        pk[v4].y = Elem<T>::pack2(__uint_as_float(t[v4 * 8 + 2]) * inv, __uint_as_float(t[v4 * 8 + 3]) * inv);
+                        pk[v4].z = Elem<T>::pack2(__uint_as_float(t[v4 * 8 + 4]) * inv, __uint_as_float(t[v4 * 8 + 5]) * inv);
+                        pk[v4].w = Elem<T>::pack2(__uint_as_float(t[v4 * 8 + 6]) * inv, __uint_as_float(t[v4 * 8 + 7]) * inv);
+                    }
+                    if (whole_tile) {
+                        if (lane == 0) tma_store_wait_read();  // the previous store has read the staging buffer
+                        __syncwarp();
+#pragma unroll
+                        for (int v4 = 0; v4 < 4; ++v4)  // row `lane` of the chunk: 64 bytes in the 64-byte swizzle of the map
+                            *reinterpret_cast<uint4*>(stage + lane * 64 + ((v4 ^ (lane >> 1)) & 3) * 16) = pk[v4];
+                        fence_proxy_async_smem();
+                        __syncwarp();
+                        if (lane == 0) {
+                            tma_store_3d(&map_o, stage, c * 32, head, it.q0 + tile_first_row + (warp & 3) * 32);
+                            tma_store_commit();
                         }
+                    } else if (row_ok) {
+#pragma unroll
+                        for (int v4 = 0; v4 < 4; ++v4) *reinterpret_cast<uint4*>(orow + c * 32 + v4 * 8) = pk[v4];
                     }
                 }
                 if (p.lse && row_ok) {
@@ -632,6 +662,7 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         }
     }
 
+    if (warp < 8 && lane == 0) tma_store_wait_read();  // shared memory stays valid until the last O store has read it
     tc_fence_before();
     __syncthreads();
     if (warp == 8) {
@@ -657,17 +688,35 @@ int make_map_3d(CUtensorMap* map, const void* base, int dtype, int64_t rows, int
     return FLASHCK_OK;
 }
 
+// O [rows, heads, 128] as 32-row x 32-column boxes (64-byte rows, 64-byte swizzle) for the epilogue's TMA stores.
+int make_map_o(CUtensorMap* map, const void* base, int dtype, int64_t rows, int64_t heads) {
+    PFN_encodeTiled enc = get_encode_tiled();
+    FCK_REQUIRE(enc != nullptr, FLASHCK_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    const cuuint64_t dims[3] = {(cuuint64_t)HD, (cuuint64_t)heads, (cuuint64_t)(rows > 0 ? rows : 1)};
+    const cuuint64_t strides[2] = {(cuuint64_t)(HD * 2), (cuuint64_t)(heads * HD * 2)};
+    const cuuint32_t box[3] = {32, 1, 32};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    const CUtensorMapDataType dt =
+        dtype == FLASHCK_DTYPE_BFLOAT16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    const CUresult r = enc(map, dt, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                           CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    FCK_REQUIRE(r == CUDA_SUCCESS, FLASHCK_ERR_CUDA, "cuTensorMapEncodeTiled (O) failed (%d) rows=%lld heads=%lld", (int)r,
+                (long long)rows, (long long)heads);
+    return FLASHCK_OK;
+}
+
 template <typename T, int NPOLY8>
 int launch_t(const FwdParams& p, const Sm100Dev& dev, cudaStream_t stream) {
     const int64_t rows_q = p.seqstart_q ? p.total_q : p.batch * p.seqlen_q;
     const int64_t rows_k = p.seqstart_k ? p.seqlen_k : p.batch * p.seqlen_k;  // group mode: packed total
-    CUtensorMap mq, mk, mv;
+    CUtensorMap mq, mk, mv, mo;
     int rc;
     if ((rc = make_map_3d(&mq, p.q, p.dtype, rows_q, p.hq))) return rc;
     if ((rc = make_map_3d(&mk, p.k, p.dtype, rows_k, p.hkv))) return rc;
     if ((rc = make_map_3d(&mv, p.v, p.dtype, rows_k, p.hkv))) return rc;
+    if ((rc = make_map_o(&mo, p.o, p.dtype, rows_q, p.hq))) return rc;
     auto kern = fmha_fwd_sm100_kernel<T, NPOLY8>;
-    const size_t smem = 1024 + (size_t)(2 + 2 * KV_SLOTS) * TILE_BYTES + sizeof(Ctrl);
+    const size_t smem = 1024 + (size_t)(2 + 2 * KV_SLOTS) * TILE_BYTES + 8 * STAGE_BYTES + sizeof(Ctrl);
     static thread_local int configured_device = -1;
     int devid = 0;
     FCK_CUDA(cudaGetDevice(&devid));
@@ -677,7 +726,7 @@ int launch_t(const FwdParams& p, const Sm100Dev& dev, cudaStream_t stream) {
     }
     if (p.max_seqlen_q == 0 || p.batch == 0) return FLASHCK_OK;
     // persistent: one CTA per SM walks the device-side work list
-    kern<<<sm_count(), NTHREADS, smem, stream>>>(mq, mk, mv, dev);
+    kern<<<sm_count(), NTHREADS, smem, stream>>>(mq, mk, mv, mo, dev);
     FCK_CUDA(cudaGetLastError());
     return FLASHCK_OK;
 }
