@@ -114,6 +114,30 @@ def make_prefill(seed: int, device, batch=16, lo=512, hi=4096):
             "max_len": max(lens)}
 
 
+def make_paged_prefill(w, page: int, seed: int, device):
+    """The K/V of a packed prefill workload scattered into paged pools [pages, page, hkv, d] behind a shuffled block
+    table (a `next` row: prefill reading K/V through the page table, as in a serving loop)."""
+    lens = w["lens"]
+    pages = [-(-L // page) for L in lens]
+    perm = iota_shuffle(sum(pages), seed)
+    table = torch.zeros((len(lens), max(pages)), dtype=torch.int32)
+    slot = torch.empty(w["total"], dtype=torch.int64)
+    off = tok = 0
+    for b, (L, n) in enumerate(zip(lens, pages)):
+        table[b, :n] = perm[off:off + n]
+        j = torch.arange(L)
+        slot[tok:tok + L] = perm[off:off + n].to(torch.int64)[j // page] * page + j % page
+        off += n
+        tok += L
+    slot = slot.to(device)
+    kpool = torch.zeros(sum(pages) * page, HKV, D, device=device, dtype=torch.bfloat16)
+    vpool = torch.zeros_like(kpool)
+    kpool[slot] = w["k"]
+    vpool[slot] = w["v"]
+    return {"k": kpool.view(-1, page, HKV, D), "v": vpool.view(-1, page, HKV, D), "table": table.to(device),
+            "seqlen": torch.tensor(lens, dtype=torch.int32, device=device), "page": page}
+
+
 def make_decode(seed: int, device, batch=64, lo=1024, hi=32768, page=16, hq=HQ, hkv=HKV, lens=None):
     lens = lens or uniform_seqlens(batch, lo, hi, seed)
     batch = len(lens)
@@ -379,6 +403,27 @@ def main():
         "clocks": clocks,
     }
     extra = {}
+
+    # ------------------------------------------------------------------ prefill through the page table (next row)
+    if not args.no_decode:
+        wp = make_paged_prefill(w, 16, 99 + rank, device)
+
+        def paged_prefill_step():
+            return ops.fmha_fwd_paged_kv_prefill(w["q"], wp["k"], wp["v"], wp["table"], wp["seqlen"], cu_seqlens_q=w["cu"],
+                                                 max_seqlen_q=w["max_len"], causal=True, return_lse=True)
+
+        ms_p = max_over_ranks(time_steps(paged_prefill_step, steps, warmup, barrier))
+        p_tflops = w["flops"] * steps / (ms_p * 1e-3) / 1e12
+        extra["paged_prefill"] = {
+            "metric": "paged_kv_prefill_tflops", "value": total_flops * steps / (ms_p * 1e-3) / 1e12, "unit": "TFLOP/s",
+            "ms_per_step": ms_p / steps, "steps": steps,
+            "config": {"workload": "the headline prefill with K/V read through a block table: pools [pages, 16, 8, 128], "
+                                   "shuffled page ids, bottom-right causal (FmhaFwdPagedKVPrefill)", "page": 16},
+            "roofline": {"bound": "tensor", "achieved": p_tflops, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                         "frac": p_tflops / peaks["bf16_tflops"], "traffic": None, "peak_source": peaks["source"] + " (burst bf16 GEMM)"},
+            "gpu_launches": steps,
+        }
+        del wp
 
     # ------------------------------------------------------------------ decode (config 3)
     if not args.no_decode:

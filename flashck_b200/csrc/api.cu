@@ -167,9 +167,10 @@ int FmhaFwdBatchPrefill(void* q, void* k, void* v, void* bias, void* o, int64_t*
     p.batch = batch; p.hq = hq; p.hkv = hkv; p.d = d; p.dv = dv; p.page = paged_block_size;
     p.max_seqlen_q = q_max_seq_len > 0 ? q_max_seq_len : q_seq_len;
     p.total_q = q_seq_len;  // packed total, like shape_seqlen_q of the other group-mode calls
+    p.num_pages = num_total_pages;
     p.scale = resolve_scale(scale, d);
     p.mask_type = (int)mask_type; p.wl = window_left; p.wr = window_right; p.dtype = dtype;
-    return launch_fwd_generic(p, (cudaStream_t)stream);
+    return run_fwd(p, (cudaStream_t)stream);
 }
 
 int FmhaFwdPagedKVPrefill(void* q, void* k, void* v, void* bias, void* o, int64_t* q_seq_start, void* k_seq_len,
@@ -193,9 +194,10 @@ int FmhaFwdPagedKVPrefill(void* q, void* k, void* v, void* bias, void* o, int64_
     p.max_seqlen_q = q_seq_start ? (q_max_seq_len > 0 ? q_max_seq_len : q_seq_len) : q_seq_len;
     p.bt_stride = max_num_page_blocks / batch;  // fmha_fwd_split_kv_jinja.h:318
     p.page = paged_block_size;
+    p.num_pages = max_num_page_blocks;  // the pools hold max_num_page_blocks pages (fmha_fwd_split_kv_jinja.h:512-519)
     p.scale = resolve_scale(scale, d);
     p.mask_type = (int)mask_type; p.wl = window_left; p.wr = window_right; p.dtype = dtype;
-    return launch_fwd_generic(p, (cudaStream_t)stream);
+    return run_fwd(p, (cudaStream_t)stream);
 }
 
 int FmhaFwdSplitKV(void* q, void* k, void* v, void* bias, void* lse_acc, void* o_acc, int64_t* q_seq_start,

@@ -26,6 +26,7 @@
 // K/V tiles hidden by the causal mask are skipped; only diagonal and tail tiles pay for masking.
 // The GQA group's q heads run in neighbouring CTAs and share K/V through L2 (no cluster multicast).
 // Every mbarrier wait is bounded; on expiry the CTA records a code in the device status word and drains.
+#include <algorithm>
 #include <atomic>
 #include <string.h>
 #include <type_traits>
@@ -55,6 +56,15 @@ struct Sm100Dev {
     const int64_t* seqstart_k;
     int* status;
     int batch, seqlen_q, seqlen_k, hq, hkv, total_q;
+    // paged K/V (page > 0): pools [num_pages, page, hkv, 128]; a sequence's page ids are page_ids[k0 ...] with k0 the
+    // sequence's offset into the list (block table row or kv_indptr entry)
+    const void* v;
+    const int32_t* page_ids;
+    const int32_t* kv_indptr;
+    const int32_t* kv_last_page_len;
+    const int32_t* seqlen_k32;
+    const int64_t* cache_batch_idx;
+    int page, bt_stride;
     int causal;       // 0 none, 1 top-left, 2 bottom-right
     int num_levels;   // row blocks of the longest sequence (128 rows when heads are paired, else 256)
     int pair_heads;   // the two Q tiles of a work item are two q heads of one kv group
@@ -323,12 +333,30 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
             smem_u32(&ctrl->tmem_base)));
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
     }
+    if (p.page > 0) {  // paged: slots start as zeros (rows that are never loaded stay finite)
+        for (int idx = threadIdx.x; idx < 2 * KV_SLOTS * TILE_BYTES / 16; idx += NTHREADS)
+            reinterpret_cast<uint4*>(sK)[idx] = make_uint4(0u, 0u, 0u, 0u);
+        fence_proxy_async_smem();
+    }
     // ---- schedule: blocks per sequence, then the first work item of every level ----
     for (int b = threadIdx.x; b < p.batch; b += NTHREADS) {
         const int64_t q0 = p.seqstart_q ? p.seqstart_q[b] : (int64_t)b * p.seqlen_q;
-        const int64_t k0 = p.seqstart_k ? p.seqstart_k[b] : (int64_t)b * p.seqlen_k;
         const int sq = p.seqstart_q ? (int)(p.seqstart_q[b + 1] - q0) : p.seqlen_q;
-        const int sk = p.seqstart_k ? (int)(p.seqstart_k[b + 1] - k0) : p.seqlen_k;
+        int64_t k0;
+        int sk;
+        if (p.page > 0) {  // k0 = where the sequence's page ids start in page_ids
+            if (p.kv_indptr) {
+                const int pb = p.kv_indptr[b], pe = p.kv_indptr[b + 1];
+                k0 = pb;
+                sk = pe > pb ? (pe - pb - 1) * p.page + p.kv_last_page_len[b] : 0;
+            } else {
+                k0 = (p.cache_batch_idx ? p.cache_batch_idx[b] : (int64_t)b) * p.bt_stride;
+                sk = p.seqlen_k32 ? p.seqlen_k32[b] : p.seqlen_k;
+            }
+        } else {
+            k0 = p.seqstart_k ? p.seqstart_k[b] : (int64_t)b * p.seqlen_k;
+            sk = p.seqstart_k ? (int)(p.seqstart_k[b + 1] - k0) : p.seqlen_k;
+        }
         ctrl->seq_q0[b] = (int)q0;  // row indices fit 31 bits (checked on the host)
         ctrl->seq_sq[b] = sq;
         ctrl->seq_k0[b] = (int)k0;
@@ -379,6 +407,14 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                 tma_prefetch_desc(&map_v);
             }
             uint32_t kv_cnt = 0, q_cnt = 0;  // K/V tiles and Q loads issued so far (ring positions)
+            // Paged pools are read in chunks of min(page, 128) tokens: one TMA box per chunk and 64-column half.
+            // A chunk that the sequence only partly fills is the tail of its last page, and what lies behind the
+            // sequence end there is whatever the allocator left: for K that is harmless (those scores are masked by
+            // index), but P = 0 times a NaN in V is NaN, so the V rows of such a chunk are copied by the warp with
+            // zeros behind the sequence end.  Chunks wholly behind the end are not loaded at all; the slot then
+            // keeps rows of earlier tiles (real data, or the zeros the slots start with).
+            const int chunk = p.page > 0 ? min(p.page, BN) : BN;
+            const int chunks = BN / chunk;
             for (int rnd = 0; rnd < rounds; ++rnd) {
                 Item it;
                 get_item(ctrl, p, rnd, total_items, lane, it);
@@ -396,22 +432,87 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                                 tma_load_3d(sQ + TILE_BYTES + hb * HALF_BYTES, &map_q, &ctrl->q_full, hb * 64, it.h[1],
                                             it.q0 + it.row0[1]);
                     }
-                    for (int n = 0; ok && n < it.N; ++n, ++kv_cnt) {
-                        const int s = kv_cnt % KV_SLOTS;
-                        const uint32_t ph = (kv_cnt / KV_SLOTS) & 1u;
-                        const int row = it.k0 + n * BN;
-                        if (!(ok = mbar_wait_bounded(&ctrl->k_empty[s], ph ^ 1u, abort_flag, p.status, 0x10))) break;
-                        mbar_expect_tx(&ctrl->k_full[s], TILE_BYTES);
-                        for (int hb = 0; hb < 2; ++hb)
-                            tma_load_3d(sK + s * TILE_BYTES + hb * HALF_BYTES, &map_k, &ctrl->k_full[s], hb * 64, it.kh, row);
-                        if (!(ok = mbar_wait_bounded(&ctrl->v_empty[s], ph ^ 1u, abort_flag, p.status, 0x20))) break;
-                        mbar_expect_tx(&ctrl->v_full[s], TILE_BYTES);
-                        for (int hb = 0; hb < 2; ++hb)
-                            tma_load_3d(sV + s * TILE_BYTES + hb * HALF_BYTES, &map_v, &ctrl->v_full[s], hb * 64, it.kh, row);
+                    if (p.page == 0) {  // contiguous K/V: one box per tile and 64-column half
+                        for (int n = 0; ok && n < it.N; ++n) {
+                            const uint32_t kc = kv_cnt + n;
+                            const int s = kc % KV_SLOTS;
+                            const uint32_t ph = (kc / KV_SLOTS) & 1u;
+                            const int row = it.k0 + n * BN;
+                            if (!(ok = mbar_wait_bounded(&ctrl->k_empty[s], ph ^ 1u, abort_flag, p.status, 0x10))) break;
+                            mbar_expect_tx(&ctrl->k_full[s], TILE_BYTES);
+                            for (int hb = 0; hb < 2; ++hb)
+                                tma_load_3d(sK + s * TILE_BYTES + hb * HALF_BYTES, &map_k, &ctrl->k_full[s], hb * 64, it.kh, row);
+                            if (!(ok = mbar_wait_bounded(&ctrl->v_empty[s], ph ^ 1u, abort_flag, p.status, 0x20))) break;
+                            mbar_expect_tx(&ctrl->v_full[s], TILE_BYTES);
+                            for (int hb = 0; hb < 2; ++hb)
+                                tma_load_3d(sV + s * TILE_BYTES + hb * HALF_BYTES, &map_v, &ctrl->v_full[s], hb * 64, it.kh, row);
+                        }
                     }
                 }
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                if (!ok) break;
+                if (p.page == 0) kv_cnt += it.N;
+                // ---- paged: lane c owns chunk c of the tile: the pool row of its first token and the tokens it holds.
+                // Each lane issues the copies of its own chunk (one warp instruction starts up to 8 of them), and the
+                // page ids of the next tile are fetched while this tile's slots are awaited.
+                auto lookup = [&](int n, int& row, int& valid) {
+                    row = 0;
+                    valid = 0;
+                    if (lane < chunks && n < it.N) {
+                        const int key0 = n * BN + lane * chunk;
+                        valid = max(0, min(chunk, it.sk - key0));
+                        if (valid > 0) row = p.page_ids[it.k0 + key0 / p.page] * p.page + key0 % p.page;
+                    }
+                };
+                int my_row = 0, my_valid = 0;
+                if (p.page > 0) lookup(0, my_row, my_valid);
+                for (int n = 0; p.page > 0 && ok && n < it.N; ++n, ++kv_cnt) {
+                    const int s = kv_cnt % KV_SLOTS;
+                    const uint32_t ph = (kv_cnt / KV_SLOTS) & 1u;
+                    int next_row, next_valid;
+                    lookup(n + 1, next_row, next_valid);
+                    const uint32_t any_mask = __ballot_sync(0xffffffffu, my_valid > 0);
+                    const uint32_t full_mask = __ballot_sync(0xffffffffu, my_valid == chunk);
+                    if (lane == 0) {
+                        ok = mbar_wait_bounded(&ctrl->k_empty[s], ph ^ 1u, abort_flag, p.status, 0x10);
+                        if (ok) mbar_expect_tx(&ctrl->k_full[s], __popc(any_mask) * chunk * HD * 2);
+                    }
+                    ok = __shfl_sync(0xffffffffu, ok, 0);
+                    if (!ok) break;
+                    if (my_valid > 0)
+                        for (int hb = 0; hb < 2; ++hb)
+                            tma_load_3d(sK + s * TILE_BYTES + hb * HALF_BYTES + lane * chunk * 128, &map_k, &ctrl->k_full[s],
+                                        hb * 64, it.kh, my_row);
+                    if (lane == 0) ok = mbar_wait_bounded(&ctrl->v_empty[s], ph ^ 1u, abort_flag, p.status, 0x20);
+                    ok = __shfl_sync(0xffffffffu, ok, 0);
+                    if (!ok) break;
+                    const uint32_t part_mask = any_mask & ~full_mask;  // at most one chunk: the tail of the last page
+                    if (part_mask) {
+                        const int c = __ffs(part_mask) - 1;
+                        const int v = __shfl_sync(0xffffffffu, my_valid, c), row = __shfl_sync(0xffffffffu, my_row, c);
+                        const uint4* src = reinterpret_cast<const uint4*>((const T*)p.v + ((int64_t)row * p.hkv + it.kh) * HD);
+                        const int64_t row_pieces = (int64_t)p.hkv * HD * 2 / 16;  // 16-byte pieces between two tokens
+                        uint8_t* dst = sV + s * TILE_BYTES + c * chunk * 128;
+                        for (int idx = lane; idx < chunk * 16; idx += 32) {
+                            const int r = idx >> 4, piece = idx & 15, hb = piece >> 3, ch = piece & 7;
+                            const int t = c * chunk + r;  // token inside the tile: selects the swizzle phase
+                            uint4 val = make_uint4(0u, 0u, 0u, 0u);
+                            if (r < v) val = src[r * row_pieces + piece];
+                            *reinterpret_cast<uint4*>(dst + hb * HALF_BYTES + r * 128 + ((ch ^ (t & 7)) << 4)) = val;
+                        }
+                        fence_proxy_async_smem();  // the MMAs read these rows through the async proxy
+                        __syncwarp();
+                    }
+                    if (lane == 0) mbar_expect_tx(&ctrl->v_full[s], __popc(full_mask) * chunk * HD * 2);
+                    if (my_valid == chunk)
+                        for (int hb = 0; hb < 2; ++hb)
+                            tma_load_3d(sV + s * TILE_BYTES + hb * HALF_BYTES + lane * chunk * 128, &map_v, &ctrl->v_full[s],
+                                        hb * 64, it.kh, my_row);
+                    my_row = next_row;
+                    my_valid = next_valid;
+                }
                 ++q_cnt;
-                if (!__shfl_sync(0xffffffffu, ok, 0)) break;
+                if (!ok) break;
             }
         } else if (warp == 8) {
             // ================================ MMA issuer ================================
@@ -671,12 +772,12 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     }
 }
 
-int make_map_3d(CUtensorMap* map, const void* base, int dtype, int64_t rows, int64_t heads) {
+int make_map_3d(CUtensorMap* map, const void* base, int dtype, int64_t rows, int64_t heads, int box_rows = BM) {
     PFN_encodeTiled enc = get_encode_tiled();
     FCK_REQUIRE(enc != nullptr, FLASHCK_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
     const cuuint64_t dims[3] = {(cuuint64_t)HD, (cuuint64_t)heads, (cuuint64_t)(rows > 0 ? rows : 1)};
     const cuuint64_t strides[2] = {(cuuint64_t)(HD * 2), (cuuint64_t)(heads * HD * 2)};
-    const cuuint32_t box[3] = {64, 1, (cuuint32_t)BM};
+    const cuuint32_t box[3] = {64, 1, (cuuint32_t)box_rows};
     const cuuint32_t estr[3] = {1, 1, 1};
     const CUtensorMapDataType dt =
         dtype == FLASHCK_DTYPE_BFLOAT16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
@@ -708,12 +809,17 @@ int make_map_o(CUtensorMap* map, const void* base, int dtype, int64_t rows, int6
 template <typename T, int NPOLY8>
 int launch_t(const FwdParams& p, const Sm100Dev& dev, cudaStream_t stream) {
     const int64_t rows_q = p.seqstart_q ? p.total_q : p.batch * p.seqlen_q;
-    const int64_t rows_k = p.seqstart_k ? p.seqlen_k : p.batch * p.seqlen_k;  // group mode: packed total
+    const bool paged = p.block_table || p.kv_indptr;
+    // contiguous: group mode carries the packed total in seqlen_k.  Paged: the reference sizes its pools to
+    // max_num_page_blocks pages, a serving pool is usually larger, so the token axis is left unbounded and page ids
+    // are trusted like any pointer.
+    const int64_t rows_k = paged ? 0x7fffff00ll : (p.seqstart_k ? p.seqlen_k : p.batch * p.seqlen_k);
+    const int box_k = paged ? (int)std::min<int64_t>(p.page, BN) : BN;
     CUtensorMap mq, mk, mv, mo;
     int rc;
     if ((rc = make_map_3d(&mq, p.q, p.dtype, rows_q, p.hq))) return rc;
-    if ((rc = make_map_3d(&mk, p.k, p.dtype, rows_k, p.hkv))) return rc;
-    if ((rc = make_map_3d(&mv, p.v, p.dtype, rows_k, p.hkv))) return rc;
+    if ((rc = make_map_3d(&mk, p.k, p.dtype, rows_k, p.hkv, box_k))) return rc;
+    if ((rc = make_map_3d(&mv, p.v, p.dtype, rows_k, p.hkv, box_k))) return rc;
     if ((rc = make_map_o(&mo, p.o, p.dtype, rows_q, p.hq))) return rc;
     auto kern = fmha_fwd_sm100_kernel<T, NPOLY8>;
     const size_t smem = 1024 + (size_t)(2 + 2 * KV_SLOTS) * TILE_BYTES + 8 * STAGE_BYTES + sizeof(Ctrl);
@@ -736,11 +842,20 @@ int launch_t(const FwdParams& p, const Sm100Dev& dev, cudaStream_t stream) {
 bool fwd_sm100_supported(const FwdParams& p) {
     if (!g_use_sm100.load()) return false;
     if (p.d != HD || p.dv != HD) return false;
-    if (p.block_table || p.kv_indptr || p.cache_batch_idx || p.seqlen_k64 || p.seqlen_k32) return false;
-    if ((p.seqstart_q == nullptr) != (p.seqstart_k == nullptr)) return false;
+    const bool paged = p.block_table || p.kv_indptr;
+    if (paged) {
+        // pages of 16 .. 128 tokens that divide a 128-key tile, or whole multiples of it
+        if (p.page < 16 || !((BN % p.page == 0) || (p.page % BN == 0))) return false;
+        if (p.seqlen_k64 || p.seqstart_k) return false;
+        if (p.kv_indptr && (!p.kv_page_indices || !p.kv_last_page_len || p.cache_batch_idx)) return false;
+    } else {
+        if (p.cache_batch_idx || p.seqlen_k64 || p.seqlen_k32) return false;
+        if ((p.seqstart_q == nullptr) != (p.seqstart_k == nullptr)) return false;
+    }
     if (p.mask_type != 0 && !(p.mask_type <= 2 && p.wl < 0 && p.wr == 0)) return false;  // none or causal
     if (p.batch > kMaxBatch || (p.max_seqlen_q + BM - 1) / BM > kMaxLevels) return false;  // on-chip schedule
-    if (p.total_q >= (1ll << 31) || p.batch * p.seqlen_k >= (1ll << 31)) return false;
+    if (p.total_q >= (1ll << 31) || (!paged && p.batch * p.seqlen_k >= (1ll << 31))) return false;
+    if (p.batch * std::max<int64_t>(p.seqlen_q, 1) >= (1ll << 31)) return false;
     return true;
 }
 
@@ -751,6 +866,12 @@ int launch_fwd_sm100(const FwdParams& p, cudaStream_t stream) {
     dev.o = p.o; dev.lse = p.lse; dev.seqstart_q = p.seqstart_q; dev.seqstart_k = p.seqstart_k; dev.status = status;
     dev.batch = (int)p.batch; dev.seqlen_q = (int)p.seqlen_q; dev.seqlen_k = (int)p.seqlen_k;
     dev.hq = (int)p.hq; dev.hkv = (int)p.hkv; dev.total_q = (int)p.total_q;
+    dev.v = p.v;
+    dev.page_ids = p.kv_indptr ? p.kv_page_indices : p.block_table;
+    dev.kv_indptr = p.kv_indptr; dev.kv_last_page_len = p.kv_last_page_len; dev.seqlen_k32 = p.seqlen_k32;
+    dev.cache_batch_idx = p.cache_batch_idx;
+    dev.page = (p.block_table || p.kv_indptr) ? (int)p.page : 0;
+    dev.bt_stride = (int)p.bt_stride;
     dev.causal = p.mask_type;
     dev.pair_heads = ((p.hq / p.hkv) % 2 == 0) ? 1 : 0;
     dev.num_levels = (int)((p.max_seqlen_q + (dev.pair_heads ? BM : 2 * BM) - 1) / (dev.pair_heads ? BM : 2 * BM));

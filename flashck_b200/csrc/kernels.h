@@ -85,6 +85,7 @@ struct FwdParams {
     int64_t batch, seqlen_q, seqlen_k, hq, hkv, d, dv, max_seqlen_q;
     int64_t total_q;
     int64_t bt_stride, page;
+    int64_t num_pages;  // paged: token-slot pages in the K/V pools (0 if unknown)
     float scale;
     int mask_type;
     int64_t wl, wr;
@@ -92,7 +93,7 @@ struct FwdParams {
 };
 int launch_fwd_generic(const FwdParams& p, cudaStream_t stream);
 
-// ---- tcgen05 prefill (fmha_fwd_sm100.cu): hdim 128, contiguous K/V ------------------------------
+// ---- tcgen05 prefill (fmha_fwd_sm100.cu): hdim 128, contiguous or paged K/V ------------------------------
 bool fwd_sm100_supported(const FwdParams& p);
 int launch_fwd_sm100(const FwdParams& p, cudaStream_t stream);
 int fwd_set_param(const char* key, int64_t value);

@@ -3,7 +3,7 @@ same seeded inputs."""
 import pytest
 import torch
 
-from flashck_b200 import ops
+from flashck_b200 import _lib, ops
 from flashck_b200.utils import MaskEnum, RopeEnum
 from flashck_b200.utils.inputs import (make_paged_cache, normal_tensor, rotary_cos_sin, to_seqstarts,
                                        uniform_seqlens)
@@ -144,6 +144,91 @@ def test_paged_prefill_variants():
                                  max(lens_q), causal=True, return_lse=True)
     assert_o_close(o2, o_ref)
     assert_lse_close(lse2, lse_ref)
+
+
+def _poison_page_tails(cache, lens, page):
+    """NaN in every token slot of a sequence's pages past its length (what a cache allocated with torch.empty may
+    hold there): no kernel may let those slots reach the output."""
+    k, v = cache.k.clone(), cache.v.clone()
+    for b, n in enumerate(lens):
+        pages = -(-n // page)
+        if pages == 0 or n % page == 0:
+            continue
+        pid = int(cache.block_table[b, pages - 1])
+        k[pid, n % page:] = float("nan")
+        v[pid, n % page:] = float("nan")
+    return k, v
+
+
+@pytest.mark.parametrize("page", [16, 32, 64, 128, 256])
+def test_paged_paths_ignore_garbage_past_the_sequence_end(page):
+    dtype = torch.bfloat16
+    hq, hkv, d = 8, 2, 128
+    lens_k = [40, 129, 17, 300, 1, 700, 256]
+    lens_q = [40, 100, 3, 64, 1, 515, 256]
+    cache = make_paged_cache(lens_k, hkv, d, d, page, dtype, seed=15)
+    k_bad, v_bad = _poison_page_tails(cache, lens_k, page)
+    cu_q = to_seqstarts(lens_q)
+    q = normal_tensor((int(cu_q[-1]), hq, d), dtype, 32)
+    o_ref, lse_ref = oracle.fmha_fwd(q, cache.k, cache.v, seqstart_q=cu_q, seqlen_k=cache.seqlen_k,
+                                     block_table=cache.block_table, mask_type=2, window=(-1, 0))
+    o, lse = ops.fmha_fwd_paged_kv_prefill(_cu(q), _cu(k_bad), _cu(v_bad), _cu(cache.block_table),
+                                           _cu(cache.seqlen_k), cu_seqlens_q=_cu(cu_q), max_seqlen_q=max(lens_q),
+                                           causal=True, return_lse=True)
+    assert_o_close(o, o_ref, "paged prefill O")
+    assert_lse_close(lse, lse_ref, "paged prefill LSE")
+    # decode over the same poisoned cache
+    qd = normal_tensor((len(lens_k), 1, hq, d), dtype, 33)
+    od_ref, lsed_ref = oracle.fmha_fwd(qd, cache.k, cache.v, seqlen_k=cache.seqlen_k, block_table=cache.block_table)
+    for splits in (1, 3):
+        od, lsed = ops.fmha_fwd_splitkv(_cu(qd), _cu(k_bad), _cu(v_bad), seqlen_k=_cu(cache.seqlen_k),
+                                        block_table=_cu(cache.block_table), num_splits=splits, return_lse=True)
+        assert_o_close(od, od_ref, f"decode O splits={splits}")
+        assert_lse_close(lsed, lsed_ref, f"decode LSE splits={splits}")
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("page,hq,hkv", [(16, 8, 2), (64, 6, 2), (128, 4, 4), (512, 8, 1)])
+def test_paged_prefill_tcgen05_instance_agrees_with_general_instance_and_oracle(dtype, page, hq, hkv):
+    """hdim 128 paged prefill runs on the tcgen05 instance; the general instance and the oracle are the checks.
+    Lengths cover: keys ending inside a page, inside a 128-key tile, on a tile edge; queries shorter than keys
+    (chunked prefill, bottom-right causal) and equal to them; a sequence with no keys."""
+    d = 128
+    lens_k = [1, 127, 128, 129, 640, 1000, 0, 333]
+    lens_q = [1, 100, 128, 5, 640, 300, 4, 333]
+    cache = make_paged_cache(lens_k, hkv, d, d, page, dtype, seed=21)
+    k_bad, v_bad = _poison_page_tails(cache, lens_k, page)
+    cu_q = to_seqstarts(lens_q)
+    q = normal_tensor((int(cu_q[-1]), hq, d), dtype, 34)
+    o_ref, lse_ref = oracle.fmha_fwd(q, cache.k, cache.v, seqstart_q=cu_q, seqlen_k=cache.seqlen_k,
+                                     block_table=cache.block_table, mask_type=2, window=(-1, 0))
+
+    def run():
+        return ops.fmha_fwd_paged_kv_prefill(_cu(q), _cu(k_bad), _cu(v_bad), _cu(cache.block_table),
+                                             _cu(cache.seqlen_k), cu_seqlens_q=_cu(cu_q), max_seqlen_q=max(lens_q),
+                                             causal=True, return_lse=True)
+    o, lse = run()
+    _lib.set_instance_param(0, "use_sm100", 0)
+    try:
+        o_gen, lse_gen = run()
+    finally:
+        _lib.set_instance_param(0, "use_sm100", 1)
+    assert _lib.device_status() == 0
+    assert_o_close(o, o_ref, "tcgen05 paged O")
+    assert_lse_close(lse, lse_ref, "tcgen05 paged LSE")
+    assert_o_close(o_gen, o_ref, "general paged O")
+    assert_lse_close(lse_gen, lse_ref, "general paged LSE")
+    # the SGLang-style page list of the same cache, no mask
+    npages = [-(-l // page) for l in lens_k]
+    indptr = torch.tensor([0] + list(torch.tensor(npages).cumsum(0)), dtype=torch.int32)
+    indices = torch.cat([cache.block_table[b, :n] for b, n in enumerate(npages)]).to(torch.int32)
+    last = torch.tensor([l - (n - 1) * page if n else 0 for l, n in zip(lens_k, npages)], dtype=torch.int32)
+    o2_ref, lse2_ref = oracle.fmha_fwd(q, cache.k, cache.v, seqstart_q=cu_q, seqlen_k=cache.seqlen_k,
+                                       block_table=cache.block_table)
+    o2, lse2 = ops.batch_prefill(_cu(q), _cu(k_bad), _cu(v_bad), _cu(cu_q), _cu(indptr), _cu(indices), _cu(last),
+                                 max(lens_q), causal=False, return_lse=True)
+    assert_o_close(o2, o2_ref, "batch_prefill O")
+    assert_lse_close(lse2, lse2_ref, "batch_prefill LSE")
 
 
 # ------------------------------------------------------------------------------------------------
