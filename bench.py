@@ -8,8 +8,8 @@ heads, hdim 128, lengths uniform in [512, 4096] from a seed.  `value` is causal-
 (4*d*hq*sum L(L+1)/2 FLOP per step) with inputs resident in HBM; `e2e` is the same metric through the public
 API with pinned host buffers, host<->device copies inside the timed region.  The same run also measures
 BASELINE config 3 (paged split-KV decode, HBM GB/s) and reports it under `extra.decode`.
-With N > 1 (torchrun, one rank per GPU) every rank runs its own seeded batch (no collective on the data path;
-weak scaling) and `extra.long_decode` runs BASELINE config 5: one long context sharded by pages across the ranks,
+With N > 1 (torchrun, one rank per GPU) every rank runs a batch of the same lengths with its own values (no
+collective on the data path; weak scaling) and `extra.long_decode` runs BASELINE config 5: one long context sharded by pages across the ranks,
 partial O/LSE merged after one NCCL all-gather.
 
 `--impl reference` times the CPU statement of the same path (the oracle; the reference's own kernels need
@@ -101,11 +101,13 @@ class ClockSampler:
 # ----------------------------------------------------------------------------------------------------
 # workloads
 # ----------------------------------------------------------------------------------------------------
-def make_prefill(seed: int, device, batch=16, lo=512, hi=4096):
+def make_prefill(seed: int, device, batch=16, lo=512, hi=4096, data_seed=None):
+    """`seed` fixes the lengths (the same on every rank, so that the ranks of a weak-scaling run carry equal work);
+    `data_seed` the values."""
     lens = uniform_seqlens(batch, lo, hi, seed)
     cu = to_seqstarts(lens)
     total = int(cu[-1])
-    g = torch.Generator(device=device).manual_seed(seed)
+    g = torch.Generator(device=device).manual_seed(seed if data_seed is None else data_seed)
     q = torch.randn(total, HQ, D, generator=g, device=device, dtype=torch.float32).to(torch.bfloat16)
     k = torch.randn(total, HKV, D, generator=g, device=device, dtype=torch.float32).to(torch.bfloat16)
     v = torch.randn(total, HKV, D, generator=g, device=device, dtype=torch.float32).to(torch.bfloat16)
@@ -138,18 +140,19 @@ def make_paged_prefill(w, page: int, seed: int, device):
             "seqlen": torch.tensor(lens, dtype=torch.int32, device=device), "page": page}
 
 
-def make_decode(seed: int, device, batch=64, lo=1024, hi=32768, page=16, hq=HQ, hkv=HKV, lens=None):
+def make_decode(seed: int, device, batch=64, lo=1024, hi=32768, page=16, hq=HQ, hkv=HKV, lens=None, data_seed=None):
     lens = lens or uniform_seqlens(batch, lo, hi, seed)
     batch = len(lens)
     pages = [-(-L // page) for L in lens]
     total_pages = sum(pages)
-    perm = iota_shuffle(total_pages, seed)
+    data_seed = seed if data_seed is None else data_seed
+    perm = iota_shuffle(total_pages, data_seed)
     table = torch.zeros((batch, max(pages)), dtype=torch.int32)
     off = 0
     for b, n in enumerate(pages):
         table[b, :n] = perm[off:off + n]
         off += n
-    g = torch.Generator(device=device).manual_seed(seed + 1)
+    g = torch.Generator(device=device).manual_seed(data_seed + 1)
     kpool = torch.empty(total_pages, page, hkv, D, device=device, dtype=torch.bfloat16)
     vpool = torch.empty(total_pages, page, hkv, D, device=device, dtype=torch.bfloat16)
     chunk = max(1, (1 << 28) // (page * hkv * D))  # fill in pieces: fp32 randn of the whole pool would double memory
@@ -165,15 +168,16 @@ def make_decode(seed: int, device, batch=64, lo=1024, hi=32768, page=16, hq=HQ, 
             "page": page, "hq": hq, "hkv": hkv}
 
 
-def make_append_decode(seed: int, device, batch=32, lo=2048, hi=16384, page=16):
+def make_append_decode(seed: int, device, batch=32, lo=2048, hi=16384, page=16, data_seed=None):
     """BASELINE config 4: a paged cache holding `ctx` tokens per sequence with room for 1..16 appended ones."""
     from flashck_b200.utils.inputs import rotary_cos_sin
     ctx = uniform_seqlens(batch, lo, hi, seed)
     new = uniform_seqlens(batch, 1, 16, seed + 1)
     cap = [c + n for c, n in zip(ctx, new)]
-    w = make_decode(seed + 2, device, lens=cap, page=page)
+    data_seed = seed if data_seed is None else data_seed
+    w = make_decode(seed + 2, device, lens=cap, page=page, data_seed=data_seed + 2)
     total = sum(new)
-    g = torch.Generator(device=device).manual_seed(seed + 3)
+    g = torch.Generator(device=device).manual_seed(data_seed + 3)
     mk = lambda h: torch.randn(total, h, D, generator=g, device=device, dtype=torch.float32).to(torch.bfloat16)
     cos, sin = rotary_cos_sin(max(cap) + 1, D, torch.bfloat16)
     w.update({"ctx": ctx, "new": new, "qn": mk(HQ), "kn": mk(HKV), "vn": mk(HKV), "cu_new": to_seqstarts(new).to(device),
@@ -345,9 +349,9 @@ def main():
 
     # ------------------------------------------------------------------ prefill (headline)
     if args.small:
-        w = make_prefill(1234 + rank, device, batch=4, lo=512, hi=2048)
+        w = make_prefill(1234, device, batch=4, lo=512, hi=2048, data_seed=1234 + rank)
     else:
-        w = make_prefill(1234 + rank, device)
+        w = make_prefill(1234, device, data_seed=1234 + rank)
 
     def prefill_step():
         return ops.fmha_fwd_var_len(w["q"], w["k"], w["v"], w["cu"], w["cu"], w["max_len"], causal=True,
@@ -388,7 +392,7 @@ def main():
         "warmup": warmup, "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic",
         "config": {"workload": "varlen causal batch prefill (BASELINE config 2): batch 16 per GPU, 32 q / 8 kv heads, "
-                               "hdim 128, L~U[512,4096], seed 1234+rank" + (" [--small]" if args.small else ""),
+                               "hdim 128, L~U[512,4096] from seed 1234 (the same lengths on every rank, values seeded per rank)" + (" [--small]" if args.small else ""),
                    "tokens_per_gpu": w["total"], "flops_per_gpu_step": w["flops"],
                    "flop_count": "causal-effective 4*d*hq*sum L(L+1)/2",
                    "l2": "inputs (q,k,v,o > 600 MB) larger than the 126 MB L2", "parallelism": f"dp{world}"},
@@ -428,9 +432,9 @@ def main():
     # ------------------------------------------------------------------ decode (config 3)
     if not args.no_decode:
         if args.small:
-            wd = make_decode(4321 + rank, device, batch=16, lo=1024, hi=16384)
+            wd = make_decode(4321, device, batch=16, lo=1024, hi=16384, data_seed=4321 + rank)
         else:
-            wd = make_decode(4321 + rank, device)
+            wd = make_decode(4321, device, data_seed=4321 + rank)
         S = ops.default_num_splits(len(wd["lens"]))
         ws = ops.splitkv_workspace(wd["q"], D, S)
 
@@ -486,7 +490,7 @@ def main():
 
     # ------------------------------------------------------------------ append + decode (config 4)
     if not args.no_decode and not args.small:
-        wa = make_append_decode(777 + rank, device)
+        wa = make_append_decode(777, device, data_seed=777 + rank)
         S4 = ops.default_num_splits(len(wa["lens"]))
         cu_n, max_new = wa["cu_new"], max(wa["new"])
         ws4 = ops.splitkv_workspace(wa["qn"], D, S4, cu_n)

@@ -5,10 +5,12 @@ API), ``nn`` (modules) and ``utils`` (registry, enums).  The compute lives in ``
 (``csrc/``, C ABI in ``include/flashck_b200.h``) and is reached through ``ctypes``; importing the package does
 not load the library, the first operator call does -- and raises if it is missing.
 """
-from . import ops, utils
+from . import nn, ops, utils
+from .compat import install_as_flash_ck
 from .ops import (batch_prefill, fmha_fwd, fmha_fwd_append_kv, fmha_fwd_paged_kv_prefill, fmha_fwd_splitkv,
                   fmha_fwd_splitkv_combine, fmha_fwd_var_len)
-from .utils import get_available_operations, is_available, register_flashck_functions
+from .utils import (get_available_operations, get_flag_value, is_available, print_all_flags, print_flag_info,
+                    register_flashck_functions, set_flag_value)
 
 __version__ = "0.1.0"
 
@@ -24,7 +26,7 @@ register_flashck_functions(utils.FlashCKOperationType.FMHA.value, {
 })
 
 __all__ = [
-    "ops", "utils", "fmha_fwd", "fmha_fwd_var_len", "batch_prefill", "fmha_fwd_paged_kv_prefill",
+    "ops", "nn", "utils", "install_as_flash_ck", "fmha_fwd", "fmha_fwd_var_len", "batch_prefill", "fmha_fwd_paged_kv_prefill",
     "fmha_fwd_splitkv", "fmha_fwd_splitkv_combine", "fmha_fwd_append_kv", "is_available",
-    "get_available_operations",
+    "get_available_operations", "get_flag_value", "set_flag_value", "print_all_flags", "print_flag_info",
 ]

@@ -65,7 +65,8 @@ struct Sm100Dev {
     const int32_t* seqlen_k32;
     const int64_t* cache_batch_idx;
     int page, bt_stride;
-    int causal;       // 0 none, 1 top-left, 2 bottom-right
+    int causal;       // mask type: 0 none, 1 top-left, 2 bottom-right, 3 window with top-left alignment
+    int wl, wr;       // window of a masked problem: keys [i + shift - wl, i + shift + wr] of row i; -1 = unbounded
     int num_levels;   // row blocks of the longest sequence (128 rows when heads are paired, else 256)
     int pair_heads;   // the two Q tiles of a work item are two q heads of one kv group
     float scale_log2;
@@ -187,7 +188,7 @@ __device__ __forceinline__ float2 exp2_poly2(float2 x) {
 constexpr int kMaxBatch = 256;    // sequences the on-chip schedule can hold (larger batches use the general instance)
 constexpr int kMaxLevels = 512;   // row blocks per sequence the on-chip schedule can hold
 constexpr int STAGE_BYTES = 32 * 32 * 2;  // per softmax warp: 32 rows x 32 columns of O on their way to a TMA store
-constexpr int kMaxRounds = 96;    // work items per CTA decoded up front (later ones are decoded on the fly)
+constexpr int kMaxRounds = 1024;  // work items per CTA (the host sends larger problems to the general instance)
 
 // One work item = two 128-row Q tiles that share their K/V tiles.  With an even GQA ratio the tiles are the same
 // 128 rows of two neighbouring q heads of one kv group: both see the same keys, so they run the same number of
@@ -198,6 +199,7 @@ struct Item {
     int h[2];     // q head of each tile
     int row0[2];  // first row (inside the sequence) of each tile
     int nt[2];    // key tiles each Q tile needs (0: the tile does not exist or sees nothing)
+    int n0;       // first key tile of the item (a left window skips the tiles before it)
     int q0, k0;   // first row of the sequence in the packed Q / K buffers
 };
 
@@ -212,7 +214,7 @@ struct Ctrl {
     int level_start[kMaxLevels + 1];    // first work item of each level; level 0 = highest block index
     int nblk[kMaxBatch];                // row blocks of each sequence
     int seq_q0[kMaxBatch], seq_sq[kMaxBatch], seq_k0[kMaxBatch], seq_sk[kMaxBatch];  // first row / length, Q and K
-    Item items[kMaxRounds];             // this CTA's work list
+    uint32_t items[kMaxRounds];         // this CTA's work list: valid << 31 | sequence << 22 | head index << 12 | row block
 };
 
 // Item taken by CTA `cta` in round `rnd` of a grid of `g` CTAs: rounds alternate direction (snake order), so that
@@ -224,7 +226,7 @@ __device__ __forceinline__ int item_of_round(int rnd, int cta, int g) {
 // Work items are ordered by decreasing row-block index (under a causal mask: decreasing cost), then by sequence,
 // then by head, so that the q heads of a GQA group -- which read the same K/V -- run at the same time on
 // neighbouring SMs and share those tiles through L2.  Warp-collective.
-__device__ __forceinline__ void decode_item(const Ctrl* ctrl, const Sm100Dev& p, int w, int lane, Item& it) {
+__device__ __forceinline__ uint32_t find_item(const Ctrl* ctrl, const Sm100Dev& p, int w, int lane) {
     int lo = 0, hi = ctrl->num_levels;  // last level whose start is <= w
     while (hi - lo > 1) {
         const int mid = (lo + hi) >> 1;
@@ -246,7 +248,13 @@ __device__ __forceinline__ void decode_item(const Ctrl* ctrl, const Sm100Dev& p,
         }
         bj -= c;
     }
-    it.valid = 1;
+    return 0x80000000u | ((uint32_t)b << 22) | ((uint32_t)hj << 12) | (uint32_t)blk;
+}
+
+// The fields of a work item from its packed form: a few shared-memory reads and integer operations.
+__device__ __forceinline__ void expand_item(const Ctrl* ctrl, const Sm100Dev& p, uint32_t packed, Item& it) {
+    it.valid = packed >> 31;
+    const int b = (packed >> 22) & 0x1ff, hj = (packed >> 12) & 0x3ff, blk = packed & 0xfff;
     it.b = b;
     it.q0 = ctrl->seq_q0[b];
     it.sq = ctrl->seq_sq[b];
@@ -262,37 +270,40 @@ __device__ __forceinline__ void decode_item(const Ctrl* ctrl, const Sm100Dev& p,
         it.row0[1] = blk * 2 * BM + BM;
     }
     it.kh = it.h[0] / (p.hq / p.hkv);
-    // key tiles each Q tile needs: all of them, or up to its last row's diagonal
+    // key tiles each Q tile needs: from the first key its first row sees to the last key its last row sees.  The two
+    // tiles of an item walk the same tiles n0 .. n0+N-1: with paired heads their ranges are equal, and without them a
+    // left window is not served by this instance (n0 = 0).
     it.shift = (p.causal == 2) ? it.sk - it.sq : 0;
-    const int nk_all = (it.sk + BN - 1) / BN;
+    it.n0 = 0;
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
         const int first = it.row0[i];
         int n = 0;
         if (first < it.sq) {
-            n = nk_all;
+            int lo_key = 0, hi_key = it.sk - 1;
             if (p.causal) {
-                const int hi_key = min(it.sq, first + BM) - 1 + it.shift;  // last visible key of the tile's last row
-                n = hi_key < 0 ? 0 : min(nk_all, hi_key / BN + 1);
+                if (p.wl >= 0) lo_key = max(0, first + it.shift - p.wl);
+                if (p.wr >= 0) hi_key = min(hi_key, min(it.sq, first + BM) - 1 + it.shift + p.wr);
+            }
+            if (hi_key >= lo_key) {
+                if (i == 0) it.n0 = lo_key / BN;
+                n = hi_key / BN - it.n0 + 1;
             }
         }
         it.nt[i] = n;
     }
+    if (it.nt[0] == 0) it.n0 = 0;
     it.N = max(it.nt[0], it.nt[1]);
 }
 
-// The work item of round `rnd`: from the table filled at start-up, or decoded on the fly.  Warp-collective.
+// The work item of round `rnd` of this CTA, from the table filled at start-up.
 __device__ __forceinline__ void get_item(const Ctrl* ctrl, const Sm100Dev& p, int rnd, int total_items, int lane, Item& it) {
-    if (rnd < kMaxRounds) {
-        it = ctrl->items[rnd];
-        return;
-    }
-    const int w = item_of_round(rnd, blockIdx.x, gridDim.x);
-    it.valid = 0;
-    if (w < total_items) decode_item(ctrl, p, w, lane, it);
+    expand_item(ctrl, p, ctrl->items[rnd], it);
 }
 
-template <typename T, int NPOLY8>
+// WINDOW: the mask has a left window or a right window other than 0 (everything but no mask / causal); a separate
+// instance, so that the common masks do not carry the second bound of the visible range through the softmax loop.
+template <typename T, int NPOLY8, bool WINDOW>
 __global__ void __launch_bounds__(NTHREADS, 1)
 fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                       const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_o,
@@ -384,13 +395,15 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     tc_fence_after();
     const uint32_t tmem = ctrl->tmem_base;
     const int total_items = ctrl->level_start[p.num_levels];
-    const int rounds = (total_items + (int)gridDim.x - 1) / (int)gridDim.x;
-    for (int rnd = warp; rnd < min(rounds, kMaxRounds); rnd += NTHREADS / 32) {  // this CTA's work list
+    int rounds = (total_items + (int)gridDim.x - 1) / (int)gridDim.x;
+    if (rounds > kMaxRounds) {  // the host checks an upper bound of this; never silently drop work
+        if (threadIdx.x == 0) atomicOr(p.status, 0x20000000);
+        rounds = 0;
+    }
+    for (int rnd = warp; rnd < rounds; rnd += NTHREADS / 32) {  // this CTA's work list
         const int w = item_of_round(rnd, blockIdx.x, gridDim.x);
-        Item it;
-        it.valid = 0;
-        if (w < total_items) decode_item(ctrl, p, w, lane, it);
-        if (lane == 0) ctrl->items[rnd] = it;
+        const uint32_t packed = w < total_items ? find_item(ctrl, p, w, lane) : 0u;
+        if (lane == 0) ctrl->items[rnd] = packed;
     }
     __syncthreads();
 
@@ -437,7 +450,7 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                             const uint32_t kc = kv_cnt + n;
                             const int s = kc % KV_SLOTS;
                             const uint32_t ph = (kc / KV_SLOTS) & 1u;
-                            const int row = it.k0 + n * BN;
+                            const int row = it.k0 + (it.n0 + n) * BN;
                             if (!(ok = mbar_wait_bounded(&ctrl->k_empty[s], ph ^ 1u, abort_flag, p.status, 0x10))) break;
                             mbar_expect_tx(&ctrl->k_full[s], TILE_BYTES);
                             for (int hb = 0; hb < 2; ++hb)
@@ -459,7 +472,7 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                     row = 0;
                     valid = 0;
                     if (lane < chunks && n < it.N) {
-                        const int key0 = n * BN + lane * chunk;
+                        const int key0 = (it.n0 + n) * BN + lane * chunk;
                         valid = max(0, min(chunk, it.sk - key0));
                         if (valid > 0) row = p.page_ids[it.k0 + key0 / p.page] * p.page + key0 % p.page;
                     }
@@ -616,7 +629,10 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
             const int tile_first_row = i ? it.row0[1] : it.row0[0];
             const int row = tile_first_row + r;      // row inside the sequence
             const bool row_ok = row < sq;
-            const int limit = p.causal ? min(sk - 1, row + shift) : sk - 1;  // last visible key of this row
+            // visible keys of this row: [first_key, limit]
+            const int wr = WINDOW ? p.wr : 0, wl = WINDOW ? p.wl : -1;
+            const int limit = (p.causal && wr >= 0) ? min(sk - 1, row + shift + wr) : sk - 1;
+            const int first_key = (WINDOW && p.causal && wl >= 0) ? row + shift - wl : 0;
 
             float m_used = -INFINITY;  // running max actually subtracted (scaled, base 2)
             float l = 0.f;
@@ -630,11 +646,14 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                 for (int c = 0; c < 4; ++c) tmem_ld32(tS + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&sreg[c * 32]));
                 tmem_wait_ld();
                 // mask the diagonal and tail tiles
-                const bool need_mask = (n * BN + BN > sk) || (p.causal && n * BN + BN - 1 > tile_first_row + shift);
+                const int key0 = (it.n0 + n) * BN;
+                const bool need_mask = (key0 + BN > sk) ||
+                                       (p.causal && wr >= 0 && key0 + BN - 1 > tile_first_row + shift + wr) ||
+                                       (WINDOW && p.causal && wl >= 0 && key0 < tile_first_row + BM - 1 + shift - wl);
                 if (need_mask) {
 #pragma unroll
                     for (int j = 0; j < 128; ++j)
-                        if (n * BN + j > limit) sreg[j] = 0xff800000u;  // -inf
+                        if (key0 + j > limit || (WINDOW && key0 + j < first_key)) sreg[j] = 0xff800000u;  // -inf
                 }
                 float mx;
                 {
@@ -806,7 +825,7 @@ int make_map_o(CUtensorMap* map, const void* base, int dtype, int64_t rows, int6
     return FLASHCK_OK;
 }
 
-template <typename T, int NPOLY8>
+template <typename T, int NPOLY8, bool WINDOW>
 int launch_t(const FwdParams& p, const Sm100Dev& dev, cudaStream_t stream) {
     const int64_t rows_q = p.seqstart_q ? p.total_q : p.batch * p.seqlen_q;
     const bool paged = p.block_table || p.kv_indptr;
@@ -821,7 +840,7 @@ int launch_t(const FwdParams& p, const Sm100Dev& dev, cudaStream_t stream) {
     if ((rc = make_map_3d(&mk, p.k, p.dtype, rows_k, p.hkv, box_k))) return rc;
     if ((rc = make_map_3d(&mv, p.v, p.dtype, rows_k, p.hkv, box_k))) return rc;
     if ((rc = make_map_o(&mo, p.o, p.dtype, rows_q, p.hq))) return rc;
-    auto kern = fmha_fwd_sm100_kernel<T, NPOLY8>;
+    auto kern = fmha_fwd_sm100_kernel<T, NPOLY8, WINDOW>;
     const size_t smem = 1024 + (size_t)(2 + 2 * KV_SLOTS) * TILE_BYTES + 8 * STAGE_BYTES + sizeof(Ctrl);
     static thread_local int configured_device = -1;
     int devid = 0;
@@ -852,8 +871,18 @@ bool fwd_sm100_supported(const FwdParams& p) {
         if (p.cache_batch_idx || p.seqlen_k64 || p.seqlen_k32) return false;
         if ((p.seqstart_q == nullptr) != (p.seqstart_k == nullptr)) return false;
     }
-    if (p.mask_type != 0 && !(p.mask_type <= 2 && p.wl < 0 && p.wr == 0)) return false;  // none or causal
+    if (p.mask_type > 3) return false;
+    // a left window needs the two Q tiles of an item to see the same key tiles: paired heads (even GQA ratio)
+    if (p.mask_type != 0 && p.wl >= 0 && (p.hq / p.hkv) % 2 != 0) return false;
+    if (p.wl >= (1ll << 30) || p.wr >= (1ll << 30)) return false;
     if (p.batch > kMaxBatch || (p.max_seqlen_q + BM - 1) / BM > kMaxLevels) return false;  // on-chip schedule
+    if (p.hq > 1023) return false;
+    {   // work items per CTA, bounded from the longest sequence: the on-chip work list holds kMaxRounds
+        const bool pair = (p.hq / p.hkv) % 2 == 0;
+        const int64_t rows_per_block = pair ? BM : 2 * BM;
+        const int64_t items = p.batch * ((p.max_seqlen_q + rows_per_block - 1) / rows_per_block) * (pair ? p.hq / 2 : p.hq);
+        if ((items + sm_count() - 1) / sm_count() > kMaxRounds) return false;
+    }
     if (p.total_q >= (1ll << 31) || (!paged && p.batch * p.seqlen_k >= (1ll << 31))) return false;
     if (p.batch * std::max<int64_t>(p.seqlen_q, 1) >= (1ll << 31)) return false;
     return true;
@@ -873,22 +902,26 @@ int launch_fwd_sm100(const FwdParams& p, cudaStream_t stream) {
     dev.page = (p.block_table || p.kv_indptr) ? (int)p.page : 0;
     dev.bt_stride = (int)p.bt_stride;
     dev.causal = p.mask_type;
+    dev.wl = p.wl < 0 ? -1 : (int)p.wl;
+    dev.wr = p.wr < 0 ? -1 : (int)p.wr;
     dev.pair_heads = ((p.hq / p.hkv) % 2 == 0) ? 1 : 0;
     dev.num_levels = (int)((p.max_seqlen_q + (dev.pair_heads ? BM : 2 * BM) - 1) / (dev.pair_heads ? BM : 2 * BM));
     dev.scale_log2 = p.scale * 1.4426950408889634f;
     const bool bf16 = p.dtype == FLASHCK_DTYPE_BFLOAT16;
-    switch ((int)g_poly8.load()) {
-        case 2: return bf16 ? launch_t<__nv_bfloat16, 2>(p, dev, stream) : launch_t<__half, 2>(p, dev, stream);
-        case 4: return bf16 ? launch_t<__nv_bfloat16, 4>(p, dev, stream) : launch_t<__half, 4>(p, dev, stream);
-        case 3: return bf16 ? launch_t<__nv_bfloat16, 3>(p, dev, stream) : launch_t<__half, 3>(p, dev, stream);
-        default: return bf16 ? launch_t<__nv_bfloat16, 0>(p, dev, stream) : launch_t<__half, 0>(p, dev, stream);
+    const bool window = p.mask_type != 0 && !(p.wl < 0 && p.wr == 0);
+    const bool poly = g_poly8.load() != 0;
+    if (window) {
+        if (poly) return bf16 ? launch_t<__nv_bfloat16, 3, true>(p, dev, stream) : launch_t<__half, 3, true>(p, dev, stream);
+        return bf16 ? launch_t<__nv_bfloat16, 0, true>(p, dev, stream) : launch_t<__half, 0, true>(p, dev, stream);
     }
+    if (poly) return bf16 ? launch_t<__nv_bfloat16, 3, false>(p, dev, stream) : launch_t<__half, 3, false>(p, dev, stream);
+    return bf16 ? launch_t<__nv_bfloat16, 0, false>(p, dev, stream) : launch_t<__half, 0, false>(p, dev, stream);
 }
 
 int fwd_set_param(const char* key, int64_t value) {
     if (!strcmp(key, "use_sm100")) { g_use_sm100 = value; return FLASHCK_OK; }
     if (!strcmp(key, "poly8")) {
-        if (value != 0 && value != 2 && value != 3 && value != 4) return FLASHCK_ERR_INVALID_ARGUMENT;
+        if (value != 0 && value != 3) return FLASHCK_ERR_INVALID_ARGUMENT;  // 3 of every 8 column pairs, or none
         g_poly8 = value;
         return FLASHCK_OK;
     }

@@ -33,18 +33,26 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 FAMILY_IDS = {"fmha_fwd": 0, "fmha_fwd_split_kv": 2}  # FmhaKind values (fmha_library.h:17-25)
 
 
+def _flag(name: str):
+    from .utils import flags
+    return flags.get_flag(name)
+
+
 @dataclass
 class TuningFlags:
-    """The reference's tuning flags with their defaults (core/utils/flags.cc:201-233)."""
-    FC_TUNING_MODE: int = 1              # 0 heuristic (first valid candidate), 1 autotuning, 2 hybrid
-    FC_TUNING_METRIC: int = 0            # 0 latency, 1 TFLOP/s, 2 bandwidth
-    FC_TUNING_NUM_COLD_ITERATION: int = 16
-    FC_TUNING_NUM_REPEATS: int = 64
-    FC_TUNING_FLUSH_CACHE: bool = True
-    FC_TUNING_SEED: int = 42
-    FC_FORCE_PROFILING: bool = False     # re-time even if the cache has an entry
-    FC_TUNING_DB_DIR: str = ""
-    FC_CONFIG_JSON_PATH: str = os.path.join(_HERE, "configs")
+    """The reference's tuning flags (core/utils/flags.cc:201-233).  The defaults are read from the flag registry
+    (``flashck_b200.utils.flags``: ``set_flag_value`` / ``FC_*`` environment variables) when a tuner is built."""
+    FC_TUNING_MODE: int = field(default_factory=lambda: _flag("FC_TUNING_MODE"))    # 0 heuristic, 1 autotuning, 2 hybrid
+    FC_TUNING_METRIC: int = field(default_factory=lambda: _flag("FC_TUNING_METRIC"))  # 0 latency, 1 TFLOP/s, 2 bandwidth
+    FC_TUNING_NUM_COLD_ITERATION: int = field(default_factory=lambda: _flag("FC_TUNING_NUM_COLD_ITERATION"))
+    FC_TUNING_NUM_REPEATS: int = field(default_factory=lambda: _flag("FC_TUNING_NUM_REPEATS"))
+    FC_TUNING_FLUSH_CACHE: bool = field(default_factory=lambda: _flag("FC_TUNING_FLUSH_CACHE"))
+    FC_TUNING_SEED: int = field(default_factory=lambda: _flag("FC_TUNING_SEED"))
+    # Re-time even if the cache has an entry.  The reference defaults both FC_FORCE_PROFILING and FC_FORCE_PROFILING_DB
+    # to true, which contradict each other; here a cached result is used unless FC_FORCE_PROFILING_DB is switched off.
+    FC_FORCE_PROFILING: bool = field(default_factory=lambda: not _flag("FC_FORCE_PROFILING_DB"))
+    FC_TUNING_DB_DIR: str = field(default_factory=lambda: _flag("FC_TUNING_DB_DIR"))
+    FC_CONFIG_JSON_PATH: str = field(default_factory=lambda: _flag("FC_CONFIG_JSON_PATH") or os.path.join(_HERE, "configs"))
 
 
 def expand_param(node: dict) -> List[int]:

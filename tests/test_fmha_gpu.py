@@ -68,6 +68,33 @@ def test_fmha_fwd_hdim128_many_tiles(dtype, sq, sk, mt):
     assert_lse_close(lse, lse_ref)
 
 
+@pytest.mark.parametrize("hq,hkv", [(4, 2), (8, 2), (3, 3)])
+@pytest.mark.parametrize("sq,sk,mask", [
+    (1000, 1000, (1, 256, 0)),    # causal sliding window: tiles left of the window are skipped
+    (1000, 1000, (2, 100, 0)),
+    (513, 1400, (2, 300, 0)),     # chunked prefill with a window, bottom-right aligned
+    (700, 700, (3, 200, 150)),    # two-sided window
+    (640, 640, (1, 0, 0)),        # only the diagonal
+    (300, 900, (1, 64, -1)),      # left window only, top-left aligned: the last rows see to the end
+    (900, 300, (2, 128, 0)),      # more queries than keys: the first rows see nothing
+    (257, 257, (1, -1, 100)),     # right window only
+])
+def test_fmha_fwd_hdim128_window_masks(hq, hkv, sq, sk, mask):
+    # window masks at hdim 128: the tcgen05 instance when the GQA ratio is even (or there is no left window), the
+    # general instance otherwise; both against the oracle
+    dtype = torch.bfloat16
+    b, d = 2, 128
+    q = normal_tensor((b, sq, hq, d), dtype, 11)
+    k = normal_tensor((b, sk, hkv, d), dtype, 12)
+    v = normal_tensor((b, sk, hkv, d), dtype, 13)
+    mt, wl, wr = mask
+    o_ref, lse_ref = oracle.fmha_fwd(q, k, v, mask_type=mt, window=(wl, wr))
+    o, lse = ops.fmha_fwd(_cu(q), _cu(k), _cu(v), window_size=(wl, wr), mask_type=mt, return_lse=True)
+    assert _lib.device_status() == 0
+    assert_o_close(o, o_ref)
+    assert_lse_close(lse, lse_ref)
+
+
 def test_fmha_fwd_instances_agree():
     # the tcgen05 instance and the general instance on the same problem
     from flashck_b200 import _lib

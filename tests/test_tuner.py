@@ -2,6 +2,8 @@
 SQLite cache round trip."""
 import os
 
+import pytest
+
 from flashck_b200 import tuner as T
 
 
@@ -23,7 +25,7 @@ def test_shipped_search_spaces_load():
 
 def test_tune_picks_best_and_caches(tmp_path):
     applied = []
-    cost = {0: 3.0, 2: 1.5, 3: 2.0}
+    cost = {0: 3.0, 3: 1.5}
     state = {"poly8": None, "timed": 0}
 
     def apply(fam, key, value):
@@ -39,15 +41,43 @@ def test_tune_picks_best_and_caches(tmp_path):
     tn = T.Tuner(flags=flags, db=T.ProfilingDB(os.path.join(str(tmp_path), "flash_ck.db")), timer=timer, apply=apply, env=env)
     problem = {"dtype": "bf16", "hq": 32, "hkv": 8, "d": 128, "mask": "causal", "mode": "group"}
     best = tn.tune("fmha_fwd", problem, run=lambda: None, flops=1e12)
-    assert best["instance"]["poly8"] == 2 and state["poly8"] == 2 and state["timed"] == 3
+    assert best["instance"]["poly8"] == 3 and state["poly8"] == 3 and state["timed"] == 2
     assert abs(best["tflops"] - 1e12 / 1.5 / 1e9) < 1e-6
     # second call: served from the cache, nothing is timed again, the winner is re-applied
     state["timed"] = 0
     again = tn.tune("fmha_fwd", problem, run=lambda: None, flops=1e12)
-    assert again["instance"] == best["instance"] and state["timed"] == 0 and state["poly8"] == 2
+    assert again["instance"] == best["instance"] and state["timed"] == 0 and state["poly8"] == 3
     # another problem is a cache miss; heuristic mode takes the first candidate without a sweep
     tn.flags.FC_TUNING_MODE = 0
     other = tn.tune("fmha_fwd", dict(problem, hq=64), run=lambda: None, flops=1e12)
     assert state["timed"] == 1 and other["instance"]["poly8"] == 0
     tn.db.flush()
     assert tn.db.query(env, tn.setting(), problem) is None
+
+
+def test_flag_api_has_the_reference_names_types_and_errors(capsys):
+    import flashck_b200 as fck
+    from flashck_b200.utils import flags
+    # defaults of core/utils/flags.cc, values as strings like the reference's binding returns them
+    assert fck.get_flag_value("FC_TUNING_NUM_REPEATS") == "64"
+    assert fck.get_flag_value("FC_TUNING_FLUSH_CACHE") == "true"
+    assert fck.get_flag_value("FC_TUNING_DB_DIR") == ""
+    try:
+        fck.set_flag_value("FC_TUNING_NUM_REPEATS", "8")
+        fck.set_flag_value("FC_TUNING_FLUSH_CACHE", "false")
+        assert flags.get_flag("FC_TUNING_NUM_REPEATS") == 8 and flags.get_flag("FC_TUNING_FLUSH_CACHE") is False
+        t = T.Tuner(timer=lambda run, cold, rep, flush: 1.0)
+        assert t.flags.FC_TUNING_NUM_REPEATS == 8 and t.flags.FC_TUNING_FLUSH_CACHE is False  # a new tuner sees them
+        with pytest.raises(RuntimeError):
+            fck.set_flag_value("FC_TUNING_NUM_REPEATS", "many")
+        with pytest.raises(RuntimeError):
+            fck.set_flag_value("FC_ROCM_PATH", "/opt/rocm")     # HIP build pipeline flag: not registered here
+        with pytest.raises(RuntimeError):
+            fck.get_flag_value("FC_NO_SUCH_FLAG")
+    finally:
+        fck.set_flag_value("FC_TUNING_NUM_REPEATS", "64")
+        fck.set_flag_value("FC_TUNING_FLUSH_CACHE", "true")
+    fck.print_flag_info("FC_TUNING_METRIC")
+    fck.print_all_flags()
+    out = capsys.readouterr().out
+    assert "FC_TUNING_METRIC (int) = 0" in out and "FC_CALL_STACK_LEVEL" in out
