@@ -399,7 +399,7 @@ def main():
         "roofline": {"bound": "tensor", "achieved": kernel_tflops, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
                      "frac": kernel_tflops / peaks["bf16_tflops"],
                      # DRAM bytes per launch from the ncu capture summarised in profiles/fmha_fwd_sm100_prefill_bf16.md
-                     "traffic": None if args.small else 1.352e9,
+                     "traffic": None if args.small else 1.406e9,
                      "algorithmic_bytes": 2.0 * w["total"] * (2 * HQ * D + 2 * HKV * D) + 4.0 * w["total"] * HQ,
                      "peak_source": peaks["source"] + " (burst bf16 GEMM)"},
         "e2e": {"value": e2e_val, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
