@@ -559,56 +559,72 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
             };
             // running counts give ring slots and barrier parities across work items
             uint32_t kv_cnt = 0, q_cnt = 0, sc0 = 0, sc1 = 0;
-            for (int rnd = 0; rnd < rounds; ++rnd) {
-                Item it;
-                get_item(ctrl, p, rnd, total_items, lane, it);
-                if (!it.valid || it.N == 0) continue;
-                bool ok = true;
-                if (lane == 0) {
-                    const int N = it.N, N0 = it.nt[0], N1 = it.nt[1];
-                    const int s0 = kv_cnt % KV_SLOTS;
-                    ok = mbar_wait_bounded(&ctrl->q_full, q_cnt & 1u, abort_flag, p.status, 0x40) &&
-                         mbar_wait_bounded(&ctrl->k_full[s0], (kv_cnt / KV_SLOTS) & 1u, abort_flag, p.status, 0x41);
-                    if (ok) {
-                        tc_fence_after();
-                        if (N0 > 0) { issue_qk(0, s0); umma_commit(&ctrl->s_full[0]); }
-                        if (N1 > 0) { issue_qk(1, s0); umma_commit(&ctrl->s_full[1]); }
-                        umma_commit(&ctrl->k_empty[s0]);
-                        if (N == 1) umma_commit(&ctrl->q_empty);  // Q may be replaced once these MMAs are done
-                    }
-                    for (int n = 0; ok && n < N; ++n) {
-                        const uint32_t kc = kv_cnt + n;
-                        const int s = kc % KV_SLOTS, s1 = (kc + 1) % KV_SLOTS;
-                        const uint32_t ph = (kc / KV_SLOTS) & 1u, ph1 = ((kc + 1) / KV_SLOTS) & 1u;
-                        if (!(ok = mbar_wait_bounded(&ctrl->v_full[s], ph, abort_flag, p.status, 0x42))) break;
-                        if (n < N0) {
-                            if (!(ok = mbar_wait_bounded(&ctrl->p_full[0], (sc0 + n) & 1u, abort_flag, p.status, 0x43))) break;
-                            tc_fence_after();
-                            issue_pv(0, s, n > 0);
-                            if (n == N0 - 1) umma_commit(&ctrl->o_full[0]);
-                        }
-                        if (n + 1 < N) {
-                            if (!(ok = mbar_wait_bounded(&ctrl->k_full[s1], ph1, abort_flag, p.status, 0x44))) break;
-                            tc_fence_after();
-                        }
-                        if (n + 1 < N0) { issue_qk(0, s1); umma_commit(&ctrl->s_full[0]); }
-                        if (n < N1) {
-                            if (!(ok = mbar_wait_bounded(&ctrl->p_full[1], (sc1 + n) & 1u, abort_flag, p.status, 0x45))) break;
-                            tc_fence_after();
-                            issue_pv(1, s, n > 0);
-                            if (n == N1 - 1) umma_commit(&ctrl->o_full[1]);
-                        }
-                        umma_commit(&ctrl->v_empty[s]);
-                        if (n + 1 < N1) { issue_qk(1, s1); umma_commit(&ctrl->s_full[1]); }
-                        if (n + 1 < N) umma_commit(&ctrl->k_empty[s1]);
-                        if (n + 2 == N) umma_commit(&ctrl->q_empty);  // the last QK^T of the item has been issued
-                    }
+            if (lane == 0) {  // the whole loop is one thread's; an item with N == 0 is skipped by every role
+                int N = 0, N0 = 0, N1 = 0;
+                if (rounds > 0) {
+                    Item it;
+                    get_item(ctrl, p, 0, total_items, lane, it);
+                    if (it.valid) { N = it.N; N0 = it.nt[0]; N1 = it.nt[1]; }
                 }
-                kv_cnt += it.N;
-                sc0 += it.nt[0];
-                sc1 += it.nt[1];
-                ++q_cnt;
-                if (!__shfl_sync(0xffffffffu, ok, 0)) break;
+                for (int rnd = 0; rnd < rounds; ++rnd) {
+                    bool ok = true;
+                    int nN = 0, nN0 = 0, nN1 = 0;
+                    if (N > 0) {
+                        const int s0 = kv_cnt % KV_SLOTS;
+                        ok = mbar_wait_bounded(&ctrl->q_full, q_cnt & 1u, abort_flag, p.status, 0x40) &&
+                             mbar_wait_bounded(&ctrl->k_full[s0], (kv_cnt / KV_SLOTS) & 1u, abort_flag, p.status, 0x41);
+                        if (ok) {
+                            tc_fence_after();
+                            if (N0 > 0) { issue_qk(0, s0); umma_commit(&ctrl->s_full[0]); }
+                            if (N1 > 0) { issue_qk(1, s0); umma_commit(&ctrl->s_full[1]); }
+                            umma_commit(&ctrl->k_empty[s0]);
+                            if (N == 1) umma_commit(&ctrl->q_empty);  // Q may be replaced once these MMAs are done
+                        }
+                        // the step counts of the next item, worked out while the first softmax of this one runs
+                        if (rnd + 1 < rounds) {
+                            Item nx;
+                            get_item(ctrl, p, rnd + 1, total_items, lane, nx);
+                            if (nx.valid) { nN = nx.N; nN0 = nx.nt[0]; nN1 = nx.nt[1]; }
+                        }
+                        for (int n = 0; ok && n < N; ++n) {
+                            const uint32_t kc = kv_cnt + n;
+                            const int s = kc % KV_SLOTS, s1 = (kc + 1) % KV_SLOTS;
+                            const uint32_t ph = (kc / KV_SLOTS) & 1u, ph1 = ((kc + 1) / KV_SLOTS) & 1u;
+                            if (!(ok = mbar_wait_bounded(&ctrl->v_full[s], ph, abort_flag, p.status, 0x42))) break;
+                            if (n < N0) {
+                                if (!(ok = mbar_wait_bounded(&ctrl->p_full[0], (sc0 + n) & 1u, abort_flag, p.status, 0x43))) break;
+                                tc_fence_after();
+                                issue_pv(0, s, n > 0);
+                                if (n == N0 - 1) umma_commit(&ctrl->o_full[0]);
+                            }
+                            if (n + 1 < N) {
+                                if (!(ok = mbar_wait_bounded(&ctrl->k_full[s1], ph1, abort_flag, p.status, 0x44))) break;
+                                tc_fence_after();
+                            }
+                            if (n + 1 < N0) { issue_qk(0, s1); umma_commit(&ctrl->s_full[0]); }
+                            if (n < N1) {
+                                if (!(ok = mbar_wait_bounded(&ctrl->p_full[1], (sc1 + n) & 1u, abort_flag, p.status, 0x45))) break;
+                                tc_fence_after();
+                                issue_pv(1, s, n > 0);
+                                if (n == N1 - 1) umma_commit(&ctrl->o_full[1]);
+                            }
+                            umma_commit(&ctrl->v_empty[s]);
+                            if (n + 1 < N1) { issue_qk(1, s1); umma_commit(&ctrl->s_full[1]); }
+                            if (n + 1 < N) umma_commit(&ctrl->k_empty[s1]);
+                            if (n + 2 == N) umma_commit(&ctrl->q_empty);  // the last QK^T of the item has been issued
+                        }
+                        kv_cnt += N;
+                        sc0 += N0;
+                        sc1 += N1;
+                        ++q_cnt;
+                    } else if (rnd + 1 < rounds) {
+                        Item nx;
+                        get_item(ctrl, p, rnd + 1, total_items, lane, nx);
+                        if (nx.valid) { nN = nx.N; nN0 = nx.nt[0]; nN1 = nx.nt[1]; }
+                    }
+                    if (!ok) break;
+                    N = nN; N0 = nN0; N1 = nN1;
+                }
             }
         }
     } else {
