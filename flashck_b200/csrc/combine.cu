@@ -77,20 +77,37 @@ __global__ void __launch_bounds__(128) combine_kernel(const CombineDev p) {
     acc[0] = make_float4(0.f, 0.f, 0.f, 0.f);
     acc[1] = acc[0];
     const float* obase = p.o_acc + b * p.ob + h * p.oh + r * p.orr;
-    for (int s = 0; s < S; ++s) {
-        const float ls = lrow[s * p.ls];
-        if (ls == ninf) continue;  // empty split: its o_acc slot is never read
-        const float w = expf(ls - m) * inv;
-        const float4* src = reinterpret_cast<const float4*>(obase + s * p.os);
+    const bool c0 = lane < nvec, c1 = lane + 32 < nvec;
+    // Lane s of a group of 32 splits holds that split's weight, so the row loop below has no load on its way to the
+    // next address: four splits' rows are fetched together.  A weight of zero marks an empty split (LSE = -inf),
+    // whose o_acc slot is never read -- it may hold anything.
+    for (int s0 = 0; s0 < S; s0 += 32) {
+        float wl = 0.f;
+        if (s0 + lane < S) {
+            const float ls = lrow[(s0 + lane) * p.ls];
+            wl = (ls == ninf) ? 0.f : expf(ls - m) * inv;
+        }
+        const int cnt = min(32, S - s0);
+        for (int j0 = 0; j0 < cnt; j0 += 4) {
+            float w[4];
+            float4 x[4][2];
 #pragma unroll
-        for (int j = 0; j < 2; ++j) {
-            const int c = lane + 32 * j;
-            if (c < nvec) {
-                const float4 x = src[c];
-                acc[j].x += w * x.x;
-                acc[j].y += w * x.y;
-                acc[j].z += w * x.z;
-                acc[j].w += w * x.w;
+            for (int u = 0; u < 4; ++u) {
+                w[u] = __shfl_sync(0xffffffffu, wl, (j0 + u) & 31);
+                if (j0 + u >= cnt) w[u] = 0.f;
+                const float4* src = reinterpret_cast<const float4*>(obase + (int64_t)(s0 + j0 + u) * p.os);
+                x[u][0] = (w[u] != 0.f && c0) ? src[lane] : make_float4(0.f, 0.f, 0.f, 0.f);
+                x[u][1] = (w[u] != 0.f && c1) ? src[lane + 32] : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    acc[j].x += w[u] * x[u][j].x;
+                    acc[j].y += w[u] * x[u][j].y;
+                    acc[j].z += w[u] * x[u][j].z;
+                    acc[j].w += w[u] * x[u][j].w;
+                }
             }
         }
     }
