@@ -237,6 +237,7 @@ int FmhaFwdSplitKV(void* q, void* k, void* v, void* bias, void* lse_acc, void* o
     }
     p.scale = resolve_scale(scale, d);
     p.mask_type = (int)mask_type; p.wl = window_left; p.wr = window_right; p.dtype = dtype;
+    if (splitkv_sm100_supported(p)) return launch_splitkv_sm100(p, (cudaStream_t)stream);
     return launch_splitkv_decode(p, (cudaStream_t)stream);
 }
 

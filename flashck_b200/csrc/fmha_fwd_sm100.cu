@@ -47,7 +47,8 @@ constexpr int NTHREADS = 384;
 constexpr float kRescaleThreshold = 8.f;  // log2 units
 
 std::atomic<int64_t> g_use_sm100{1};
-std::atomic<int64_t> g_poly8{0};  // column pairs of every 8 whose exp2 runs on the FMA pipe (0, 2, 3 or 4)
+std::atomic<int64_t> g_poly8{0};  // 3: three of every 8 column pairs take the exp2 polynomial on the FMA pipe; 0: none
+std::atomic<int64_t> g_use_sm100_splitkv{1};  // multi-token split-KV on the tcgen05 instance
 
 struct Sm100Dev {
     void* o;
@@ -65,6 +66,12 @@ struct Sm100Dev {
     const int32_t* seqlen_k32;
     const int64_t* cache_batch_idx;
     int page, bt_stride;
+    // split mode (FmhaFwdSplitKV with several query rows per kv head): work item = (sequence, kv head, piece of
+    // `piece_tiles` key tiles); its Q tile holds the (token, group head) rows of that kv head; the result is split
+    // `piece` of the caller's fp32 workspaces
+    float* o_acc;
+    float* lse_acc;
+    int num_splits, piece_tiles, group, sq_cap;
     int causal;       // mask type: 0 none, 1 top-left, 2 bottom-right, 3 window with top-left alignment
     int wl, wr;       // window of a masked problem: keys [i + shift - wl, i + shift + wr] of row i; -1 = unbounded
     int num_levels;   // row blocks of the longest sequence (128 rows when heads are paired, else 256)
@@ -226,6 +233,53 @@ __device__ __forceinline__ int item_of_round(int rnd, int cta, int g) {
 // Work items are ordered by decreasing row-block index (under a causal mask: decreasing cost), then by sequence,
 // then by head, so that the q heads of a GQA group -- which read the same K/V -- run at the same time on
 // neighbouring SMs and share those tiles through L2.  Warp-collective.
+// Split mode: items are numbered sequence by sequence (level_start holds the prefix), inside a sequence piece by
+// piece, then kv head, then 128-row block of the packed (token, group head) rows.
+__device__ __forceinline__ uint32_t find_item_split(const Ctrl* ctrl, const Sm100Dev& p, int w) {
+    int lo = 0, hi = p.batch;  // last sequence whose first item is <= w
+    while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (ctrl->level_start[mid] <= w) lo = mid; else hi = mid;
+    }
+    const int b = lo;
+    const int rb_cnt = (ctrl->seq_sq[b] * p.group + BM - 1) / BM;
+    const int per_piece = p.hkv * rb_cnt;
+    const int rem = w - ctrl->level_start[b];
+    const int piece = rem / per_piece, r2 = rem - piece * per_piece;
+    const int kh = r2 / rb_cnt, rb = r2 - kh * rb_cnt;
+    return 0x80000000u | ((uint32_t)b << 22) | ((uint32_t)kh << 12) | ((uint32_t)piece << 4) | (uint32_t)rb;
+}
+
+__device__ __forceinline__ void expand_item_split(const Ctrl* ctrl, const Sm100Dev& p, uint32_t packed, Item& it) {
+    it.valid = packed >> 31;
+    const int b = (packed >> 22) & 0x1ff, kh = (packed >> 12) & 0x3ff, piece = (packed >> 4) & 0xff, rb = packed & 0xf;
+    it.b = b;
+    it.q0 = ctrl->seq_q0[b];
+    it.sq = ctrl->seq_sq[b];
+    it.k0 = ctrl->seq_k0[b];
+    it.sk = ctrl->seq_sk[b];
+    it.kh = kh;
+    it.h[0] = kh * p.group;  // first q head of the group
+    it.h[1] = piece;         // split slot of the result
+    it.row0[0] = rb * BM;    // first packed row (token * group + group head)
+    it.row0[1] = 0x3fffffff; // tile 1 does not exist
+    it.shift = (p.causal == 2) ? it.sk - it.sq : 0;
+    it.n0 = piece * p.piece_tiles;
+    int n = 0;
+    const int first_tok = it.row0[0] / p.group;
+    if (first_tok < it.sq && it.sk > 0) {
+        int hi_key = it.sk - 1;
+        if (p.causal) {
+            const int last_tok = min(it.sq, (it.row0[0] + BM + p.group - 1) / p.group) - 1;
+            hi_key = min(hi_key, last_tok + it.shift);
+        }
+        if (hi_key >= 0) n = max(0, min(it.n0 + p.piece_tiles, hi_key / BN + 1) - it.n0);
+    }
+    it.nt[0] = n;
+    it.nt[1] = 0;
+    it.N = n;
+}
+
 __device__ __forceinline__ uint32_t find_item(const Ctrl* ctrl, const Sm100Dev& p, int w, int lane) {
     int lo = 0, hi = ctrl->num_levels;  // last level whose start is <= w
     while (hi - lo > 1) {
@@ -297,13 +351,16 @@ __device__ __forceinline__ void expand_item(const Ctrl* ctrl, const Sm100Dev& p,
 }
 
 // The work item of round `rnd` of this CTA, from the table filled at start-up.
+template <bool SPLIT = false>
 __device__ __forceinline__ void get_item(const Ctrl* ctrl, const Sm100Dev& p, int rnd, int total_items, int lane, Item& it) {
-    expand_item(ctrl, p, ctrl->items[rnd], it);
+    if (SPLIT) expand_item_split(ctrl, p, ctrl->items[rnd], it);
+    else expand_item(ctrl, p, ctrl->items[rnd], it);
 }
 
 // WINDOW: the mask has a left window or a right window other than 0 (everything but no mask / causal); a separate
 // instance, so that the common masks do not carry the second bound of the visible range through the softmax loop.
-template <typename T, int NPOLY8, bool WINDOW>
+// SPLIT: the split-KV form described at Sm100Dev (one Q tile per item, tile 1 unused).
+template <typename T, int NPOLY8, bool WINDOW, bool SPLIT>
 __global__ void __launch_bounds__(NTHREADS, 1)
 fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                       const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_o,
@@ -361,7 +418,8 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                 k0 = pb;
                 sk = pe > pb ? (pe - pb - 1) * p.page + p.kv_last_page_len[b] : 0;
             } else {
-                k0 = (p.cache_batch_idx ? p.cache_batch_idx[b] : (int64_t)b) * p.bt_stride;
+                // block table row, or (no page list) the first token row of a contiguous cache [rows, seqlen_k, hkv, d]
+                k0 = (p.cache_batch_idx ? p.cache_batch_idx[b] : (int64_t)b) * (p.page_ids ? p.bt_stride : p.seqlen_k);
                 sk = p.seqlen_k32 ? p.seqlen_k32[b] : p.seqlen_k;
             }
         } else {
@@ -373,16 +431,47 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         ctrl->seq_k0[b] = (int)k0;
         ctrl->seq_sk[b] = sk;
         const int rows_per_block = p.pair_heads ? BM : 2 * BM;
-        ctrl->nblk[b] = min(p.num_levels, (sq + rows_per_block - 1) / rows_per_block);
+        if (SPLIT) {  // pieces = splits in use; more than the workspace has means a length beyond the stated capacity
+            int pieces = ((sk + BN - 1) / BN + p.piece_tiles - 1) / p.piece_tiles;
+            if (pieces > p.num_splits) {
+                pieces = p.num_splits;
+                atomicOr(p.status, 0x10000000);
+            }
+            ctrl->nblk[b] = pieces;
+        }
+        else ctrl->nblk[b] = min(p.num_levels, (sq + rows_per_block - 1) / rows_per_block);
     }
     __syncthreads();
-    for (int lv = threadIdx.x; lv < p.num_levels; lv += NTHREADS) {  // count of sequences that have block index lv
+    if (SPLIT) {
+        if (threadIdx.x == 0) {  // first item of every sequence
+            int run = 0;
+            for (int b = 0; b < p.batch; ++b) {
+                ctrl->level_start[b] = run;
+                run += ctrl->nblk[b] * p.hkv * ((ctrl->seq_sq[b] * p.group + BM - 1) / BM);
+            }
+            ctrl->level_start[p.batch] = run;
+        }
+        // splits a sequence does not use: LSE = -inf, so that the merge gives them no weight
+        if (p.lse_acc) {
+            for (int b = blockIdx.x; b < p.batch; b += gridDim.x) {
+                const int used = ctrl->nblk[b], sq = ctrl->seq_sq[b], q0 = ctrl->seq_q0[b];
+                const int cnt = (p.num_splits - used) * p.hq * sq;
+                for (int e = threadIdx.x; e < cnt; e += NTHREADS) {
+                    const int s = used + e / (p.hq * sq), rem = e % (p.hq * sq), h = rem / sq, i = rem - h * sq;
+                    const int64_t slot = p.seqstart_q ? ((int64_t)h * p.num_splits + s) * p.total_q + q0 + i
+                                                      : (((int64_t)b * p.hq + h) * p.num_splits + s) * p.sq_cap + i;
+                    p.lse_acc[slot] = -INFINITY;
+                }
+            }
+        }
+    }
+    for (int lv = threadIdx.x; !SPLIT && lv < p.num_levels; lv += NTHREADS) {  // count of sequences that have block index lv
         int c = 0;
         for (int b = 0; b < p.batch; ++b) c += ctrl->nblk[b] > lv;
         ctrl->level_start[p.num_levels - lv] = c * (p.pair_heads ? p.hq / 2 : p.hq);  // summed up below
     }
     __syncthreads();
-    if (threadIdx.x == 0) {
+    if (!SPLIT && threadIdx.x == 0) {
         int run = 0;
         ctrl->level_start[0] = 0;
         for (int lv = 1; lv <= p.num_levels; ++lv) {
@@ -394,7 +483,7 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = ctrl->tmem_base;
-    const int total_items = ctrl->level_start[p.num_levels];
+    const int total_items = SPLIT ? ctrl->level_start[p.batch] : ctrl->level_start[p.num_levels];
     int rounds = (total_items + (int)gridDim.x - 1) / (int)gridDim.x;
     if (rounds > kMaxRounds) {  // the host checks an upper bound of this; never silently drop work
         if (threadIdx.x == 0) atomicOr(p.status, 0x20000000);
@@ -402,7 +491,7 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     }
     for (int rnd = warp; rnd < rounds; rnd += NTHREADS / 32) {  // this CTA's work list
         const int w = item_of_round(rnd, blockIdx.x, gridDim.x);
-        const uint32_t packed = w < total_items ? find_item(ctrl, p, w, lane) : 0u;
+        const uint32_t packed = w >= total_items ? 0u : (SPLIT ? find_item_split(ctrl, p, w) : find_item(ctrl, p, w, lane));
         if (lane == 0) ctrl->items[rnd] = packed;
     }
     __syncthreads();
@@ -430,12 +519,18 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
             const int chunks = BN / chunk;
             for (int rnd = 0; rnd < rounds; ++rnd) {
                 Item it;
-                get_item(ctrl, p, rnd, total_items, lane, it);
+                get_item<SPLIT>(ctrl, p, rnd, total_items, lane, it);
                 if (!it.valid || it.N == 0) continue;
                 bool ok = true;
                 if (lane == 0) {
                     ok = mbar_wait_bounded(&ctrl->q_empty, (q_cnt & 1u) ^ 1u, abort_flag, p.status, 0x08);
-                    if (ok) {
+                    if (ok && SPLIT) {
+                        // one box of (64 columns, group heads, 128/group tokens) per half: the rows land in
+                        // (token, group head) order
+                        mbar_expect_tx(&ctrl->q_full, TILE_BYTES);
+                        for (int hb = 0; hb < 2; ++hb)
+                            tma_load_4d(sQ + hb * HALF_BYTES, &map_q, &ctrl->q_full, hb * 64, 0, it.kh, it.q0 + it.row0[0] / p.group);
+                    } else if (ok) {
                         const int q_tiles = (it.row0[1] < it.sq) ? 2 : 1;
                         mbar_expect_tx(&ctrl->q_full, q_tiles * TILE_BYTES);
                         for (int hb = 0; hb < 2; ++hb)
@@ -474,7 +569,8 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                     if (lane < chunks && n < it.N) {
                         const int key0 = (it.n0 + n) * BN + lane * chunk;
                         valid = max(0, min(chunk, it.sk - key0));
-                        if (valid > 0) row = p.page_ids[it.k0 + key0 / p.page] * p.page + key0 % p.page;
+                        if (valid > 0)  // no page list: a contiguous cache read in 128-token chunks
+                            row = p.page_ids ? p.page_ids[it.k0 + key0 / p.page] * p.page + key0 % p.page : it.k0 + key0;
                     }
                 };
                 int my_row = 0, my_valid = 0;
@@ -563,7 +659,7 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                 int N = 0, N0 = 0, N1 = 0;
                 if (rounds > 0) {
                     Item it;
-                    get_item(ctrl, p, 0, total_items, lane, it);
+                    get_item<SPLIT>(ctrl, p, 0, total_items, lane, it);
                     if (it.valid) { N = it.N; N0 = it.nt[0]; N1 = it.nt[1]; }
                 }
                 for (int rnd = 0; rnd < rounds; ++rnd) {
@@ -583,7 +679,7 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                         // the step counts of the next item, worked out while the first softmax of this one runs
                         if (rnd + 1 < rounds) {
                             Item nx;
-                            get_item(ctrl, p, rnd + 1, total_items, lane, nx);
+                            get_item<SPLIT>(ctrl, p, rnd + 1, total_items, lane, nx);
                             if (nx.valid) { nN = nx.N; nN0 = nx.nt[0]; nN1 = nx.nt[1]; }
                         }
                         for (int n = 0; ok && n < N; ++n) {
@@ -619,7 +715,7 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                         ++q_cnt;
                     } else if (rnd + 1 < rounds) {
                         Item nx;
-                        get_item(ctrl, p, rnd + 1, total_items, lane, nx);
+                        get_item<SPLIT>(ctrl, p, rnd + 1, total_items, lane, nx);
                         if (nx.valid) { nN = nx.N; nN0 = nx.nt[0]; nN1 = nx.nt[1]; }
                     }
                     if (!ok) break;
@@ -638,13 +734,18 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         bool ok = true;
         for (int rnd = 0; ok && rnd < rounds; ++rnd) {
             Item it;
-            get_item(ctrl, p, rnd, total_items, lane, it);
+            get_item<SPLIT>(ctrl, p, rnd, total_items, lane, it);
             if (!it.valid) continue;
-            const int Ni = i ? it.nt[1] : it.nt[0], head = i ? it.h[1] : it.h[0];
+            const int Ni = i ? it.nt[1] : it.nt[0];
+            int head = i ? it.h[1] : it.h[0];
             const int sq = it.sq, sk = it.sk, shift = it.shift;
-            const int tile_first_row = i ? it.row0[1] : it.row0[0];
-            const int row = tile_first_row + r;      // row inside the sequence
+            // split mode packs (token, group head) into the rows; `row` is the query token either way
+            const int packed_first = i ? it.row0[1] : it.row0[0];
+            const int group = SPLIT ? p.group : 1;
+            const int tile_first_row = SPLIT ? packed_first / group : packed_first;
+            const int row = SPLIT ? (packed_first + r) / group : packed_first + r;      // row inside the sequence
             const bool row_ok = row < sq;
+            if (SPLIT) head += (packed_first + r) - row * group;
             // visible keys of this row: [first_key, limit]
             const int wr = WINDOW ? p.wr : 0, wl = WINDOW ? p.wl : -1;
             const int limit = (p.causal && wr >= 0) ? min(sk - 1, row + shift + wr) : sk - 1;
@@ -745,7 +846,36 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                 ++oc;
                 tc_fence_after();
             }
-            if (tile_first_row < sq) {
+            if (SPLIT) {
+                // fp32 partial of this split, normalised inside the split, and its LSE (natural log)
+                if (i == 0 && tile_first_row < sq) {
+                    const float inv = l > 0.f ? 1.f / l : 0.f;
+                    const int64_t slot = p.seqstart_q
+                        ? ((int64_t)head * p.num_splits + it.h[1]) * p.total_q + it.q0 + row
+                        : (((int64_t)it.b * p.hq + head) * p.num_splits + it.h[1]) * p.sq_cap + row;
+                    float* orow = p.o_acc + slot * HD;
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        uint32_t t[32];
+                        if (Ni > 0) {
+                            tmem_ld32(tO + c * 32, t);
+                            tmem_wait_ld();
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) t[j] = 0u;
+                        }
+                        if (row_ok) {
+#pragma unroll
+                            for (int v4 = 0; v4 < 8; ++v4)
+                                *reinterpret_cast<float4*>(orow + c * 32 + v4 * 4) =
+                                    make_float4(__uint_as_float(t[v4 * 4 + 0]) * inv, __uint_as_float(t[v4 * 4 + 1]) * inv,
+                                                __uint_as_float(t[v4 * 4 + 2]) * inv, __uint_as_float(t[v4 * 4 + 3]) * inv);
+                        }
+                    }
+                    if (p.lse_acc && row_ok)
+                        p.lse_acc[slot] = l > 0.f ? (m_used + log2f(l)) * 0.6931471805599453f : -INFINITY;
+                }
+            } else if (tile_first_row < sq) {
                 const float inv = l > 0.f ? 1.f / l : 0.f;
                 // Whole tiles leave through shared memory and TMA stores (32 rows x 32 columns per warp and store), which
                 // keeps the load/store unit free for the other warps; a tile that reaches past the end of its sequence
@@ -841,7 +971,7 @@ int make_map_o(CUtensorMap* map, const void* base, int dtype, int64_t rows, int6
     return FLASHCK_OK;
 }
 
-template <typename T, int NPOLY8, bool WINDOW>
+template <typename T, int NPOLY8, bool WINDOW, bool SPLIT>
 int launch_t(const FwdParams& p, const Sm100Dev& dev, cudaStream_t stream) {
     const int64_t rows_q = p.seqstart_q ? p.total_q : p.batch * p.seqlen_q;
     const bool paged = p.block_table || p.kv_indptr;
@@ -856,7 +986,7 @@ int launch_t(const FwdParams& p, const Sm100Dev& dev, cudaStream_t stream) {
     if ((rc = make_map_3d(&mk, p.k, p.dtype, rows_k, p.hkv, box_k))) return rc;
     if ((rc = make_map_3d(&mv, p.v, p.dtype, rows_k, p.hkv, box_k))) return rc;
     if ((rc = make_map_o(&mo, p.o, p.dtype, rows_q, p.hq))) return rc;
-    auto kern = fmha_fwd_sm100_kernel<T, NPOLY8, WINDOW>;
+    auto kern = fmha_fwd_sm100_kernel<T, NPOLY8, WINDOW, SPLIT>;
     const size_t smem = 1024 + (size_t)(2 + 2 * KV_SLOTS) * TILE_BYTES + 8 * STAGE_BYTES + sizeof(Ctrl);
     static thread_local int configured_device = -1;
     int devid = 0;
@@ -927,15 +1057,119 @@ int launch_fwd_sm100(const FwdParams& p, cudaStream_t stream) {
     const bool window = p.mask_type != 0 && !(p.wl < 0 && p.wr == 0);
     const bool poly = g_poly8.load() != 0;
     if (window) {
-        if (poly) return bf16 ? launch_t<__nv_bfloat16, 3, true>(p, dev, stream) : launch_t<__half, 3, true>(p, dev, stream);
-        return bf16 ? launch_t<__nv_bfloat16, 0, true>(p, dev, stream) : launch_t<__half, 0, true>(p, dev, stream);
+        if (poly) return bf16 ? launch_t<__nv_bfloat16, 3, true, false>(p, dev, stream) : launch_t<__half, 3, true, false>(p, dev, stream);
+        return bf16 ? launch_t<__nv_bfloat16, 0, true, false>(p, dev, stream) : launch_t<__half, 0, true, false>(p, dev, stream);
     }
-    if (poly) return bf16 ? launch_t<__nv_bfloat16, 3, false>(p, dev, stream) : launch_t<__half, 3, false>(p, dev, stream);
-    return bf16 ? launch_t<__nv_bfloat16, 0, false>(p, dev, stream) : launch_t<__half, 0, false>(p, dev, stream);
+    if (poly) return bf16 ? launch_t<__nv_bfloat16, 3, false, false>(p, dev, stream) : launch_t<__half, 3, false, false>(p, dev, stream);
+    return bf16 ? launch_t<__nv_bfloat16, 0, false, false>(p, dev, stream) : launch_t<__half, 0, false, false>(p, dev, stream);
+}
+
+// ---- split-KV with several query rows per kv head (append + decode, speculative decoding, chunked prefill) ----
+namespace {
+
+constexpr int kMinPieceTiles = 8;  // at least 1024 keys per work item
+
+// Q [tokens, hkv, group, 128] as boxes of (64 columns, group heads, 1 kv head, 128/group tokens).
+int make_map_q_packed(CUtensorMap* map, const void* base, int dtype, int64_t tokens, int64_t hkv, int64_t group) {
+    PFN_encodeTiled enc = get_encode_tiled();
+    FCK_REQUIRE(enc != nullptr, FLASHCK_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    const cuuint64_t dims[4] = {(cuuint64_t)HD, (cuuint64_t)group, (cuuint64_t)hkv, (cuuint64_t)(tokens > 0 ? tokens : 1)};
+    const cuuint64_t strides[3] = {(cuuint64_t)(HD * 2), (cuuint64_t)(group * HD * 2), (cuuint64_t)(hkv * group * HD * 2)};
+    const cuuint32_t box[4] = {64, (cuuint32_t)group, 1, (cuuint32_t)(BM / group)};
+    const cuuint32_t estr[4] = {1, 1, 1, 1};
+    const CUtensorMapDataType dt =
+        dtype == FLASHCK_DTYPE_BFLOAT16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    const CUresult r = enc(map, dt, 4, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    FCK_REQUIRE(r == CUDA_SUCCESS, FLASHCK_ERR_CUDA, "cuTensorMapEncodeTiled (packed Q) failed (%d)", (int)r);
+    return FLASHCK_OK;
+}
+
+int64_t split_cap_tiles(const SplitKVParams& p) {  // key tiles of the longest sequence the cache can hold
+    const int64_t cap = p.block_table ? p.bt_stride * p.page : p.seqlen_k_cap;
+    return (cap + BN - 1) / BN;
+}
+
+template <typename T>
+int launch_split_t(const SplitKVParams& p, const Sm100Dev& dev, cudaStream_t stream) {
+    const int64_t tokens = p.seqstart_q ? p.total_q : p.batch * p.seqlen_q;
+    const int box_k = p.block_table ? (int)std::min<int64_t>(p.page, BN) : BN;
+    CUtensorMap mq, mk, mv;
+    int rc;
+    if ((rc = make_map_q_packed(&mq, p.q, p.dtype, tokens, p.hkv, p.hq / p.hkv))) return rc;
+    if ((rc = make_map_3d(&mk, p.k, p.dtype, 0x7fffff00ll, p.hkv, box_k))) return rc;  // cache rows are trusted
+    if ((rc = make_map_3d(&mv, p.v, p.dtype, 0x7fffff00ll, p.hkv, box_k))) return rc;
+    auto kern = fmha_fwd_sm100_kernel<T, 0, false, true>;
+    const size_t smem = 1024 + (size_t)(2 + 2 * KV_SLOTS) * TILE_BYTES + 8 * STAGE_BYTES + sizeof(Ctrl);
+    static thread_local int configured_device = -1;
+    int devid = 0;
+    FCK_CUDA(cudaGetDevice(&devid));
+    if (configured_device != devid) {
+        FCK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        configured_device = devid;
+    }
+    kern<<<sm_count(), NTHREADS, smem, stream>>>(mq, mk, mv, mq, dev);
+    FCK_CUDA(cudaGetLastError());
+    return FLASHCK_OK;
+}
+
+}  // namespace
+
+bool splitkv_sm100_supported(const SplitKVParams& p) {
+    if (!g_use_sm100_splitkv.load()) return false;
+    if (p.d != HD || p.dv != HD || p.batch <= 0 || p.batch > kMaxBatch || p.hq > 1023) return false;
+    const int64_t group = p.hq / p.hkv;
+    if (group > BM || BM % group != 0) return false;
+    // one 16-row tile of (token, group head) rows is what the mma.sync decode kernel serves at the HBM rate
+    if (p.max_seqlen_q * group <= 16) return false;
+    if ((p.max_seqlen_q * group + BM - 1) / BM > 16) return false;
+    if (p.seqstart_k) return false;                           // paged or [rows, seqlen_k, hkv, d] caches
+    if (p.mask_type > 2 || (p.mask_type != 0 && !(p.wl < 0 && p.wr == 0))) return false;  // none or causal
+    if (p.block_table) {
+        if (p.page < 16 || !((BN % p.page == 0) || (p.page % BN == 0)) || p.cache_batch_idx) return false;
+    } else if (p.seqlen_k_cap <= 0) {
+        return false;
+    }
+    if (p.num_splits > 1 && !p.lse_acc) return false;
+    const int64_t cap_tiles = split_cap_tiles(p);
+    const int64_t piece = std::max<int64_t>(kMinPieceTiles, (cap_tiles + p.num_splits - 1) / p.num_splits);
+    if ((cap_tiles + piece - 1) / piece > 255) return false;
+    const int64_t items = p.batch * p.hkv * ((p.max_seqlen_q * group + BM - 1) / BM) * ((cap_tiles + piece - 1) / piece);
+    if ((items + sm_count() - 1) / sm_count() > kMaxRounds) return false;
+    const int64_t tokens = p.seqstart_q ? p.total_q : p.batch * p.seqlen_q;
+    if (tokens >= (1ll << 31) || (!p.block_table && p.batch * p.seqlen_k_cap >= (1ll << 31))) return false;
+    return true;
+}
+
+int launch_splitkv_sm100(const SplitKVParams& p, cudaStream_t stream) {
+    int* status = device_status_ptr();
+    if (!status) return FLASHCK_ERR_CUDA;
+    if (p.batch == 0 || p.max_seqlen_q == 0) return FLASHCK_OK;
+    Sm100Dev dev{};
+    dev.o = nullptr; dev.lse = nullptr; dev.seqstart_q = p.seqstart_q; dev.seqstart_k = nullptr; dev.status = status;
+    dev.batch = (int)p.batch; dev.seqlen_q = (int)p.seqlen_q; dev.seqlen_k = (int)p.seqlen_k_cap;
+    dev.hq = (int)p.hq; dev.hkv = (int)p.hkv; dev.total_q = (int)p.total_q;
+    dev.v = p.v;
+    dev.page_ids = p.block_table; dev.seqlen_k32 = p.seqlen_k; dev.cache_batch_idx = p.cache_batch_idx;
+    // a contiguous cache goes through the chunked loader too (chunk = 128 tokens): the rows behind a sequence's end
+    // are uninitialised cache, which the loader keeps out of V
+    dev.page = p.block_table ? (int)p.page : BN;
+    dev.bt_stride = (int)p.bt_stride;
+    dev.o_acc = p.o_acc; dev.lse_acc = p.lse_acc; dev.num_splits = (int)p.num_splits;
+    const int64_t cap_tiles = split_cap_tiles(p);
+    dev.piece_tiles = (int)std::max<int64_t>(kMinPieceTiles, (cap_tiles + p.num_splits - 1) / p.num_splits);
+    dev.group = (int)(p.hq / p.hkv);
+    dev.sq_cap = (int)p.seqlen_q;
+    dev.causal = p.mask_type; dev.wl = -1; dev.wr = p.mask_type ? 0 : -1;
+    dev.pair_heads = 0; dev.num_levels = 1;
+    dev.scale_log2 = p.scale * 1.4426950408889634f;
+    return p.dtype == FLASHCK_DTYPE_BFLOAT16 ? launch_split_t<__nv_bfloat16>(p, dev, stream)
+                                              : launch_split_t<__half>(p, dev, stream);
 }
 
 int fwd_set_param(const char* key, int64_t value) {
     if (!strcmp(key, "use_sm100")) { g_use_sm100 = value; return FLASHCK_OK; }
+    if (!strcmp(key, "use_sm100_splitkv")) { g_use_sm100_splitkv = value; return FLASHCK_OK; }
     if (!strcmp(key, "poly8")) {
         if (value != 0 && value != 3) return FLASHCK_ERR_INVALID_ARGUMENT;  // 3 of every 8 column pairs, or none
         g_poly8 = value;
@@ -945,6 +1179,7 @@ int fwd_set_param(const char* key, int64_t value) {
 }
 int fwd_get_param(const char* key, int64_t* value) {
     if (!strcmp(key, "use_sm100")) { *value = g_use_sm100; return FLASHCK_OK; }
+    if (!strcmp(key, "use_sm100_splitkv")) { *value = g_use_sm100_splitkv; return FLASHCK_OK; }
     if (!strcmp(key, "poly8")) { *value = g_poly8; return FLASHCK_OK; }
     return FLASHCK_ERR_INVALID_ARGUMENT;
 }

@@ -96,6 +96,9 @@ int launch_fwd_generic(const FwdParams& p, cudaStream_t stream);
 // ---- tcgen05 prefill (fmha_fwd_sm100.cu): hdim 128, contiguous or paged K/V ------------------------------
 bool fwd_sm100_supported(const FwdParams& p);
 int launch_fwd_sm100(const FwdParams& p, cudaStream_t stream);
+// the same kernel as a split-KV backend for several query rows per kv head (partials into the caller's workspaces)
+bool splitkv_sm100_supported(const SplitKVParams& p);
+int launch_splitkv_sm100(const SplitKVParams& p, cudaStream_t stream);
 int fwd_set_param(const char* key, int64_t value);
 int fwd_get_param(const char* key, int64_t* value);
 

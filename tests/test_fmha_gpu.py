@@ -339,6 +339,65 @@ def test_splitkv_multi_token_queries_causal_and_window():
         assert_lse_close(lse, lse_ref)
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("page,hq,hkv", [(16, 32, 8), (64, 16, 2), (128, 8, 8), (256, 8, 1)])
+@pytest.mark.parametrize("num_splits", [1, 3, 16])
+def test_splitkv_many_query_rows_tcgen05_instance(dtype, page, hq, hkv, num_splits):
+    """More than 16 (token, group head) rows per kv head at hdim 128: the split-KV call runs on the tcgen05 instance
+    (packed rows as one Q tile, pieces of the context as splits).  Checked against the oracle and against the
+    mma.sync instance; page tails are poisoned with NaN.  Ragged query lengths (one sequence with a single token, one
+    with more tokens than keys are not possible here: bottom-right causal needs sq <= sk for every row to see a key,
+    so a short context is included instead), a sequence without keys, none and causal masks."""
+    d = 128
+    lens_k = [2000, 40, 1300, 0, 129, 3100]
+    lens_q = [16, 7, 1, 3, 40, 33]
+    cache = make_paged_cache(lens_k, hkv, d, d, page, dtype, seed=23)
+    k_bad, v_bad = _poison_page_tails(cache, lens_k, page)
+    cu_q = to_seqstarts(lens_q)
+    q = normal_tensor((int(cu_q[-1]), hq, d), dtype, 35)
+    for causal in (True, False):
+        o_ref, lse_ref = oracle.fmha_fwd(q, cache.k, cache.v, seqstart_q=cu_q, seqlen_k=cache.seqlen_k,
+                                         block_table=cache.block_table, mask_type=2 if causal else 0,
+                                         window=(-1, 0) if causal else (-1, -1))
+
+        def run():
+            return ops.fmha_fwd_splitkv(_cu(q), _cu(k_bad), _cu(v_bad), seqlen_k=_cu(cache.seqlen_k),
+                                        block_table=_cu(cache.block_table), cu_seqlens_q=_cu(cu_q),
+                                        max_seqlen_q=max(lens_q), num_splits=num_splits, causal=causal, return_lse=True)
+        o, lse = run()
+        _lib.set_instance_param(0, "use_sm100_splitkv", 0)
+        try:
+            o_mma, lse_mma = run()
+        finally:
+            _lib.set_instance_param(0, "use_sm100_splitkv", 1)
+        assert _lib.device_status() == 0
+        assert_o_close(o, o_ref, f"tcgen05 split-KV O causal={causal}")
+        assert_lse_close(lse, lse_ref, f"tcgen05 split-KV LSE causal={causal}")
+        assert_o_close(o_mma, o_ref, f"mma.sync split-KV O causal={causal}")
+        assert_lse_close(lse_mma, lse_ref, f"mma.sync split-KV LSE causal={causal}")
+
+
+def test_splitkv_many_query_rows_contiguous_cache_batch_mode():
+    # batch-mode q [b, sq, hq, d] against a contiguous cache [b, cap, hkv, d] with garbage behind each length
+    dtype = torch.bfloat16
+    b, sq, hq, hkv, d, cap = 3, 12, 16, 4, 128, 700
+    lens = [700, 129, 333]
+    k = normal_tensor((b, cap, hkv, d), dtype, 81)
+    v = normal_tensor((b, cap, hkv, d), dtype, 82)
+    k_bad, v_bad = k.clone(), v.clone()
+    for i, n in enumerate(lens):
+        k_bad[i, n:] = float("nan")
+        v_bad[i, n:] = float("nan")
+    q = normal_tensor((b, sq, hq, d), dtype, 83)
+    sl = torch.tensor(lens, dtype=torch.int32)
+    o_ref, lse_ref = oracle.fmha_fwd(q, k, v, seqlen_k=sl, mask_type=2, window=(-1, 0))
+    o, lse = ops.fmha_fwd_splitkv(_cu(q), _cu(k_bad), _cu(v_bad), seqlen_k=_cu(sl), num_splits=4, causal=True,
+                                  return_lse=True)
+    assert _lib.device_status() == 0
+    assert_o_close(o, o_ref)
+    assert_lse_close(lse, lse_ref)
+
+
 def test_splitkv_config3_small():
     # BASELINE config 3 geometry (32/8 heads, hdim 128, page 16, shuffled block table) at reduced batch/context
     dtype = torch.bfloat16
