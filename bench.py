@@ -491,7 +491,7 @@ def main():
     # ------------------------------------------------------------------ append + decode (config 4)
     if not args.no_decode and not args.small:
         wa = make_append_decode(777, device, data_seed=777 + rank)
-        S4 = ops.default_num_splits(len(wa["lens"]))
+        S4 = ops.default_num_splits(len(wa["lens"]), rows_per_kv_head=max(wa["new"]) * (HQ // HKV))
         cu_n, max_new = wa["cu_new"], max(wa["new"])
         ws4 = ops.splitkv_workspace(wa["qn"], D, S4, cu_n)
 

@@ -213,7 +213,7 @@ struct Item {
 // Shared-memory control block placed after the tiles.
 struct Ctrl {
     uint64_t q_full, q_empty;
-    uint64_t k_full[KV_SLOTS], k_empty[KV_SLOTS], v_full[KV_SLOTS], v_empty[KV_SLOTS];
+    uint64_t k_full[3], k_empty[3], v_full[KV_SLOTS], v_empty[KV_SLOTS];  // (the split modes use a third K slot)
     uint64_t s_full[2], p_full[2], o_full[2];
     uint32_t tmem_base;
     int abort_flag;
@@ -351,7 +351,7 @@ __device__ __forceinline__ void expand_item(const Ctrl* ctrl, const Sm100Dev& p,
 }
 
 // The work item of round `rnd` of this CTA, from the table filled at start-up.
-template <bool SPLIT = false>
+template <int SPLIT = 0>
 __device__ __forceinline__ void get_item(const Ctrl* ctrl, const Sm100Dev& p, int rnd, int total_items, int lane, Item& it) {
     if (SPLIT) expand_item_split(ctrl, p, ctrl->items[rnd], it);
     else expand_item(ctrl, p, ctrl->items[rnd], it);
@@ -359,8 +359,12 @@ __device__ __forceinline__ void get_item(const Ctrl* ctrl, const Sm100Dev& p, in
 
 // WINDOW: the mask has a left window or a right window other than 0 (everything but no mask / causal); a separate
 // instance, so that the common masks do not carry the second bound of the visible range through the softmax loop.
-// SPLIT: the split-KV form described at Sm100Dev (one Q tile per item, tile 1 unused).
-template <typename T, int NPOLY8, bool WINDOW, bool SPLIT>
+// SPLIT 1: the split-KV form described at Sm100Dev (one Q tile per item, tile 1 unused).
+// SPLIT 2: the same for at most 64 packed rows: the rows are loaded twice (tile rows 0-63 and 64-127); the copy in rows
+//          0-63 takes keys 0-63 of every 128-key tile, the copy in rows 64-127 takes keys 64-127, each as a split of its
+//          own (2 * piece, 2 * piece + 1).  Every softmax thread then handles 64 columns instead of 128 with half of the
+//          threads idle, which halves the softmax part of the per-tile chain.
+template <typename T, int NPOLY8, bool WINDOW, int SPLIT>
 __global__ void __launch_bounds__(NTHREADS, 1)
 fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                       const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_o,
@@ -372,8 +376,11 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     const uint32_t raw = smem_u32(smem_raw);
     uint8_t* base = smem_raw + (((raw + 1023u) & ~1023u) - raw);
     uint8_t* sQ = base;                                  // 2 tiles
-    uint8_t* sK = base + 2 * TILE_BYTES;                 // KV_SLOTS tiles
-    uint8_t* sV = sK + KV_SLOTS * TILE_BYTES;            // KV_SLOTS tiles
+    // The split modes have one Q tile; the room of the second one is a third K slot: with a single tile per item
+    // the step is short, and two K tiles ahead keep the loads in flight that the HBM rate needs.
+    constexpr int KS = SPLIT ? 3 : 2;
+    uint8_t* sK = base + (SPLIT ? 1 : 2) * TILE_BYTES;   // KS tiles
+    uint8_t* sV = sK + KS * TILE_BYTES;                  // KV_SLOTS tiles
     uint8_t* sStage = sV + KV_SLOTS * TILE_BYTES;        // 8 x STAGE_BYTES: O chunks of the softmax warps
     Ctrl* ctrl = reinterpret_cast<Ctrl*>(sStage + 8 * STAGE_BYTES);
     volatile int* abort_flag = &ctrl->abort_flag;
@@ -381,9 +388,11 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     if (threadIdx.x == 0) {
         mbar_init(&ctrl->q_full, 1);
         mbar_init(&ctrl->q_empty, 1);
-        for (int s = 0; s < KV_SLOTS; ++s) {
+        for (int s = 0; s < 3; ++s) {
             mbar_init(&ctrl->k_full[s], 1);
             mbar_init(&ctrl->k_empty[s], 1);
+        }
+        for (int s = 0; s < KV_SLOTS; ++s) {
             mbar_init(&ctrl->v_full[s], 1);
             mbar_init(&ctrl->v_empty[s], 1);
         }
@@ -402,7 +411,7 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
     }
     if (p.page > 0) {  // paged: slots start as zeros (rows that are never loaded stay finite)
-        for (int idx = threadIdx.x; idx < 2 * KV_SLOTS * TILE_BYTES / 16; idx += NTHREADS)
+        for (int idx = threadIdx.x; idx < (KS + KV_SLOTS) * TILE_BYTES / 16; idx += NTHREADS)
             reinterpret_cast<uint4*>(sK)[idx] = make_uint4(0u, 0u, 0u, 0u);
         fence_proxy_async_smem();
     }
@@ -433,11 +442,11 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         const int rows_per_block = p.pair_heads ? BM : 2 * BM;
         if (SPLIT) {  // pieces = splits in use; more than the workspace has means a length beyond the stated capacity
             int pieces = ((sk + BN - 1) / BN + p.piece_tiles - 1) / p.piece_tiles;
-            if (pieces > p.num_splits) {
-                pieces = p.num_splits;
+            if (pieces > p.num_splits / (SPLIT == 2 ? 2 : 1)) {
+                pieces = p.num_splits / (SPLIT == 2 ? 2 : 1);
                 atomicOr(p.status, 0x10000000);
             }
-            ctrl->nblk[b] = pieces;
+            ctrl->nblk[b] = pieces;  // (with duplicated rows every piece is two splits; see the users of nblk)
         }
         else ctrl->nblk[b] = min(p.num_levels, (sq + rows_per_block - 1) / rows_per_block);
     }
@@ -454,7 +463,7 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         // splits a sequence does not use: LSE = -inf, so that the merge gives them no weight
         if (p.lse_acc) {
             for (int b = blockIdx.x; b < p.batch; b += gridDim.x) {
-                const int used = ctrl->nblk[b], sq = ctrl->seq_sq[b], q0 = ctrl->seq_q0[b];
+                const int used = ctrl->nblk[b] * (SPLIT == 2 ? 2 : 1), sq = ctrl->seq_sq[b], q0 = ctrl->seq_q0[b];
                 const int cnt = (p.num_splits - used) * p.hq * sq;
                 for (int e = threadIdx.x; e < cnt; e += NTHREADS) {
                     const int s = used + e / (p.hq * sq), rem = e % (p.hq * sq), h = rem / sq, i = rem - h * sq;
@@ -501,8 +510,11 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         // to the CTA's pool and setmaxnreg.inc waits -- without a bound -- until the pool can serve it, so the sum
         // after the moves must stay below the launch allocation: 256 x 208 + 128 x 80 = 63488.
         asm volatile("setmaxnreg.dec.sync.aligned.u32 80;\n" ::);
-        if (warp == 9) {
-            // ================================ TMA producer ================================
+        // With paged K/V the copies are many small boxes and their issue takes a warp a good part of a step, so K and V
+        // have a producer warp each (9: Q and K, 10: V); contiguous K/V is two boxes per tile and warp 9 does it all.
+        const bool k_role = warp == 9, v_role = p.page > 0 ? warp == 10 : warp == 9;
+        if (k_role || v_role) {
+            // ================================ TMA producers ================================
             if (lane == 0) {
                 tma_prefetch_desc(&map_q);
                 tma_prefetch_desc(&map_k);
@@ -522,14 +534,20 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                 get_item<SPLIT>(ctrl, p, rnd, total_items, lane, it);
                 if (!it.valid || it.N == 0) continue;
                 bool ok = true;
-                if (lane == 0) {
+                if (lane == 0 && k_role) {
                     ok = mbar_wait_bounded(&ctrl->q_empty, (q_cnt & 1u) ^ 1u, abort_flag, p.status, 0x08);
                     if (ok && SPLIT) {
                         // one box of (64 columns, group heads, 128/group tokens) per half: the rows land in
                         // (token, group head) order
                         mbar_expect_tx(&ctrl->q_full, TILE_BYTES);
-                        for (int hb = 0; hb < 2; ++hb)
-                            tma_load_4d(sQ + hb * HALF_BYTES, &map_q, &ctrl->q_full, hb * 64, 0, it.kh, it.q0 + it.row0[0] / p.group);
+                        for (int hb = 0; hb < 2; ++hb) {
+                            if (SPLIT == 2) {  // the box holds 64 rows: once for tile rows 0-63, once for 64-127
+                                tma_load_4d(sQ + hb * HALF_BYTES, &map_q, &ctrl->q_full, hb * 64, 0, it.kh, it.q0);
+                                tma_load_4d(sQ + hb * HALF_BYTES + 64 * 128, &map_q, &ctrl->q_full, hb * 64, 0, it.kh, it.q0);
+                            } else {
+                                tma_load_4d(sQ + hb * HALF_BYTES, &map_q, &ctrl->q_full, hb * 64, 0, it.kh, it.q0 + it.row0[0] / p.group);
+                            }
+                        }
                     } else if (ok) {
                         const int q_tiles = (it.row0[1] < it.sq) ? 2 : 1;
                         mbar_expect_tx(&ctrl->q_full, q_tiles * TILE_BYTES);
@@ -543,13 +561,13 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                     if (p.page == 0) {  // contiguous K/V: one box per tile and 64-column half
                         for (int n = 0; ok && n < it.N; ++n) {
                             const uint32_t kc = kv_cnt + n;
-                            const int s = kc % KV_SLOTS;
-                            const uint32_t ph = (kc / KV_SLOTS) & 1u;
+                            const int s = kc % KV_SLOTS, sk_ = kc % KS;
+                            const uint32_t ph = (kc / KV_SLOTS) & 1u, phk = (kc / KS) & 1u;
                             const int row = it.k0 + (it.n0 + n) * BN;
-                            if (!(ok = mbar_wait_bounded(&ctrl->k_empty[s], ph ^ 1u, abort_flag, p.status, 0x10))) break;
-                            mbar_expect_tx(&ctrl->k_full[s], TILE_BYTES);
+                            if (!(ok = mbar_wait_bounded(&ctrl->k_empty[sk_], phk ^ 1u, abort_flag, p.status, 0x10))) break;
+                            mbar_expect_tx(&ctrl->k_full[sk_], TILE_BYTES);
                             for (int hb = 0; hb < 2; ++hb)
-                                tma_load_3d(sK + s * TILE_BYTES + hb * HALF_BYTES, &map_k, &ctrl->k_full[s], hb * 64, it.kh, row);
+                                tma_load_3d(sK + sk_ * TILE_BYTES + hb * HALF_BYTES, &map_k, &ctrl->k_full[sk_], hb * 64, it.kh, row);
                             if (!(ok = mbar_wait_bounded(&ctrl->v_empty[s], ph ^ 1u, abort_flag, p.status, 0x20))) break;
                             mbar_expect_tx(&ctrl->v_full[s], TILE_BYTES);
                             for (int hb = 0; hb < 2; ++hb)
@@ -576,22 +594,27 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                 int my_row = 0, my_valid = 0;
                 if (p.page > 0) lookup(0, my_row, my_valid);
                 for (int n = 0; p.page > 0 && ok && n < it.N; ++n, ++kv_cnt) {
-                    const int s = kv_cnt % KV_SLOTS;
-                    const uint32_t ph = (kv_cnt / KV_SLOTS) & 1u;
+                    const int s = kv_cnt % KV_SLOTS, sk_ = kv_cnt % KS;
+                    const uint32_t ph = (kv_cnt / KV_SLOTS) & 1u, phk = (kv_cnt / KS) & 1u;
                     int next_row, next_valid;
                     lookup(n + 1, next_row, next_valid);
                     const uint32_t any_mask = __ballot_sync(0xffffffffu, my_valid > 0);
                     const uint32_t full_mask = __ballot_sync(0xffffffffu, my_valid == chunk);
-                    if (lane == 0) {
-                        ok = mbar_wait_bounded(&ctrl->k_empty[s], ph ^ 1u, abort_flag, p.status, 0x10);
-                        if (ok) mbar_expect_tx(&ctrl->k_full[s], __popc(any_mask) * chunk * HD * 2);
+                    if (lane == 0 && k_role) {
+                        ok = mbar_wait_bounded(&ctrl->k_empty[sk_], phk ^ 1u, abort_flag, p.status, 0x10);
+                        if (ok) mbar_expect_tx(&ctrl->k_full[sk_], __popc(any_mask) * chunk * HD * 2);
                     }
                     ok = __shfl_sync(0xffffffffu, ok, 0);
                     if (!ok) break;
-                    if (my_valid > 0)
+                    if (k_role && my_valid > 0)
                         for (int hb = 0; hb < 2; ++hb)
-                            tma_load_3d(sK + s * TILE_BYTES + hb * HALF_BYTES + lane * chunk * 128, &map_k, &ctrl->k_full[s],
+                            tma_load_3d(sK + sk_ * TILE_BYTES + hb * HALF_BYTES + lane * chunk * 128, &map_k, &ctrl->k_full[sk_],
                                         hb * 64, it.kh, my_row);
+                    if (!v_role) {
+                        my_row = next_row;
+                        my_valid = next_valid;
+                        continue;
+                    }
                     if (lane == 0) ok = mbar_wait_bounded(&ctrl->v_empty[s], ph ^ 1u, abort_flag, p.status, 0x20);
                     ok = __shfl_sync(0xffffffffu, ok, 0);
                     if (!ok) break;
@@ -634,11 +657,10 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
             const uint64_t dQ0 = make_smem_desc(smem_u32(sQ), 0, 1024);
             const uint64_t dQ1 = make_smem_desc(smem_u32(sQ + TILE_BYTES), 0, 1024);
             const uint64_t dK0 = make_smem_desc(smem_u32(sK), 0, 1024);
-            const uint64_t dK1 = make_smem_desc(smem_u32(sK + TILE_BYTES), 0, 1024);
             const uint64_t dV0 = make_smem_desc(smem_u32(sV), HALF_BYTES, 1024);
             const uint64_t dV1 = make_smem_desc(smem_u32(sV + TILE_BYTES), HALF_BYTES, 1024);
             auto issue_qk = [&](int i, int s) {  // S_i = Q_i K^T : 8 steps of 16 along the head dim
-                const uint64_t qd = i ? dQ1 : dQ0, kd = s ? dK1 : dK0;
+                const uint64_t qd = i ? dQ1 : dQ0, kd = dK0 + (uint64_t)((s * TILE_BYTES) >> 4);
                 const uint32_t d = tS[i];
 #pragma unroll
                 for (int ks = 0; ks < HD / 16; ++ks) {
@@ -653,6 +675,21 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                 for (int ks = 0; ks < BN / 16; ++ks)
                     umma_ts(d, a + ks * 8, vd + (uint64_t)((ks * 2048) >> 4), idesc_pv, (accumulate || ks > 0) ? 1u : 0u);
             };
+            // split modes: tile 0's Q against S buffer `buf` (the S columns of either tile), P read from the same buffer
+            auto issue_qk_to = [&](uint32_t buf, int s) {
+                const uint64_t kd = dK0 + (uint64_t)((s * TILE_BYTES) >> 4);
+#pragma unroll
+                for (int ks = 0; ks < HD / 16; ++ks) {
+                    const uint64_t off = (uint64_t)(((ks / 4) * HALF_BYTES + (ks % 4) * 32) >> 4);
+                    umma_ss(tS[0] + buf * 128, dQ0 + off, kd + off, idesc_qk, ks > 0 ? 1u : 0u);
+                }
+            };
+            auto issue_pv_from = [&](uint32_t buf, int s, bool accumulate) {
+                const uint64_t vd = s ? dV1 : dV0;
+#pragma unroll
+                for (int ks = 0; ks < BN / 16; ++ks)
+                    umma_ts(tO[0], tS[0] + buf * 128 + ks * 8, vd + (uint64_t)((ks * 2048) >> 4), idesc_pv, (accumulate || ks > 0) ? 1u : 0u);
+            };
             // running counts give ring slots and barrier parities across work items
             uint32_t kv_cnt = 0, q_cnt = 0, sc0 = 0, sc1 = 0;
             if (lane == 0) {  // the whole loop is one thread's; an item with N == 0 is skipped by every role
@@ -666,10 +703,16 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                     bool ok = true;
                     int nN = 0, nN0 = 0, nN1 = 0;
                     if (N > 0) {
-                        const int s0 = kv_cnt % KV_SLOTS;
+                        const int s0 = kv_cnt % KS;
                         ok = mbar_wait_bounded(&ctrl->q_full, q_cnt & 1u, abort_flag, p.status, 0x40) &&
-                             mbar_wait_bounded(&ctrl->k_full[s0], (kv_cnt / KV_SLOTS) & 1u, abort_flag, p.status, 0x41);
-                        if (ok) {
+                             mbar_wait_bounded(&ctrl->k_full[s0], (kv_cnt / KS) & 1u, abort_flag, p.status, 0x41);
+                        if (ok && SPLIT) {  // S buffers alternate with the step (sc0 counts the steps so far)
+                            tc_fence_after();
+                            issue_qk_to(sc0 & 1u, s0);
+                            umma_commit(&ctrl->s_full[sc0 & 1u]);
+                            umma_commit(&ctrl->k_empty[s0]);
+                            if (N == 1) umma_commit(&ctrl->q_empty);
+                        } else if (ok) {
                             tc_fence_after();
                             if (N0 > 0) { issue_qk(0, s0); umma_commit(&ctrl->s_full[0]); }
                             if (N1 > 0) { issue_qk(1, s0); umma_commit(&ctrl->s_full[1]); }
@@ -684,8 +727,27 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                         }
                         for (int n = 0; ok && n < N; ++n) {
                             const uint32_t kc = kv_cnt + n;
-                            const int s = kc % KV_SLOTS, s1 = (kc + 1) % KV_SLOTS;
-                            const uint32_t ph = (kc / KV_SLOTS) & 1u, ph1 = ((kc + 1) / KV_SLOTS) & 1u;
+                            const int s = kc % KV_SLOTS, s1 = (kc + 1) % KS;           // V slot of this step, K slot of the next
+                            const uint32_t ph = (kc / KV_SLOTS) & 1u, ph1 = ((kc + 1) / KS) & 1u;
+                            if (SPLIT) {
+                                const uint32_t g = sc0 + n;
+                                if (n + 1 < N) {  // S of the next step, into the other buffer, ahead of this step's PV
+                                    if (!(ok = mbar_wait_bounded(&ctrl->k_full[s1], ph1, abort_flag, p.status, 0x44))) break;
+                                    tc_fence_after();
+                                    issue_qk_to((g + 1u) & 1u, s1);
+                                    umma_commit(&ctrl->s_full[(g + 1u) & 1u]);
+                                    umma_commit(&ctrl->k_empty[s1]);
+                                    if (n + 2 == N) umma_commit(&ctrl->q_empty);
+                                }
+                                if (!(ok = mbar_wait_bounded(&ctrl->v_full[s], ph, abort_flag, p.status, 0x42))) break;
+                                if (!(ok = mbar_wait_bounded(&ctrl->p_full[g & 1u], (g >> 1) & 1u, abort_flag, p.status, 0x43))) break;
+                                tc_fence_after();
+                                issue_pv_from(g & 1u, s, n > 0);
+                                if (n + 2 == N) umma_commit(&ctrl->o_full[1]);  // the last PV but one is done
+                                if (n + 1 == N) umma_commit(&ctrl->o_full[0]);
+                                umma_commit(&ctrl->v_empty[s]);
+                                continue;
+                            }
                             if (!(ok = mbar_wait_bounded(&ctrl->v_full[s], ph, abort_flag, p.status, 0x42))) break;
                             if (n < N0) {
                                 if (!(ok = mbar_wait_bounded(&ctrl->p_full[0], (sc0 + n) & 1u, abort_flag, p.status, 0x43))) break;
@@ -731,6 +793,7 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         const uint32_t lane_addr = tmem + ((uint32_t)((warp & 3) * 32) << 16);
         const uint32_t tS = lane_addr + i * 128, tO = lane_addr + 256 + i * 128;
         uint32_t sc = 0, oc = 0;  // S tiles and O accumulators consumed so far (barrier parities)
+        uint32_t oc1 = 0;         // split modes: items with two or more steps so far (parity of the o_full[1] commits)
         bool ok = true;
         for (int rnd = 0; ok && rnd < rounds; ++rnd) {
             Item it;
@@ -742,10 +805,12 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
             // split mode packs (token, group head) into the rows; `row` is the query token either way
             const int packed_first = i ? it.row0[1] : it.row0[0];
             const int group = SPLIT ? p.group : 1;
+            const int rr = SPLIT == 2 ? (r & 63) : r;   // packed row inside the tile
+            const int khalf = SPLIT == 2 ? (r >> 6) : 0;  // which 64 keys of every tile this thread's copy of the row takes
             const int tile_first_row = SPLIT ? packed_first / group : packed_first;
-            const int row = SPLIT ? (packed_first + r) / group : packed_first + r;      // row inside the sequence
+            const int row = SPLIT ? (packed_first + rr) / group : packed_first + r;      // row inside the sequence
             const bool row_ok = row < sq;
-            if (SPLIT) head += (packed_first + r) - row * group;
+            if (SPLIT) head += (packed_first + rr) - row * group;
             // visible keys of this row: [first_key, limit]
             const int wr = WINDOW ? p.wr : 0, wl = WINDOW ? p.wl : -1;
             const int limit = (p.causal && wr >= 0) ? min(sk - 1, row + shift + wr) : sk - 1;
@@ -755,28 +820,37 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
             float l = 0.f;
             for (int n = 0; n < Ni; ++n) {
                 // warp-uniform outcome: the loads, votes and stores below are warp-collective
-                ok = __all_sync(0xffffffffu, mbar_wait_bounded(&ctrl->s_full[i], (sc + n) & 1u, abort_flag, p.status, 0x100 << i));
+                // The split modes have one Q tile and use the other tile's S columns as a second S buffer: the QK^T of
+                // step n+1 is issued before the PV of step n, so the next S is there when P has been handed over.
+                // Buffer and barrier index are the step's parity there, the Q tile otherwise.
+                const uint32_t gstep = sc + n;
+                const int sb = SPLIT ? (int)(gstep & 1u) : i;
+                const uint32_t tSb = SPLIT ? lane_addr + sb * 128 : tS;
+                ok = __all_sync(0xffffffffu, mbar_wait_bounded(&ctrl->s_full[sb], (SPLIT ? (gstep >> 1) : gstep) & 1u, abort_flag,
+                                                               p.status, 0x100 << i));
                 if (!ok) break;
                 tc_fence_after();
-                uint32_t sreg[128];
+                constexpr int NC = SPLIT == 2 ? 64 : 128;  // columns of the row this thread handles
+                uint32_t sreg[NC];
 #pragma unroll
-                for (int c = 0; c < 4; ++c) tmem_ld32(tS + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&sreg[c * 32]));
+                for (int c = 0; c < NC / 32; ++c)
+                    tmem_ld32(tSb + khalf * 64 + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&sreg[c * 32]));
                 tmem_wait_ld();
                 // mask the diagonal and tail tiles
-                const int key0 = (it.n0 + n) * BN;
-                const bool need_mask = (key0 + BN > sk) ||
-                                       (p.causal && wr >= 0 && key0 + BN - 1 > tile_first_row + shift + wr) ||
+                const int key0 = (it.n0 + n) * BN + khalf * 64;
+                const bool need_mask = (key0 + NC > sk) ||
+                                       (p.causal && wr >= 0 && key0 + NC - 1 > tile_first_row + shift + wr) ||
                                        (WINDOW && p.causal && wl >= 0 && key0 < tile_first_row + BM - 1 + shift - wl);
                 if (need_mask) {
 #pragma unroll
-                    for (int j = 0; j < 128; ++j)
+                    for (int j = 0; j < NC; ++j)
                         if (key0 + j > limit || (WINDOW && key0 + j < first_key)) sreg[j] = 0xff800000u;  // -inf
                 }
                 float mx;
                 {
                     float a0 = -INFINITY, a1 = -INFINITY, a2 = -INFINITY, a3 = -INFINITY;  // four independent chains
 #pragma unroll
-                    for (int j = 0; j < 128; j += 8) {
+                    for (int j = 0; j < NC; j += 8) {
                         a0 = max3(a0, __uint_as_float(sreg[j]), __uint_as_float(sreg[j + 1]));
                         a1 = max3(a1, __uint_as_float(sreg[j + 2]), __uint_as_float(sreg[j + 3]));
                         a2 = max3(a2, __uint_as_float(sreg[j + 4]), __uint_as_float(sreg[j + 5]));
@@ -788,6 +862,19 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                 // raise the running max only on a jump of more than 2^8; rescale O in TMEM when that happens
                 const bool grow = mx > m_used + kRescaleThreshold;
                 if (n > 0 && __any_sync(0xffffffffu, grow)) {
+                    if (SPLIT) {
+                        // O must be at rest: the PV of step n-1 may still be running, S of this step was computed ahead
+                        // of it.  The QK^T of step n+1 is issued behind that PV and the pipe runs in order, so the next
+                        // S being ready tells that it is over; the last step has no next S and waits for the commit
+                        // the issuer makes behind the item's last PV but one.
+                        if (n + 1 < Ni)
+                            ok = __all_sync(0xffffffffu, mbar_wait_bounded(&ctrl->s_full[sb ^ 1], ((gstep + 1u) >> 1) & 1u,
+                                                                           abort_flag, p.status, 0x1000));
+                        else
+                            ok = __all_sync(0xffffffffu, mbar_wait_bounded(&ctrl->o_full[1], oc1 & 1u, abort_flag, p.status, 0x2000));
+                        if (!ok) break;
+                        tc_fence_after();
+                    }
                     const float alpha = grow ? fast_exp2(m_used - mx) : 1.f;  // exp2(-inf) = 0
                     l *= alpha;
 #pragma unroll
@@ -822,23 +909,30 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                         if (j & 1) psb = __fadd2_rn(psb, pr); else psa = __fadd2_rn(psa, pr);
                         pk[j] = Elem<T>::pack2(pr.x, pr.y);
                     }
-                    tmem_st32(tS + c * 32, pk);
+                    tmem_st32(tSb + (SPLIT == 2 ? khalf : c) * 32, pk);
                 };
                 if (need_mask) {
                     exp_half(0, std::integral_constant<int, 0>{});
-                    exp_half(1, std::integral_constant<int, 0>{});
+                    if (SPLIT != 2) exp_half(1, std::integral_constant<int, 0>{});
                 } else {
                     exp_half(0, std::integral_constant<int, NPOLY8>{});
-                    exp_half(1, std::integral_constant<int, NPOLY8>{});
+                    if (SPLIT != 2) exp_half(1, std::integral_constant<int, NPOLY8>{});
+                }
+                if (SPLIT == 2) {  // this copy of the row gives the other 64 keys no weight
+                    uint32_t zero[32];
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) zero[j] = 0u;
+                    tmem_st32(tSb + (1 - khalf) * 32, zero);
                 }
                 l += (psa.x + psa.y) + (psb.x + psb.y);
                 tmem_wait_st();
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&ctrl->p_full[i]);
+                if (lane == 0) mbar_arrive(&ctrl->p_full[sb]);
             }
             if (!ok) break;
             sc += Ni;
+            if (SPLIT && Ni >= 2) ++oc1;
             // ---- epilogue: O / l and LSE ----
             if (Ni > 0) {
                 ok = __all_sync(0xffffffffu, mbar_wait_bounded(&ctrl->o_full[i], oc & 1u, abort_flag, p.status, 0x400 << i));
@@ -850,9 +944,10 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                 // fp32 partial of this split, normalised inside the split, and its LSE (natural log)
                 if (i == 0 && tile_first_row < sq) {
                     const float inv = l > 0.f ? 1.f / l : 0.f;
+                    const int split = SPLIT == 2 ? 2 * it.h[1] + khalf : it.h[1];
                     const int64_t slot = p.seqstart_q
-                        ? ((int64_t)head * p.num_splits + it.h[1]) * p.total_q + it.q0 + row
-                        : (((int64_t)it.b * p.hq + head) * p.num_splits + it.h[1]) * p.sq_cap + row;
+                        ? ((int64_t)head * p.num_splits + split) * p.total_q + it.q0 + row
+                        : (((int64_t)it.b * p.hq + head) * p.num_splits + split) * p.sq_cap + row;
                     float* orow = p.o_acc + slot * HD;
 #pragma unroll
                     for (int c = 0; c < 4; ++c) {
@@ -971,7 +1066,7 @@ int make_map_o(CUtensorMap* map, const void* base, int dtype, int64_t rows, int6
     return FLASHCK_OK;
 }
 
-template <typename T, int NPOLY8, bool WINDOW, bool SPLIT>
+template <typename T, int NPOLY8, bool WINDOW, int SPLIT>
 int launch_t(const FwdParams& p, const Sm100Dev& dev, cudaStream_t stream) {
     const int64_t rows_q = p.seqstart_q ? p.total_q : p.batch * p.seqlen_q;
     const bool paged = p.block_table || p.kv_indptr;
@@ -1057,11 +1152,11 @@ int launch_fwd_sm100(const FwdParams& p, cudaStream_t stream) {
     const bool window = p.mask_type != 0 && !(p.wl < 0 && p.wr == 0);
     const bool poly = g_poly8.load() != 0;
     if (window) {
-        if (poly) return bf16 ? launch_t<__nv_bfloat16, 3, true, false>(p, dev, stream) : launch_t<__half, 3, true, false>(p, dev, stream);
-        return bf16 ? launch_t<__nv_bfloat16, 0, true, false>(p, dev, stream) : launch_t<__half, 0, true, false>(p, dev, stream);
+        if (poly) return bf16 ? launch_t<__nv_bfloat16, 3, true, 0>(p, dev, stream) : launch_t<__half, 3, true, 0>(p, dev, stream);
+        return bf16 ? launch_t<__nv_bfloat16, 0, true, 0>(p, dev, stream) : launch_t<__half, 0, true, 0>(p, dev, stream);
     }
-    if (poly) return bf16 ? launch_t<__nv_bfloat16, 3, false, false>(p, dev, stream) : launch_t<__half, 3, false, false>(p, dev, stream);
-    return bf16 ? launch_t<__nv_bfloat16, 0, false, false>(p, dev, stream) : launch_t<__half, 0, false, false>(p, dev, stream);
+    if (poly) return bf16 ? launch_t<__nv_bfloat16, 3, false, 0>(p, dev, stream) : launch_t<__half, 3, false, 0>(p, dev, stream);
+    return bf16 ? launch_t<__nv_bfloat16, 0, false, 0>(p, dev, stream) : launch_t<__half, 0, false, 0>(p, dev, stream);
 }
 
 // ---- split-KV with several query rows per kv head (append + decode, speculative decoding, chunked prefill) ----
@@ -1070,12 +1165,12 @@ namespace {
 constexpr int kMinPieceTiles = 8;  // at least 1024 keys per work item
 
 // Q [tokens, hkv, group, 128] as boxes of (64 columns, group heads, 1 kv head, 128/group tokens).
-int make_map_q_packed(CUtensorMap* map, const void* base, int dtype, int64_t tokens, int64_t hkv, int64_t group) {
+int make_map_q_packed(CUtensorMap* map, const void* base, int dtype, int64_t tokens, int64_t hkv, int64_t group, int rows) {
     PFN_encodeTiled enc = get_encode_tiled();
     FCK_REQUIRE(enc != nullptr, FLASHCK_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
     const cuuint64_t dims[4] = {(cuuint64_t)HD, (cuuint64_t)group, (cuuint64_t)hkv, (cuuint64_t)(tokens > 0 ? tokens : 1)};
     const cuuint64_t strides[3] = {(cuuint64_t)(HD * 2), (cuuint64_t)(group * HD * 2), (cuuint64_t)(hkv * group * HD * 2)};
-    const cuuint32_t box[4] = {64, (cuuint32_t)group, 1, (cuuint32_t)(BM / group)};
+    const cuuint32_t box[4] = {64, (cuuint32_t)group, 1, (cuuint32_t)(rows / group)};
     const cuuint32_t estr[4] = {1, 1, 1, 1};
     const CUtensorMapDataType dt =
         dtype == FLASHCK_DTYPE_BFLOAT16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
@@ -1089,17 +1184,25 @@ int64_t split_cap_tiles(const SplitKVParams& p) {  // key tiles of the longest s
     const int64_t cap = p.block_table ? p.bt_stride * p.page : p.seqlen_k_cap;
     return (cap + BN - 1) / BN;
 }
+// At most 64 packed rows and room for two splits per piece: the rows are duplicated (kernel mode 2).
+bool split_duplicates_rows(const SplitKVParams& p) {
+    return p.max_seqlen_q * (p.hq / p.hkv) <= 64 && p.num_splits >= 2;
+}
+int64_t split_piece_tiles(const SplitKVParams& p) {  // key tiles per work item, so that the splits fit num_splits
+    const int64_t slots = split_duplicates_rows(p) ? p.num_splits / 2 : p.num_splits;
+    return std::max<int64_t>(kMinPieceTiles, (split_cap_tiles(p) + slots - 1) / slots);
+}
 
-template <typename T>
+template <typename T, int SPLIT>
 int launch_split_t(const SplitKVParams& p, const Sm100Dev& dev, cudaStream_t stream) {
     const int64_t tokens = p.seqstart_q ? p.total_q : p.batch * p.seqlen_q;
     const int box_k = p.block_table ? (int)std::min<int64_t>(p.page, BN) : BN;
     CUtensorMap mq, mk, mv;
     int rc;
-    if ((rc = make_map_q_packed(&mq, p.q, p.dtype, tokens, p.hkv, p.hq / p.hkv))) return rc;
+    if ((rc = make_map_q_packed(&mq, p.q, p.dtype, tokens, p.hkv, p.hq / p.hkv, SPLIT == 2 ? 64 : BM))) return rc;
     if ((rc = make_map_3d(&mk, p.k, p.dtype, 0x7fffff00ll, p.hkv, box_k))) return rc;  // cache rows are trusted
     if ((rc = make_map_3d(&mv, p.v, p.dtype, 0x7fffff00ll, p.hkv, box_k))) return rc;
-    auto kern = fmha_fwd_sm100_kernel<T, 0, false, true>;
+    auto kern = fmha_fwd_sm100_kernel<T, 0, false, SPLIT>;
     const size_t smem = 1024 + (size_t)(2 + 2 * KV_SLOTS) * TILE_BYTES + 8 * STAGE_BYTES + sizeof(Ctrl);
     static thread_local int configured_device = -1;
     int devid = 0;
@@ -1132,7 +1235,7 @@ bool splitkv_sm100_supported(const SplitKVParams& p) {
     }
     if (p.num_splits > 1 && !p.lse_acc) return false;
     const int64_t cap_tiles = split_cap_tiles(p);
-    const int64_t piece = std::max<int64_t>(kMinPieceTiles, (cap_tiles + p.num_splits - 1) / p.num_splits);
+    const int64_t piece = split_piece_tiles(p);
     if ((cap_tiles + piece - 1) / piece > 255) return false;
     const int64_t items = p.batch * p.hkv * ((p.max_seqlen_q * group + BM - 1) / BM) * ((cap_tiles + piece - 1) / piece);
     if ((items + sm_count() - 1) / sm_count() > kMaxRounds) return false;
@@ -1156,15 +1259,16 @@ int launch_splitkv_sm100(const SplitKVParams& p, cudaStream_t stream) {
     dev.page = p.block_table ? (int)p.page : BN;
     dev.bt_stride = (int)p.bt_stride;
     dev.o_acc = p.o_acc; dev.lse_acc = p.lse_acc; dev.num_splits = (int)p.num_splits;
-    const int64_t cap_tiles = split_cap_tiles(p);
-    dev.piece_tiles = (int)std::max<int64_t>(kMinPieceTiles, (cap_tiles + p.num_splits - 1) / p.num_splits);
+    dev.piece_tiles = (int)split_piece_tiles(p);
     dev.group = (int)(p.hq / p.hkv);
     dev.sq_cap = (int)p.seqlen_q;
     dev.causal = p.mask_type; dev.wl = -1; dev.wr = p.mask_type ? 0 : -1;
     dev.pair_heads = 0; dev.num_levels = 1;
     dev.scale_log2 = p.scale * 1.4426950408889634f;
-    return p.dtype == FLASHCK_DTYPE_BFLOAT16 ? launch_split_t<__nv_bfloat16>(p, dev, stream)
-                                              : launch_split_t<__half>(p, dev, stream);
+    const bool bf16 = p.dtype == FLASHCK_DTYPE_BFLOAT16;
+    if (split_duplicates_rows(p))
+        return bf16 ? launch_split_t<__nv_bfloat16, 2>(p, dev, stream) : launch_split_t<__half, 2>(p, dev, stream);
+    return bf16 ? launch_split_t<__nv_bfloat16, 1>(p, dev, stream) : launch_split_t<__half, 1>(p, dev, stream);
 }
 
 int fwd_set_param(const char* key, int64_t value) {

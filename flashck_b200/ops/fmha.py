@@ -242,13 +242,19 @@ def fmha_fwd_paged_kv_prefill(q: torch.Tensor, k_pool: torch.Tensor, v_pool: tor
 # --------------------------------------------------------------------------------------------
 # split-KV decode
 # --------------------------------------------------------------------------------------------
-def default_num_splits(batch: int, sm_count: int = 148, max_splits: int = 128) -> int:
+def default_num_splits(batch: int, sm_count: int = 148, max_splits: int = 128, rows_per_kv_head: int = 1) -> int:
     """Workspace depth for ``fmha_fwd_splitkv`` when the caller passes ``num_splits=0``.
+
+    With more than 16 query rows per kv head (``seqlen_q * hq / hkv``) the call runs on the tcgen05 instance, whose
+    work items are pieces of at least 1024 keys, each one split (two with at most 64 rows): 16 splits keep its
+    148 CTAs evenly loaded for contexts up to 8k-16k keys.  Otherwise:
 
     The kernel cuts the concatenated key stream of all sequences into one equal piece per SM, so a sequence of
     average length is touched by about ``sm_count / batch`` pieces; twice that (plus one for a piece boundary)
     keeps the cut even when the longest sequence is twice the average.  The reference leaves this heuristic
     open ("0 to determine actual number by heuristic", fmha_fwd_split_kv_jinja.h:28-30)."""
+    if rows_per_kv_head > 16:
+        return int(min(max_splits, 16))
     return int(max(2, min(max_splits, -(-2 * sm_count // max(batch, 1)) + 1)))
 
 
@@ -382,7 +388,8 @@ def fmha_fwd_splitkv(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
     else:
         page, max_pages = 0, 0
         shape_sk = k_cache.shape[0] if cu_k is not None else k_cache.shape[1]
-    S = int(num_splits) if num_splits and num_splits > 0 else default_num_splits(batch)
+    S = int(num_splits) if num_splits and num_splits > 0 else \
+        default_num_splits(batch, rows_per_kv_head=max_sq * (hq // max(hkv, 1)))
     if workspace is None:
         lse_acc, o_acc = splitkv_workspace(q, dv, S, cu_q)
     else:

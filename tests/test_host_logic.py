@@ -37,6 +37,8 @@ def test_default_num_splits():
     assert default_num_splits(4) == 75
     assert default_num_splits(100000) == 2
     assert default_num_splits(1) == 128
+    assert default_num_splits(32, rows_per_kv_head=64) == 16   # many query rows: tcgen05 instance, pieces as splits
+    assert default_num_splits(32, rows_per_kv_head=16) == default_num_splits(32)
 
 
 def test_input_generators():
