@@ -306,6 +306,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-decode", action="store_true")
     ap.add_argument("--small", action="store_true", help="reduced sizes (for profiler captures)")
+    ap.add_argument("--profile-append-decode", type=int, default=0, metavar="BATCH",
+                    help="profiler aid: only run the config 4 decode step (after one append) on BATCH sequences, no JSON")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -346,6 +348,21 @@ def main():
 
     peaks = load_peaks()
     steps, warmup = args.steps, max(args.warmup, 3)
+
+    if args.profile_append_decode > 0:  # a small, bounded run for `ncu -k ... -c ...` captures of the config 4 kernels
+        wa = make_append_decode(777, device, batch=args.profile_append_decode)
+        cu_n, max_new = wa["cu_new"], max(wa["new"])
+        S4 = ops.default_num_splits(len(wa["lens"]), rows_per_kv_head=max_new * (HQ // HKV))
+        ws4 = ops.splitkv_workspace(wa["qn"], D, S4, cu_n)
+        ops.fmha_fwd_append_kv(wa["qn"], wa["k"], wa["v"], wa["kn"], wa["vn"], wa["ctx_len"], wa["cos"], wa["sin"],
+                               block_table=wa["table"], cu_seqlens_q=cu_n, cu_seqlens_knew=cu_n)
+        for _ in range(max(steps, 1) + warmup):
+            ops.fmha_fwd_splitkv(wa["qn"], wa["k"], wa["v"], seqlen_k=wa["seqlen"], block_table=wa["table"],
+                                 cu_seqlens_q=cu_n, max_seqlen_q=max_new, num_splits=S4, causal=True, workspace=ws4)
+        torch.cuda.synchronize()
+        print(json.dumps({"profile_append_decode": {"batch": args.profile_append_decode, "tokens": sum(wa["lens"]),
+                                                    "algorithmic_bytes": wa["bytes"], "num_splits": S4}}))
+        return
 
     # ------------------------------------------------------------------ prefill (headline)
     if args.small:
