@@ -510,10 +510,12 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         // to the CTA's pool and setmaxnreg.inc waits -- without a bound -- until the pool can serve it, so the sum
         // after the moves must stay below the launch allocation: 256 x 208 + 128 x 80 = 63488.
         asm volatile("setmaxnreg.dec.sync.aligned.u32 80;\n" ::);
-        // With paged K/V the copies are many small boxes and their issue takes a warp a good part of a step, so K and V
-        // have a producer warp each (9: Q and K, 10: V); contiguous K/V is two boxes per tile and warp 9 does it all.
-        const bool k_role = warp == 9, v_role = p.page > 0 ? warp == 10 : warp == 9;
-        if (k_role || v_role) {
+        // With paged K/V the copies are many small boxes and their issue takes a warp a good part of a step, so K, V
+        // and Q have a producer warp each (9, 10, 11): the K producer then runs ahead into the next item (its first
+        // page-id lookup is a round trip to memory) instead of waiting for the Q buffer, which frees late.  Contiguous
+        // K/V is two boxes per tile and warp 9 does it all.
+        const bool k_role = warp == 9, v_role = p.page > 0 ? warp == 10 : warp == 9, q_role = p.page > 0 ? warp == 11 : warp == 9;
+        if (k_role || v_role || q_role) {
             // ================================ TMA producers ================================
             if (lane == 0) {
                 tma_prefetch_desc(&map_q);
@@ -534,7 +536,7 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                 get_item<SPLIT>(ctrl, p, rnd, total_items, lane, it);
                 if (!it.valid || it.N == 0) continue;
                 bool ok = true;
-                if (lane == 0 && k_role) {
+                if (lane == 0 && q_role) {
                     ok = mbar_wait_bounded(&ctrl->q_empty, (q_cnt & 1u) ^ 1u, abort_flag, p.status, 0x08);
                     if (ok && SPLIT) {
                         // one box of (64 columns, group heads, 128/group tokens) per half: the rows land in
@@ -592,8 +594,9 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                     }
                 };
                 int my_row = 0, my_valid = 0;
-                if (p.page > 0) lookup(0, my_row, my_valid);
-                for (int n = 0; p.page > 0 && ok && n < it.N; ++n, ++kv_cnt) {
+                const bool kv_paged = p.page > 0 && (k_role || v_role);
+                if (kv_paged) lookup(0, my_row, my_valid);
+                for (int n = 0; kv_paged && ok && n < it.N; ++n, ++kv_cnt) {
                     const int s = kv_cnt % KV_SLOTS, sk_ = kv_cnt % KS;
                     const uint32_t ph = (kv_cnt / KV_SLOTS) & 1u, phk = (kv_cnt / KS) & 1u;
                     int next_row, next_valid;
@@ -948,7 +951,11 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                     const int64_t slot = p.seqstart_q
                         ? ((int64_t)head * p.num_splits + split) * p.total_q + it.q0 + row
                         : (((int64_t)it.b * p.hq + head) * p.num_splits + split) * p.sq_cap + row;
-                    float* orow = p.o_acc + slot * HD;
+                    // The rows of a warp go to 32 different places of the workspace (one per token and head), 512
+                    // bytes each.  They pass through shared memory (32 rows x 32 columns, 16-byte pieces rotated by
+                    // row against bank conflicts) so that eight lanes write one row's 128 bytes together.
+                    const unsigned long long my_ptr = row_ok ? (unsigned long long)(p.o_acc + slot * HD) : 0ull;
+                    float* stage = reinterpret_cast<float*>(sStage + (warp & 3) * 4096);
 #pragma unroll
                     for (int c = 0; c < 4; ++c) {
                         uint32_t t[32];
@@ -959,12 +966,19 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
 #pragma unroll
                             for (int j = 0; j < 32; ++j) t[j] = 0u;
                         }
-                        if (row_ok) {
+                        __syncwarp();  // the previous chunk has been read out of the staging rows
 #pragma unroll
-                            for (int v4 = 0; v4 < 8; ++v4)
-                                *reinterpret_cast<float4*>(orow + c * 32 + v4 * 4) =
-                                    make_float4(__uint_as_float(t[v4 * 4 + 0]) * inv, __uint_as_float(t[v4 * 4 + 1]) * inv,
-                                                __uint_as_float(t[v4 * 4 + 2]) * inv, __uint_as_float(t[v4 * 4 + 3]) * inv);
+                        for (int v4 = 0; v4 < 8; ++v4)
+                            *reinterpret_cast<float4*>(stage + lane * 32 + ((v4 ^ (lane & 7)) << 2)) =
+                                make_float4(__uint_as_float(t[v4 * 4 + 0]) * inv, __uint_as_float(t[v4 * 4 + 1]) * inv,
+                                            __uint_as_float(t[v4 * 4 + 2]) * inv, __uint_as_float(t[v4 * 4 + 3]) * inv);
+                        __syncwarp();
+#pragma unroll
+                        for (int g4 = 0; g4 < 8; ++g4) {  // four rows per pass: lane = (row in the pass, 16-byte piece)
+                            const int srow = g4 * 4 + (lane >> 3), piece = lane & 7;
+                            const unsigned long long dst = __shfl_sync(0xffffffffu, my_ptr, srow);
+                            const float4 val = *reinterpret_cast<const float4*>(stage + srow * 32 + ((piece ^ (srow & 7)) << 2));
+                            if (dst) *reinterpret_cast<float4*>(reinterpret_cast<float*>(dst) + c * 32 + piece * 4) = val;
                         }
                     }
                     if (p.lse_acc && row_ok)
