@@ -510,11 +510,11 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         // to the CTA's pool and setmaxnreg.inc waits -- without a bound -- until the pool can serve it, so the sum
         // after the moves must stay below the launch allocation: 256 x 208 + 128 x 80 = 63488.
         asm volatile("setmaxnreg.dec.sync.aligned.u32 80;\n" ::);
-        // With paged K/V the copies are many small boxes and their issue takes a warp a good part of a step, so K, V
-        // and Q have a producer warp each (9, 10, 11): the K producer then runs ahead into the next item (its first
-        // page-id lookup is a round trip to memory) instead of waiting for the Q buffer, which frees late.  Contiguous
-        // K/V is two boxes per tile and warp 9 does it all.
-        const bool k_role = warp == 9, v_role = p.page > 0 ? warp == 10 : warp == 9, q_role = p.page > 0 ? warp == 11 : warp == 9;
+        // In the split modes a step is short and the copies are many small boxes whose issue takes a warp a good part
+        // of it, so K, V and Q have a producer warp each (9, 10, 11): the K producer then runs ahead into the next item
+        // (its first page-id lookup is a round trip to memory) instead of waiting for the Q buffer, which frees late.
+        // Prefill steps are long: warp 9 does it all there (measured: extra producer warps cost paged prefill 7 %).
+        const bool k_role = warp == 9, v_role = SPLIT ? warp == 10 : warp == 9, q_role = SPLIT ? warp == 11 : warp == 9;
         if (k_role || v_role || q_role) {
             // ================================ TMA producers ================================
             if (lane == 0) {
