@@ -1,7 +1,10 @@
-// fmha_fwd / batch prefill -- the tcgen05 instance (hdim 128, contiguous K/V, no mask or causal).
+// fmha_fwd / batch prefill / paged prefill / multi-token split-KV -- the tcgen05 instance (hdim 128).
 // Replaces ck_tile::FmhaFwdKernel<BlockFmhaPipelineQRKSVS...> as instantiated by the reference
 // (core/profiling/attention/fmha_fwd/fmha_fwd_codegen.cc:86-118) behind the C symbol FmhaFwd
-// (attention_kernels/fmha_fwd/fmha_fwd_jinja.h:124-147), batch and group mode, GQA, fp32 LSE.
+// (attention_kernels/fmha_fwd/fmha_fwd_jinja.h:124-147), batch and group mode, GQA, fp32 LSE; the paged variants
+// (fmha_fwd_batch_prefill_codegen.cc:93-162, fmha_fwd_paged_kv_prefill_codegen.cc:85-144) read K/V through a page list;
+// and, behind FmhaFwdSplitKV (fmha_fwd_split_kv_jinja.h:155-184), the calls with more than one 16-row tile of query
+// rows per kv head (the "split modes" described at Sm100Dev and at the kernel template).
 //
 // Persistent kernel: one CTA per SM (384 threads; it owns all 512 TMEM columns) walks a work list that every CTA
 // derives on chip from the sequence lengths: items sorted by decreasing row-block index (decreasing cost under a
@@ -10,7 +13,9 @@
 // same number of steps and meet the diagonal together), else two consecutive row tiles of one head.  The two
 // tiles ping-pong through the pipeline:
 //   warp 9      TMA producer: Q tiles of the item (4 boxes of 64 x 128, 128-byte swizzle), then K and V tiles of
-//               128 keys into two-slot rings that run on across work items; mbarrier expect-tx.
+//               128 keys into two-slot rings that run on across work items; mbarrier expect-tx.  Paged K/V: one box
+//               per page chunk and 64-column half, each lane issuing its own chunk's boxes; the tail of a sequence's
+//               last page is kept out of V (copied by hand with zeros behind the end).
 //   warp 8      MMA issuer (one elected thread): S_i = Q_i K^T with tcgen05.mma (both operands in shared
 //               memory, K-major), O_i += P_i V with the A operand P_i read from tensor memory and V taken
 //               MN-major straight from its [key][hdim] tile.  Accumulators live in TMEM: S0,S1 (128 columns
@@ -22,9 +27,10 @@
 //               of S_i (the next QK^T of the tile is issued after the PV that reads P, and the tensor pipe runs
 //               in order).  The running max is only raised -- and O_i rescaled in TMEM -- when it grows by more
 //               than 2^8, so the correction is off the steady-state path; the final 1/l normalisation and the
-//               O / LSE stores are done by the same warpgroup while the MMA warp already starts the next item.
-// K/V tiles hidden by the causal mask are skipped; only diagonal and tail tiles pay for masking.
-// The GQA group's q heads run in neighbouring CTAs and share K/V through L2 (no cluster multicast).
+//               O / LSE stores (O through shared memory and TMA stores) are done by the same warpgroup while the
+//               MMA warp already starts the next item.
+// K/V tiles hidden by the mask are skipped (a left window also skips the tiles before it); only boundary tiles pay
+// for masking.  The GQA group's q heads run in neighbouring CTAs and share K/V through L2 (no cluster multicast).
 // Every mbarrier wait is bounded; on expiry the CTA records a code in the device status word and drains.
 #include <algorithm>
 #include <atomic>
