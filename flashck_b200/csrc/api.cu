@@ -313,7 +313,7 @@ int FlashckSetInstanceParam(int family, const char* key, int64_t value) {
     FCK_REQUIRE(key != nullptr, FLASHCK_ERR_INVALID_ARGUMENT, "FlashckSetInstanceParam: null key");
     int rc = FLASHCK_ERR_INVALID_ARGUMENT;
     if (family == 0) rc = fwd_set_param(key, value);
-    else if (family == 2) rc = splitkv_set_param(key, value);
+    else if (family == 2) rc = !strcmp(key, "use_sm100_splitkv") ? fwd_set_param(key, value) : splitkv_set_param(key, value);
     if (rc) set_last_error("FlashckSetInstanceParam: unknown family/key %d/%s", family, key);
     return rc;
 }
@@ -321,7 +321,7 @@ int FlashckGetInstanceParam(int family, const char* key, int64_t* value_out) {
     FCK_REQUIRE(key != nullptr && value_out != nullptr, FLASHCK_ERR_INVALID_ARGUMENT, "FlashckGetInstanceParam: null argument");
     int rc = FLASHCK_ERR_INVALID_ARGUMENT;
     if (family == 0) rc = fwd_get_param(key, value_out);
-    else if (family == 2) rc = splitkv_get_param(key, value_out);
+    else if (family == 2) rc = !strcmp(key, "use_sm100_splitkv") ? fwd_get_param(key, value_out) : splitkv_get_param(key, value_out);
     if (rc) set_last_error("FlashckGetInstanceParam: unknown family/key %d/%s", family, key);
     return rc;
 }

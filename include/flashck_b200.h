@@ -201,8 +201,11 @@ FLASHCK_API int FmhaFwdSplitKVStatic(void* q_buf_ptr, void* k_buf_ptr, void* v_b
 /*
  * Instance selection (the reference picks a tile instance per problem through its tuner,
  * core/profiling/attention/fmha_fwd/fmha_fwd_emitter.cc:325-466).  `family`: 0 fmha_fwd, 2 fmha_fwd_split_kv
- * (FmhaKind values, fmha_library.h:17-25).  `key`/`value` pairs are documented in the tuner; unknown keys
- * return FLASHCK_ERR_INVALID_ARGUMENT.  Process-wide, set before launching; not thread-safe against launches.
+ * (FmhaKind values, fmha_library.h:17-25).  Keys: family 0 -- "use_sm100" (1: hdim-128 problems run on the tcgen05
+ * instance, 0: on the general one), "poly8" (0 or 3: column pairs of every 8 whose exp2 is a polynomial);
+ * family 2 -- "stages" (0 = as many as fit), "ctas_per_sm_x100", "use_sm100_splitkv" (1: calls with more than 16
+ * query rows per kv head run on the tcgen05 instance).  Unknown keys return FLASHCK_ERR_INVALID_ARGUMENT.
+ * Process-wide, set before launching; not thread-safe against launches.
  */
 FLASHCK_API int FlashckSetInstanceParam(int family, const char* key, int64_t value);
 FLASHCK_API int FlashckGetInstanceParam(int family, const char* key, int64_t* value_out);
