@@ -398,6 +398,39 @@ def test_splitkv_many_query_rows_contiguous_cache_batch_mode():
     assert_lse_close(lse, lse_ref)
 
 
+def test_splitkv_many_query_rows_batch_mode_paged_cache_batch_idx_and_top_left_mask():
+    """The remaining forms of the multi-token split-KV call on the tcgen05 instance: batch-mode q against a paged
+    cache; a contiguous cache addressed through cache_batch_idx; a top-left aligned causal mask with far more keys
+    than queries (most pieces of the context are then invisible and must come out as empty splits)."""
+    dtype = torch.bfloat16
+    hq, hkv, d, sq = 16, 4, 128, 9
+    # batch mode + pages
+    lens = [1500, 260, 17]
+    cache = make_paged_cache(lens, hkv, d, d, 32, dtype, seed=27)
+    q = normal_tensor((len(lens), sq, hq, d), dtype, 91)
+    for mt in (2, 1):
+        o_ref, lse_ref = oracle.fmha_fwd(q, cache.k, cache.v, seqlen_k=cache.seqlen_k, block_table=cache.block_table,
+                                         mask_type=mt, window=(-1, 0))
+        o, lse = ops.fmha_fwd_splitkv(_cu(q), _cu(cache.k), _cu(cache.v), seqlen_k=_cu(cache.seqlen_k),
+                                      block_table=_cu(cache.block_table), num_splits=6, mask_type=mt, window_size=(-1, 0),
+                                      return_lse=True)
+        assert _lib.device_status() == 0
+        assert_o_close(o, o_ref, f"paged batch mode, mask {mt}")
+        assert_lse_close(lse, lse_ref, f"paged batch mode, mask {mt}")
+    # contiguous cache rows picked by cache_batch_idx
+    rows, cap = 5, 600
+    k = normal_tensor((rows, cap, hkv, d), dtype, 92)
+    v = normal_tensor((rows, cap, hkv, d), dtype, 93)
+    idx = torch.tensor([3, 0, 4], dtype=torch.int64)
+    sl = torch.tensor([600, 77, 300], dtype=torch.int32)
+    o_ref, lse_ref = oracle.fmha_fwd(q, k[idx], v[idx], seqlen_k=sl, mask_type=2, window=(-1, 0))
+    o, lse = ops.fmha_fwd_splitkv(_cu(q), _cu(k), _cu(v), seqlen_k=_cu(sl), cache_batch_idx=_cu(idx), num_splits=4,
+                                  causal=True, return_lse=True)
+    assert _lib.device_status() == 0
+    assert_o_close(o, o_ref, "contiguous cache with cache_batch_idx")
+    assert_lse_close(lse, lse_ref, "contiguous cache with cache_batch_idx")
+
+
 def test_splitkv_config3_small():
     # BASELINE config 3 geometry (32/8 heads, hdim 128, page 16, shuffled block table) at reduced batch/context
     dtype = torch.bfloat16
