@@ -72,9 +72,9 @@ struct Sm100Dev {
     const int32_t* seqlen_k32;
     const int64_t* cache_batch_idx;
     int page, bt_stride;
-    // split mode (FmhaFwdSplitKV with several query rows per kv head): work item = (sequence, kv head, piece of
-    // `piece_tiles` key tiles); its Q tile holds the (token, group head) rows of that kv head; the result is split
-    // `piece` of the caller's fp32 workspaces
+    // split mode (FmhaFwdSplitKV with several query rows per kv head): work item = (sequence, kv head, 128-row block,
+    // run of key tiles); its Q tile holds the (token, group head) rows of that kv head; the result is one split of the
+    // caller's fp32 workspaces.  `piece_tiles` is the shortest piece the work is cut into.
     float* o_acc;
     float* lse_acc;
     int num_splits, piece_tiles, group, sq_cap;
@@ -221,6 +221,7 @@ struct Ctrl {
     uint64_t q_full, q_empty;
     uint64_t k_full[3], k_empty[3], v_full[KV_SLOTS], v_empty[KV_SLOTS];  // (the split modes use a third K slot)
     uint64_t s_full[2], p_full[2], o_full[2];
+    uint64_t pv_done[2];  // split modes: the PV that read S/P buffer b is complete (buffer b may take the next S)
     uint32_t tmem_base;
     int abort_flag;
     int num_levels;                     // row-block indices 0 .. num_levels-1
@@ -228,6 +229,8 @@ struct Ctrl {
     int nblk[kMaxBatch];                // row blocks of each sequence
     int seq_q0[kMaxBatch], seq_sq[kMaxBatch], seq_k0[kMaxBatch], seq_sk[kMaxBatch];  // first row / length, Q and K
     uint32_t items[kMaxRounds];         // this CTA's work list: valid << 31 | sequence << 22 | head index << 12 | row block
+    uint32_t items2[kMaxRounds];        // split modes: first key tile << 16 | key tiles of the item
+    int split_w, split_items;           // split modes: length of a CTA's piece of the work stream; items of this CTA
 };
 
 // Item taken by CTA `cta` in round `rnd` of a grid of `g` CTAs: rounds alternate direction (snake order), so that
@@ -239,24 +242,33 @@ __device__ __forceinline__ int item_of_round(int rnd, int cta, int g) {
 // Work items are ordered by decreasing row-block index (under a causal mask: decreasing cost), then by sequence,
 // then by head, so that the q heads of a GQA group -- which read the same K/V -- run at the same time on
 // neighbouring SMs and share those tiles through L2.  Warp-collective.
-// Split mode: items are numbered sequence by sequence (level_start holds the prefix), inside a sequence piece by
-// piece, then kv head, then 128-row block of the packed (token, group head) rows.
-__device__ __forceinline__ uint32_t find_item_split(const Ctrl* ctrl, const Sm100Dev& p, int w) {
-    int lo = 0, hi = p.batch;  // last sequence whose first item is <= w
-    while (hi - lo > 1) {
-        const int mid = (lo + hi) >> 1;
-        if (ctrl->level_start[mid] <= w) lo = mid; else hi = mid;
+// Split modes.  A stream is the key tiles one (sequence, 128-row block of the packed rows, kv head) needs; all streams,
+// in that order, each preceded by kItemCost units that stand for an item's fixed cost (Q load, pipeline fill, epilogue),
+// form one line that is cut into equal pieces of split_w units, one per CTA, so that the SMs finish together whatever
+// the lengths are.  The part of a stream inside one CTA's piece is a work item and one split of the result; a stream
+// cut k times uses splits 0..k.  split_w is raised where needed so that no stream needs more splits than the
+// workspace has; with a single split per stream the whole stream goes to the CTA its start falls to.
+constexpr int kItemCost = 3;
+
+// key tiles the rows of row block `rb` of a sequence see
+__device__ __forceinline__ int split_stream_tiles(const Sm100Dev& p, int sq, int sk, int rb) {
+    const int first_tok = rb * BM / p.group;
+    if (first_tok >= sq || sk <= 0) return 0;
+    int hi_key = sk - 1;
+    if (p.causal) {
+        const int last_tok = min(sq, (rb * BM + BM + p.group - 1) / p.group) - 1;
+        hi_key = min(hi_key, last_tok + ((p.causal == 2) ? sk - sq : 0));
     }
-    const int b = lo;
-    const int rb_cnt = (ctrl->seq_sq[b] * p.group + BM - 1) / BM;
-    const int per_piece = p.hkv * rb_cnt;
-    const int rem = w - ctrl->level_start[b];
-    const int piece = rem / per_piece, r2 = rem - piece * per_piece;
-    const int kh = r2 / rb_cnt, rb = r2 - kh * rb_cnt;
-    return 0x80000000u | ((uint32_t)b << 22) | ((uint32_t)kh << 12) | ((uint32_t)piece << 4) | (uint32_t)rb;
+    return hi_key >= 0 ? hi_key / BN + 1 : 0;
 }
 
-__device__ __forceinline__ void expand_item_split(const Ctrl* ctrl, const Sm100Dev& p, uint32_t packed, Item& it) {
+// splits a stream of n tiles starting at unit g0 of the line uses (pieces; the mode with duplicated rows writes two per piece)
+__device__ __forceinline__ int split_stream_pieces(int g0, int n, int w, int max_pieces) {
+    if (n == 0 || max_pieces == 1) return 1;
+    return (g0 + kItemCost + n - 1) / w - (g0 + kItemCost) / w + 1;
+}
+
+__device__ __forceinline__ void expand_item_split(const Ctrl* ctrl, const Sm100Dev& p, uint32_t packed, uint32_t packed2, Item& it) {
     it.valid = packed >> 31;
     const int b = (packed >> 22) & 0x1ff, kh = (packed >> 12) & 0x3ff, piece = (packed >> 4) & 0xff, rb = packed & 0xf;
     it.b = b;
@@ -270,20 +282,10 @@ __device__ __forceinline__ void expand_item_split(const Ctrl* ctrl, const Sm100D
     it.row0[0] = rb * BM;    // first packed row (token * group + group head)
     it.row0[1] = 0x3fffffff; // tile 1 does not exist
     it.shift = (p.causal == 2) ? it.sk - it.sq : 0;
-    it.n0 = piece * p.piece_tiles;
-    int n = 0;
-    const int first_tok = it.row0[0] / p.group;
-    if (first_tok < it.sq && it.sk > 0) {
-        int hi_key = it.sk - 1;
-        if (p.causal) {
-            const int last_tok = min(it.sq, (it.row0[0] + BM + p.group - 1) / p.group) - 1;
-            hi_key = min(hi_key, last_tok + it.shift);
-        }
-        if (hi_key >= 0) n = max(0, min(it.n0 + p.piece_tiles, hi_key / BN + 1) - it.n0);
-    }
-    it.nt[0] = n;
+    it.n0 = (int)(packed2 >> 16);
+    it.nt[0] = (int)(packed2 & 0xffffu);
     it.nt[1] = 0;
-    it.N = n;
+    it.N = it.nt[0];
 }
 
 __device__ __forceinline__ uint32_t find_item(const Ctrl* ctrl, const Sm100Dev& p, int w, int lane) {
@@ -359,7 +361,7 @@ __device__ __forceinline__ void expand_item(const Ctrl* ctrl, const Sm100Dev& p,
 // The work item of round `rnd` of this CTA, from the table filled at start-up.
 template <int SPLIT = 0>
 __device__ __forceinline__ void get_item(const Ctrl* ctrl, const Sm100Dev& p, int rnd, int total_items, int lane, Item& it) {
-    if (SPLIT) expand_item_split(ctrl, p, ctrl->items[rnd], it);
+    if (SPLIT) expand_item_split(ctrl, p, ctrl->items[rnd], ctrl->items2[rnd], it);
     else expand_item(ctrl, p, ctrl->items[rnd], it);
 }
 
@@ -406,6 +408,7 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
             mbar_init(&ctrl->s_full[i], 1);
             mbar_init(&ctrl->p_full[i], 4);  // one arrival per softmax warp
             mbar_init(&ctrl->o_full[i], 1);
+            mbar_init(&ctrl->pv_done[i], 1);
         }
         ctrl->abort_flag = 0;
         ctrl->num_levels = p.num_levels;
@@ -446,38 +449,80 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         ctrl->seq_k0[b] = (int)k0;
         ctrl->seq_sk[b] = sk;
         const int rows_per_block = p.pair_heads ? BM : 2 * BM;
-        if (SPLIT) {  // pieces = splits in use; more than the workspace has means a length beyond the stated capacity
-            int pieces = ((sk + BN - 1) / BN + p.piece_tiles - 1) / p.piece_tiles;
-            if (pieces > p.num_splits / (SPLIT == 2 ? 2 : 1)) {
-                pieces = p.num_splits / (SPLIT == 2 ? 2 : 1);
-                atomicOr(p.status, 0x10000000);
+        if (SPLIT) {  // units of the work line this sequence takes, and its longest stream
+            const int rbc = (sq * p.group + BM - 1) / BM;
+            int cost = 0, nmax = 0;
+            for (int rb = 0; rb < rbc; ++rb) {
+                const int n = split_stream_tiles(p, sq, sk, rb);
+                cost += n + kItemCost;
+                nmax = max(nmax, n);
             }
-            ctrl->nblk[b] = pieces;  // (with duplicated rows every piece is two splits; see the users of nblk)
+            ctrl->nblk[b] = cost * p.hkv;
+            ctrl->items2[b] = (uint32_t)nmax;  // (scratch until the work list is written)
         }
         else ctrl->nblk[b] = min(p.num_levels, (sq + rows_per_block - 1) / rows_per_block);
     }
     __syncthreads();
     if (SPLIT) {
-        if (threadIdx.x == 0) {  // first item of every sequence
-            int run = 0;
+        constexpr int kDup = SPLIT == 2 ? 2 : 1;  // splits per piece
+        const int max_pieces = max(1, p.num_splits / kDup);
+        if (threadIdx.x == 0) {  // first unit of every sequence; length of a CTA's piece
+            int run = 0, nmax = 0;
             for (int b = 0; b < p.batch; ++b) {
                 ctrl->level_start[b] = run;
-                run += ctrl->nblk[b] * p.hkv * ((ctrl->seq_sq[b] * p.group + BM - 1) / BM);
+                run += ctrl->nblk[b];
+                nmax = max(nmax, (int)ctrl->items2[b]);
             }
             ctrl->level_start[p.batch] = run;
+            int w = max((run + (int)gridDim.x - 1) / (int)gridDim.x, p.piece_tiles + kItemCost);
+            if (max_pieces >= 2) w = max(w, (nmax + max_pieces - 2) / (max_pieces - 1));  // ceil(n / w) + 1 <= max_pieces
+            ctrl->split_w = w;
         }
-        // splits a sequence does not use: LSE = -inf, so that the merge gives them no weight
-        if (p.lse_acc) {
-            for (int b = blockIdx.x; b < p.batch; b += gridDim.x) {
-                const int used = ctrl->nblk[b] * (SPLIT == 2 ? 2 : 1), sq = ctrl->seq_sq[b], q0 = ctrl->seq_q0[b];
-                const int cnt = (p.num_splits - used) * p.hq * sq;
-                for (int e = threadIdx.x; e < cnt; e += NTHREADS) {
-                    const int s = used + e / (p.hq * sq), rem = e % (p.hq * sq), h = rem / sq, i = rem - h * sq;
-                    const int64_t slot = p.seqstart_q ? ((int64_t)h * p.num_splits + s) * p.total_q + q0 + i
-                                                      : (((int64_t)b * p.hq + h) * p.num_splits + s) * p.sq_cap + i;
-                    p.lse_acc[slot] = -INFINITY;
+        __syncthreads();
+        const int w = ctrl->split_w;
+        if (threadIdx.x == 0) {
+            // this CTA's work list: the streams that reach into units [lo, hi) of the line
+            const int lo = (int)blockIdx.x * w, hi = lo + w, total = ctrl->level_start[p.batch];
+            int cnt = 0;
+            bool overflow = false;
+            if (lo < total) {
+                int b = 0, bh = p.batch;  // last sequence that starts at or before lo
+                while (bh - b > 1) {
+                    const int mid = (b + bh) >> 1;
+                    if (ctrl->level_start[mid] <= lo) b = mid; else bh = mid;
+                }
+                for (; b < p.batch && ctrl->level_start[b] < hi; ++b) {
+                    const int sq = ctrl->seq_sq[b], sk = ctrl->seq_sk[b];
+                    const int rbc = (sq * p.group + BM - 1) / BM;
+                    int seg0 = ctrl->level_start[b];
+                    for (int rb = 0; rb < rbc && seg0 < hi; ++rb) {
+                        const int n = split_stream_tiles(p, sq, sk, rb), c = n + kItemCost;
+                        const int kh_lo = max(0, (lo - seg0) / c), kh_hi = min(p.hkv - 1, (hi - 1 - seg0) / c);
+                        for (int kh = kh_lo; kh <= kh_hi; ++kh) {
+                            const int g0 = seg0 + kh * c;
+                            int t_lo = 0, t_hi = n, piece = 0;
+                            if (n == 0 || max_pieces == 1) {
+                                if (g0 < lo) continue;  // the whole stream belongs to the CTA its start falls to
+                            } else {
+                                t_lo = max(0, lo - g0 - kItemCost);
+                                t_hi = min(n, hi - g0 - kItemCost);
+                                if (t_hi <= t_lo) continue;
+                                piece = (int)blockIdx.x - (g0 + kItemCost) / w;
+                            }
+                            if (cnt >= kMaxRounds) { overflow = true; break; }
+                            ctrl->items[cnt] = 0x80000000u | ((uint32_t)b << 22) | ((uint32_t)kh << 12) | ((uint32_t)piece << 4) | (uint32_t)rb;
+                            ctrl->items2[cnt] = ((uint32_t)t_lo << 16) | (uint32_t)(t_hi - t_lo);
+                            ++cnt;
+                        }
+                        seg0 += p.hkv * c;
+                    }
                 }
             }
+            if (overflow) {  // the host checks an upper bound of this; never silently drop work
+                atomicOr(p.status, 0x20000000);
+                cnt = 0;
+            }
+            ctrl->split_items = cnt;
         }
     }
     for (int lv = threadIdx.x; !SPLIT && lv < p.num_levels; lv += NTHREADS) {  // count of sequences that have block index lv
@@ -498,15 +543,15 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = ctrl->tmem_base;
-    const int total_items = SPLIT ? ctrl->level_start[p.batch] : ctrl->level_start[p.num_levels];
-    int rounds = (total_items + (int)gridDim.x - 1) / (int)gridDim.x;
+    const int total_items = SPLIT ? 0 : ctrl->level_start[p.num_levels];
+    int rounds = SPLIT ? ctrl->split_items : (total_items + (int)gridDim.x - 1) / (int)gridDim.x;
     if (rounds > kMaxRounds) {  // the host checks an upper bound of this; never silently drop work
         if (threadIdx.x == 0) atomicOr(p.status, 0x20000000);
         rounds = 0;
     }
-    for (int rnd = warp; rnd < rounds; rnd += NTHREADS / 32) {  // this CTA's work list
+    for (int rnd = warp; !SPLIT && rnd < rounds; rnd += NTHREADS / 32) {  // this CTA's work list
         const int w = item_of_round(rnd, blockIdx.x, gridDim.x);
-        const uint32_t packed = w >= total_items ? 0u : (SPLIT ? find_item_split(ctrl, p, w) : find_item(ctrl, p, w, lane));
+        const uint32_t packed = w >= total_items ? 0u : find_item(ctrl, p, w, lane);
         if (lane == 0) ctrl->items[rnd] = packed;
     }
     __syncthreads();
@@ -693,15 +738,37 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                     umma_ss(tS[0] + buf * 128, dQ0 + off, kd + off, idesc_qk, ks > 0 ? 1u : 0u);
                 }
             };
-            auto issue_pv_from = [&](uint32_t buf, int s, bool accumulate) {
-                const uint64_t vd = s ? dV1 : dV0;
-#pragma unroll
-                for (int ks = 0; ks < BN / 16; ++ks)
-                    umma_ts(tO[0], tS[0] + buf * 128 + ks * 8, vd + (uint64_t)((ks * 2048) >> 4), idesc_pv, (accumulate || ks > 0) ? 1u : 0u);
-            };
             // running counts give ring slots and barrier parities across work items
             uint32_t kv_cnt = 0, q_cnt = 0, sc0 = 0, sc1 = 0;
-            if (lane == 0) {  // the whole loop is one thread's; an item with N == 0 is skipped by every role
+            if (SPLIT && lane == 0) {
+                // Split modes: this thread issues only the QK^T, warp 4's first thread the PV (the warps of tile 1's
+                // softmax warpgroup have nothing else to do there).  Each polls its own barriers while the other's
+                // block of MMAs runs, which a single issuer could not do (the tensor pipe takes instructions only about
+                // one ahead).  The two S buffers are handed back by pv_done: S of step g goes into buffer g & 1 once
+                // the PV of step g - 2, which read P from it, is complete.
+                for (int rnd = 0; rnd < rounds; ++rnd) {
+                    Item it;
+                    get_item<SPLIT>(ctrl, p, rnd, total_items, lane, it);
+                    if (!it.valid || it.N == 0) continue;
+                    const int N = it.N;
+                    bool ok = mbar_wait_bounded(&ctrl->q_full, q_cnt & 1u, abort_flag, p.status, 0x40);
+                    for (int n = 0; ok && n < N; ++n) {
+                        const uint32_t kc = kv_cnt + n, g = sc0 + n, b = g & 1u;
+                        const int s = kc % KS;
+                        if (!(ok = mbar_wait_bounded(&ctrl->k_full[s], (kc / KS) & 1u, abort_flag, p.status, 0x41))) break;
+                        if (g >= 2 && !(ok = mbar_wait_bounded(&ctrl->pv_done[b], ((g >> 1) + 1u) & 1u, abort_flag, p.status, 0x44))) break;
+                        tc_fence_after();
+                        issue_qk_to(b, s);
+                        umma_commit(&ctrl->s_full[b]);
+                        umma_commit(&ctrl->k_empty[s]);
+                        if (n + 1 == N) umma_commit(&ctrl->q_empty);  // Q may be replaced once these MMAs are done
+                    }
+                    if (!ok) break;
+                    kv_cnt += N;
+                    sc0 += N;
+                    ++q_cnt;
+                }
+            } else if (lane == 0) {  // the whole loop is one thread's; an item with N == 0 is skipped by every role
                 int N = 0, N0 = 0, N1 = 0;
                 if (rounds > 0) {
                     Item it;
@@ -715,13 +782,7 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                         const int s0 = kv_cnt % KS;
                         ok = mbar_wait_bounded(&ctrl->q_full, q_cnt & 1u, abort_flag, p.status, 0x40) &&
                              mbar_wait_bounded(&ctrl->k_full[s0], (kv_cnt / KS) & 1u, abort_flag, p.status, 0x41);
-                        if (ok && SPLIT) {  // S buffers alternate with the step (sc0 counts the steps so far)
-                            tc_fence_after();
-                            issue_qk_to(sc0 & 1u, s0);
-                            umma_commit(&ctrl->s_full[sc0 & 1u]);
-                            umma_commit(&ctrl->k_empty[s0]);
-                            if (N == 1) umma_commit(&ctrl->q_empty);
-                        } else if (ok) {
+                        if (ok) {
                             tc_fence_after();
                             if (N0 > 0) { issue_qk(0, s0); umma_commit(&ctrl->s_full[0]); }
                             if (N1 > 0) { issue_qk(1, s0); umma_commit(&ctrl->s_full[1]); }
@@ -738,25 +799,6 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                             const uint32_t kc = kv_cnt + n;
                             const int s = kc % KV_SLOTS, s1 = (kc + 1) % KS;           // V slot of this step, K slot of the next
                             const uint32_t ph = (kc / KV_SLOTS) & 1u, ph1 = ((kc + 1) / KS) & 1u;
-                            if (SPLIT) {
-                                const uint32_t g = sc0 + n;
-                                if (n + 1 < N) {  // S of the next step, into the other buffer, ahead of this step's PV
-                                    if (!(ok = mbar_wait_bounded(&ctrl->k_full[s1], ph1, abort_flag, p.status, 0x44))) break;
-                                    tc_fence_after();
-                                    issue_qk_to((g + 1u) & 1u, s1);
-                                    umma_commit(&ctrl->s_full[(g + 1u) & 1u]);
-                                    umma_commit(&ctrl->k_empty[s1]);
-                                    if (n + 2 == N) umma_commit(&ctrl->q_empty);
-                                }
-                                if (!(ok = mbar_wait_bounded(&ctrl->v_full[s], ph, abort_flag, p.status, 0x42))) break;
-                                if (!(ok = mbar_wait_bounded(&ctrl->p_full[g & 1u], (g >> 1) & 1u, abort_flag, p.status, 0x43))) break;
-                                tc_fence_after();
-                                issue_pv_from(g & 1u, s, n > 0);
-                                if (n + 2 == N) umma_commit(&ctrl->o_full[1]);  // the last PV but one is done
-                                if (n + 1 == N) umma_commit(&ctrl->o_full[0]);
-                                umma_commit(&ctrl->v_empty[s]);
-                                continue;
-                            }
                             if (!(ok = mbar_wait_bounded(&ctrl->v_full[s], ph, abort_flag, p.status, 0x42))) break;
                             if (n < N0) {
                                 if (!(ok = mbar_wait_bounded(&ctrl->p_full[0], (sc0 + n) & 1u, abort_flag, p.status, 0x43))) break;
@@ -802,8 +844,69 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         const uint32_t lane_addr = tmem + ((uint32_t)((warp & 3) * 32) << 16);
         const uint32_t tS = lane_addr + i * 128, tO = lane_addr + 256 + i * 128;
         uint32_t sc = 0, oc = 0;  // S tiles and O accumulators consumed so far (barrier parities)
-        uint32_t oc1 = 0;         // split modes: items with two or more steps so far (parity of the o_full[1] commits)
         bool ok = true;
+        if (SPLIT && i == 1) {
+            // Split modes have no second Q tile; the first thread of this warpgroup issues the PV products instead
+            // (the QK^T come from warp 8): O += P V from S/P buffer g & 1 once V has landed and the softmax has
+            // handed P over, then pv_done tells the softmax (which may rescale O) and the QK^T issuer (which may
+            // overwrite the buffer) that this product is complete.
+            if (warp == 4 && lane == 0) {
+                constexpr uint32_t idesc_pv = make_idesc<T>(true);
+                const uint64_t dV0 = make_smem_desc(smem_u32(sV), HALF_BYTES, 1024);
+                const uint64_t dV1 = make_smem_desc(smem_u32(sV + TILE_BYTES), HALF_BYTES, 1024);
+                uint32_t kv_cnt = 0, g = 0;
+                for (int rnd = 0; ok && rnd < rounds; ++rnd) {
+                    Item it;
+                    get_item<SPLIT>(ctrl, p, rnd, total_items, lane, it);
+                    if (!it.valid || it.N == 0) continue;
+                    const int N = it.N;
+                    for (int n = 0; n < N; ++n, ++g) {
+                        const uint32_t kc = kv_cnt + n, b = g & 1u;
+                        const int s = kc % KV_SLOTS;
+                        if (!(ok = mbar_wait_bounded(&ctrl->v_full[s], (kc / KV_SLOTS) & 1u, abort_flag, p.status, 0x42))) break;
+                        if (!(ok = mbar_wait_bounded(&ctrl->p_full[b], (g >> 1) & 1u, abort_flag, p.status, 0x43))) break;
+                        tc_fence_after();
+                        const uint64_t vd = s ? dV1 : dV0;
+#pragma unroll
+                        for (int ks = 0; ks < BN / 16; ++ks)
+                            umma_ts(tmem + 256, tmem + b * 128 + ks * 8, vd + (uint64_t)((ks * 2048) >> 4), idesc_pv,
+                                    (n > 0 || ks > 0) ? 1u : 0u);
+                        umma_commit(&ctrl->pv_done[b]);
+                        if (n + 1 == N) umma_commit(&ctrl->o_full[0]);
+                        umma_commit(&ctrl->v_empty[s]);
+                    }
+                    kv_cnt += N;
+                }
+            }
+            else if (warp > 4 && p.lse_acc) {
+                // (warps 5-7, while the others work) splits a stream does not use: LSE = -inf, so that the merge gives
+                // them no weight
+                constexpr int kDup = SPLIT == 2 ? 2 : 1;
+                const int max_pieces = max(1, p.num_splits / kDup), w = ctrl->split_w;
+                for (int b = blockIdx.x; b < p.batch; b += gridDim.x) {
+                    const int sq = ctrl->seq_sq[b], sk = ctrl->seq_sk[b], q0 = ctrl->seq_q0[b];
+                    const int rbc = (sq * p.group + BM - 1) / BM;
+                    int seg0 = ctrl->level_start[b];
+                    for (int rb = 0; rb < rbc; ++rb) {
+                        const int n = split_stream_tiles(p, sq, sk, rb), c = n + kItemCost;
+                        const int rows = min(BM, sq * p.group - rb * BM);
+                        for (int kh = 0; kh < p.hkv; ++kh) {
+                            const int used = split_stream_pieces(seg0 + kh * c, n, w, max_pieces) * kDup;
+                            const int cnt = (p.num_splits - used) * rows;
+                            for (int e = (int)threadIdx.x - 160; e < cnt; e += 96) {
+                                const int sp = used + e / rows, pr = rb * BM + e % rows;
+                                const int tok = pr / p.group, h = kh * p.group + (pr - tok * p.group);
+                                const int64_t slot = p.seqstart_q ? ((int64_t)h * p.num_splits + sp) * p.total_q + q0 + tok
+                                                                  : (((int64_t)b * p.hq + h) * p.num_splits + sp) * p.sq_cap + tok;
+                                p.lse_acc[slot] = -INFINITY;
+                            }
+                        }
+                        seg0 += p.hkv * c;
+                    }
+                }
+            }
+            ok = false;  // nothing else for this warpgroup
+        }
         for (int rnd = 0; ok && rnd < rounds; ++rnd) {
             Item it;
             get_item<SPLIT>(ctrl, p, rnd, total_items, lane, it);
@@ -873,14 +976,9 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                 if (n > 0 && __any_sync(0xffffffffu, grow)) {
                     if (SPLIT) {
                         // O must be at rest: the PV of step n-1 may still be running, S of this step was computed ahead
-                        // of it.  The QK^T of step n+1 is issued behind that PV and the pipe runs in order, so the next
-                        // S being ready tells that it is over; the last step has no next S and waits for the commit
-                        // the issuer makes behind the item's last PV but one.
-                        if (n + 1 < Ni)
-                            ok = __all_sync(0xffffffffu, mbar_wait_bounded(&ctrl->s_full[sb ^ 1], ((gstep + 1u) >> 1) & 1u,
-                                                                           abort_flag, p.status, 0x1000));
-                        else
-                            ok = __all_sync(0xffffffffu, mbar_wait_bounded(&ctrl->o_full[1], oc1 & 1u, abort_flag, p.status, 0x2000));
+                        // of it.
+                        ok = __all_sync(0xffffffffu, mbar_wait_bounded(&ctrl->pv_done[sb ^ 1], ((gstep - 1u) >> 1) & 1u,
+                                                                       abort_flag, p.status, 0x1000));
                         if (!ok) break;
                         tc_fence_after();
                     }
@@ -941,7 +1039,6 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
             }
             if (!ok) break;
             sc += Ni;
-            if (SPLIT && Ni >= 2) ++oc1;
             // ---- epilogue: O / l and LSE ----
             if (Ni > 0) {
                 ok = __all_sync(0xffffffffu, mbar_wait_bounded(&ctrl->o_full[i], oc & 1u, abort_flag, p.status, 0x400 << i));
@@ -1208,10 +1305,6 @@ int64_t split_cap_tiles(const SplitKVParams& p) {  // key tiles of the longest s
 bool split_duplicates_rows(const SplitKVParams& p) {
     return p.max_seqlen_q * (p.hq / p.hkv) <= 64 && p.num_splits >= 2;
 }
-int64_t split_piece_tiles(const SplitKVParams& p) {  // key tiles per work item, so that the splits fit num_splits
-    const int64_t slots = split_duplicates_rows(p) ? p.num_splits / 2 : p.num_splits;
-    return std::max<int64_t>(kMinPieceTiles, (split_cap_tiles(p) + slots - 1) / slots);
-}
 
 template <typename T, int SPLIT>
 int launch_split_t(const SplitKVParams& p, const Sm100Dev& dev, cudaStream_t stream) {
@@ -1254,11 +1347,14 @@ bool splitkv_sm100_supported(const SplitKVParams& p) {
         return false;
     }
     if (p.num_splits > 1 && !p.lse_acc) return false;
+    if (p.num_splits > 255) return false;  // the split index of a work item has 8 bits
+    // The work line (see kItemCost) is indexed with 31 bits, an item's first tile and tile count with 16 each, and a
+    // CTA's work list holds kMaxRounds items: a CTA's piece of w units reaches into at most w / kItemCost + 2 streams.
     const int64_t cap_tiles = split_cap_tiles(p);
-    const int64_t piece = split_piece_tiles(p);
-    if ((cap_tiles + piece - 1) / piece > 255) return false;
-    const int64_t items = p.batch * p.hkv * ((p.max_seqlen_q * group + BM - 1) / BM) * ((cap_tiles + piece - 1) / piece);
-    if ((items + sm_count() - 1) / sm_count() > kMaxRounds) return false;
+    const int64_t streams = p.batch * p.hkv * ((p.max_seqlen_q * group + BM - 1) / BM);
+    const int64_t line = streams * (cap_tiles + kItemCost);
+    if (cap_tiles > 0xffff || line >= (1ll << 31)) return false;
+    if (streams > kMaxRounds - 2 && (line / sm_count() + 1) / kItemCost + 2 > kMaxRounds) return false;
     const int64_t tokens = p.seqstart_q ? p.total_q : p.batch * p.seqlen_q;
     if (tokens >= (1ll << 31) || (!p.block_table && p.batch * p.seqlen_k_cap >= (1ll << 31))) return false;
     return true;
@@ -1279,7 +1375,7 @@ int launch_splitkv_sm100(const SplitKVParams& p, cudaStream_t stream) {
     dev.page = p.block_table ? (int)p.page : BN;
     dev.bt_stride = (int)p.bt_stride;
     dev.o_acc = p.o_acc; dev.lse_acc = p.lse_acc; dev.num_splits = (int)p.num_splits;
-    dev.piece_tiles = (int)split_piece_tiles(p);
+    dev.piece_tiles = kMinPieceTiles;
     dev.group = (int)(p.hq / p.hkv);
     dev.sq_cap = (int)p.seqlen_q;
     dev.causal = p.mask_type; dev.wl = -1; dev.wr = p.mask_type ? 0 : -1;
