@@ -367,7 +367,10 @@ __device__ __forceinline__ void get_item(const Ctrl* ctrl, const Sm100Dev& p, in
 
 // WINDOW: the mask has a left window or a right window other than 0 (everything but no mask / causal); a separate
 // instance, so that the common masks do not carry the second bound of the visible range through the softmax loop.
-// SPLIT 1: the split-KV form described at Sm100Dev (one Q tile per item, tile 1 unused).
+// SPLIT 1: the split-KV form described at Sm100Dev (one Q tile per item; work cut as described at kItemCost).  The S
+//          columns of tile 1 are a second S buffer, its Q room a third K slot; K, V and Q have a producer warp each
+//          (9, 10, 11); warp 8 issues the QK^T, the first thread of warp 4 the PV products, warps 5-7 write LSE = -inf
+//          to the splits no work item fills.
 // SPLIT 2: the same for at most 64 packed rows: the rows are loaded twice (tile rows 0-63 and 64-127); the copy in rows
 //          0-63 takes keys 0-63 of every 128-key tile, the copy in rows 64-127 takes keys 64-127, each as a split of its
 //          own (2 * piece, 2 * piece + 1).  Every softmax thread then handles 64 columns instead of 128 with half of the

@@ -431,6 +431,27 @@ def test_splitkv_many_query_rows_batch_mode_paged_cache_batch_idx_and_top_left_m
     assert_lse_close(lse, lse_ref, "contiguous cache with cache_batch_idx")
 
 
+@pytest.mark.parametrize("num_splits", [1, 2, 3, 4, 16])
+@pytest.mark.parametrize("sq", [8, 40])
+def test_splitkv_many_query_rows_long_stream_and_few_splits(num_splits, sq):
+    """One context far longer than a CTA's share of the work: its key tiles are cut over many CTAs, and the number of
+    cuts is bounded by the splits the workspace has (a single split: the whole stream stays in one CTA; two pieces: one
+    cut; 16 splits: as many as fit).  sq = 8 gives 32 packed rows (the form with duplicated rows, two splits per piece),
+    sq = 40 gives 160 (two row blocks, one split per piece)."""
+    dtype = torch.bfloat16
+    hq, hkv, d, page = 8, 2, 128, 64
+    lens_k = [40000, 5000, 300]
+    cache = make_paged_cache(lens_k, hkv, d, d, page, dtype, seed=29)
+    q = normal_tensor((len(lens_k), sq, hq, d), dtype, 97)
+    o_ref, lse_ref = oracle.fmha_fwd(q, cache.k, cache.v, seqlen_k=cache.seqlen_k, block_table=cache.block_table,
+                                     mask_type=2, window=(-1, 0))
+    o, lse = ops.fmha_fwd_splitkv(_cu(q), _cu(cache.k), _cu(cache.v), seqlen_k=_cu(cache.seqlen_k),
+                                  block_table=_cu(cache.block_table), num_splits=num_splits, causal=True, return_lse=True)
+    assert _lib.device_status() == 0
+    assert_o_close(o, o_ref)
+    assert_lse_close(lse, lse_ref)
+
+
 def test_splitkv_config3_small():
     # BASELINE config 3 geometry (32/8 heads, hdim 128, page 16, shuffled block table) at reduced batch/context
     dtype = torch.bfloat16
