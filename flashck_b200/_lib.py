@@ -22,6 +22,7 @@ SIGNATURES = {
     "FlashckVersion": ([], ctypes.c_char_p),
     "FlashckDeviceStatus": ([ctypes.POINTER(ctypes.c_int)], _I),
     "FmhaFwd": ([_P] * 8 + [_I64] * 8 + [_F, _I64, _I64, _U32, _P, _P, _I], _I),
+    "FmhaFwdBias": ([_P] * 8 + [_I64] * 8 + [_F, _I64, _I64, _U32, _P, _P, _I, _I, _I, _F], _I),
     "FmhaFwdBatchPrefill": ([_P] * 9 + [_I64] * 9 + [_F, _I64, _I64, _U32, _P, _P, _I], _I),
     "FmhaFwdPagedKVPrefill": ([_P] * 9 + [_I64] * 9 + [_F, _I64, _I64, _U32, _P, _P, _I], _I),
     "FmhaFwdSplitKV": ([_P] * 11 + [_I64] * 11 + [_F, _I64, _I64, _U32, _P, _I], _I),

@@ -7,6 +7,7 @@
 #include <stdio.h>
 #include <string.h>
 
+#include <atomic>
 #include <mutex>
 
 #include "kernels.h"
@@ -81,6 +82,9 @@ PFN_encodeTiled get_encode_tiled() {
 
 namespace {
 
+// how FmhaFwd reads a non-null bias pointer (the reference fixes both per compiled instance)
+std::atomic<int64_t> g_bias_enum{1}, g_bias_rank_info{0};
+
 int check_common(const char* fn, int dtype, int64_t hq, int64_t hkv, int64_t d, int64_t dv, const void* bias) {
     FCK_REQUIRE(dtype == FLASHCK_DTYPE_FLOAT16 || dtype == FLASHCK_DTYPE_BFLOAT16, FLASHCK_ERR_UNSUPPORTED,
                 "%s: dtype must be 3 (float16) or 4 (bfloat16), got %d", fn, dtype);
@@ -128,8 +132,26 @@ int FmhaFwd(void* q, void* k, void* v, void* bias, void* o, int64_t* q_seq_start
             int64_t* k_seq_len, int64_t batch, int64_t q_seq_len, int64_t kv_seq_len, int64_t hq, int64_t hkv,
             int64_t d, int64_t dv, int64_t q_max_seq_len, float scale, int64_t window_left, int64_t window_right,
             uint32_t mask_type, void* stream, void* lse, int dtype) {
-    int rc = check_common("FmhaFwd", dtype, hq, hkv, d, dv, bias);
+    // The reference fixes the kind of bias per compiled instance (bias_enum, bias_rank_info); here the instance
+    // parameters of the fmha_fwd family say how a non-null bias pointer is read.
+    return FmhaFwdBias(q, k, v, bias, o, q_seq_start, k_seq_start, k_seq_len, batch, q_seq_len, kv_seq_len, hq, hkv, d, dv,
+                       q_max_seq_len, scale, window_left, window_right, mask_type, stream, lse, dtype,
+                       bias ? (int)g_bias_enum.load() : 0, (int)g_bias_rank_info.load(), 0.f);
+}
+
+int FmhaFwdBias(void* q, void* k, void* v, void* bias, void* o, int64_t* q_seq_start, int64_t* k_seq_start,
+                int64_t* k_seq_len, int64_t batch, int64_t q_seq_len, int64_t kv_seq_len, int64_t hq, int64_t hkv,
+                int64_t d, int64_t dv, int64_t q_max_seq_len, float scale, int64_t window_left, int64_t window_right,
+                uint32_t mask_type, void* stream, void* lse, int dtype, int bias_enum, int bias_rank_info,
+                float logits_soft_cap) {
+    int rc = check_common("FmhaFwd", dtype, hq, hkv, d, dv, nullptr);
     if (rc) return rc;
+    FCK_REQUIRE(bias_enum >= 0 && bias_enum <= 2, FLASHCK_ERR_INVALID_ARGUMENT,
+                "FmhaFwd: bias_enum must be 0 (none), 1 (elementwise) or 2 (alibi), got %d", bias_enum);
+    FCK_REQUIRE(bias_enum == 0 || bias != nullptr, FLASHCK_ERR_INVALID_ARGUMENT, "FmhaFwd: bias_enum %d without a bias buffer", bias_enum);
+    FCK_REQUIRE(bias_rank_info >= 0 && bias_rank_info <= (bias_enum == 2 ? 1 : 2), FLASHCK_ERR_INVALID_ARGUMENT,
+                "FmhaFwd: bias_rank_info %d out of range for bias_enum %d", bias_rank_info, bias_enum);
+    FCK_REQUIRE(logits_soft_cap >= 0.f, FLASHCK_ERR_INVALID_ARGUMENT, "FmhaFwd: logits_soft_cap must be >= 0");
     FCK_REQUIRE(q && k && v && o, FLASHCK_ERR_INVALID_ARGUMENT, "FmhaFwd: q, k, v and o must not be null");
     FCK_REQUIRE(batch >= 0 && q_seq_len >= 0 && kv_seq_len >= 0, FLASHCK_ERR_INVALID_ARGUMENT, "FmhaFwd: negative size");
     FCK_REQUIRE(mask_type <= 3, FLASHCK_ERR_INVALID_ARGUMENT, "FmhaFwd: mask_type must be 0..3");
@@ -144,6 +166,8 @@ int FmhaFwd(void* q, void* k, void* v, void* bias, void* o, int64_t* q_seq_start
     p.max_seqlen_q = q_seq_start ? (q_max_seq_len > 0 ? q_max_seq_len : q_seq_len) : q_seq_len;
     p.scale = resolve_scale(scale, d);
     p.mask_type = (int)mask_type; p.wl = window_left; p.wr = window_right; p.dtype = dtype;
+    p.bias = bias_enum ? bias : nullptr; p.bias_type = bias_enum; p.bias_rank = bias_rank_info;
+    p.logits_soft_cap = logits_soft_cap;
     return run_fwd(p, (cudaStream_t)stream);
 }
 
@@ -312,6 +336,16 @@ int FmhaFwdAppendKV(void* q, void* k_cache, void* knew, void* v_cache, void* vne
 int FlashckSetInstanceParam(int family, const char* key, int64_t value) {
     FCK_REQUIRE(key != nullptr, FLASHCK_ERR_INVALID_ARGUMENT, "FlashckSetInstanceParam: null key");
     int rc = FLASHCK_ERR_INVALID_ARGUMENT;
+    if (family == 0 && !strcmp(key, "bias_enum")) {
+        FCK_REQUIRE(value >= 0 && value <= 2, FLASHCK_ERR_INVALID_ARGUMENT, "bias_enum must be 0, 1 or 2");
+        g_bias_enum = value;
+        return FLASHCK_OK;
+    }
+    if (family == 0 && !strcmp(key, "bias_rank_info")) {
+        FCK_REQUIRE(value >= 0 && value <= 2, FLASHCK_ERR_INVALID_ARGUMENT, "bias_rank_info must be 0, 1 or 2");
+        g_bias_rank_info = value;
+        return FLASHCK_OK;
+    }
     if (family == 0) rc = fwd_set_param(key, value);
     else if (family == 2) rc = !strcmp(key, "use_sm100_splitkv") ? fwd_set_param(key, value) : splitkv_set_param(key, value);
     if (rc) set_last_error("FlashckSetInstanceParam: unknown family/key %d/%s", family, key);
@@ -320,6 +354,8 @@ int FlashckSetInstanceParam(int family, const char* key, int64_t value) {
 int FlashckGetInstanceParam(int family, const char* key, int64_t* value_out) {
     FCK_REQUIRE(key != nullptr && value_out != nullptr, FLASHCK_ERR_INVALID_ARGUMENT, "FlashckGetInstanceParam: null argument");
     int rc = FLASHCK_ERR_INVALID_ARGUMENT;
+    if (family == 0 && !strcmp(key, "bias_enum")) { *value_out = g_bias_enum; return FLASHCK_OK; }
+    if (family == 0 && !strcmp(key, "bias_rank_info")) { *value_out = g_bias_rank_info; return FLASHCK_OK; }
     if (family == 0) rc = fwd_get_param(key, value_out);
     else if (family == 2) rc = !strcmp(key, "use_sm100_splitkv") ? fwd_get_param(key, value_out) : splitkv_get_param(key, value_out);
     if (rc) set_last_error("FlashckGetInstanceParam: unknown family/key %d/%s", family, key);

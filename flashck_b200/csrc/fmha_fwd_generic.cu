@@ -37,6 +37,13 @@ struct FwdDev {
     int batch, seqlen_q, seqlen_k, hq, hkv, total_q, bt_stride, page;
     int mask_type, wl, wr;
     float scale_log2;
+    // instances with score additions (template parameter EXTRA)
+    const void* bias;
+    int bias_type, bias_rank;
+    int64_t bias_sk;       // row stride of an elementwise bias (key length, packed total in group mode)
+    int64_t bias_sq;       // rows of one head's bias plane
+    float soft_cap;        // 0 = off
+    float scale;
 };
 
 // Row-major [rows][D] 16-bit tile; 16-byte chunk index XORed with (row & 7).
@@ -45,7 +52,10 @@ __device__ __forceinline__ uint32_t swz(int row, int chunk) {
     return (uint32_t)(row * (D * 2) + (((chunk & ~7) | ((chunk ^ row) & 7)) << 4));
 }
 
-template <typename T, int D>
+// EXTRA: the instance adds an elementwise bias or ALiBi to the scaled scores and/or soft-caps them (the reference
+// compiles these as separate kernel instances too: bias_enum and has_logits_soft_cap are part of the instance name,
+// core/profiling/attention/fmha_fwd/fmha_fwd_problem.h:59-64).
+template <typename T, int D, bool EXTRA>
 __global__ void __launch_bounds__(NWARP * 32)
 fmha_fwd_generic_kernel(const FwdDev p) {
     constexpr int CH = D / 8;                    // 16-byte chunks per row
@@ -139,6 +149,20 @@ fmha_fwd_generic_kernel(const FwdDev p) {
     visible_range(i0, sq, sk, p.mask_type, p.wl, p.wr, lo0, hi0);
     visible_range(i1, sq, sk, p.mask_type, p.wl, p.wr, lo1, hi1);
 
+    // score additions of this (sequence, head): first bias element of the sequence's block, or the head's slope
+    const T* bias_el = nullptr;
+    float alibi_slope = 0.f;
+    if (EXTRA && p.bias_type == 1) {
+        const int64_t plane = p.bias_sq * p.bias_sk;
+        const int64_t head_off = p.bias_rank >= 1 ? (int64_t)h * plane : 0;
+        const int64_t batch_off = (p.bias_rank == 2 && !p.seqstart_q) ? (int64_t)b * p.hq * plane : 0;
+        // group mode: the block of this sequence inside the packed [total_q, total_k] plane
+        const int64_t blk = p.seqstart_q ? q0 * p.bias_sk + (p.seqstart_k ? p.seqstart_k[b] : 0) : 0;
+        bias_el = (const T*)p.bias + batch_off + head_off + blk;
+    } else if (EXTRA && p.bias_type == 2) {
+        alibi_slope = ((const float*)p.bias)[(p.bias_rank >= 1 ? (int64_t)b * p.hq : 0) + h];
+    }
+
     for (int n = n_begin; n < n_end; ++n) {
         const int buf = (n - n_begin) & 1;
         __syncthreads();  // everyone is done with the buffer the next load overwrites
@@ -181,6 +205,17 @@ fmha_fwd_generic_kernel(const FwdDev p) {
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 float x = s[j][e] * p.scale_log2;
+                if (EXTRA) {
+                    const int key = k0 + j * 8 + qlane * 2 + (e & 1), row = (e < 2) ? i0 : i1;
+                    float y = s[j][e] * p.scale;
+                    if (p.soft_cap > 0.f) y = p.soft_cap * tanhf(y / p.soft_cap);
+                    if (p.bias_type == 1) {
+                        if (row < sq && key < sk) y += Elem<T>::to_f32(bias_el[(int64_t)row * p.bias_sk + key]);
+                    } else if (p.bias_type == 2) {
+                        y -= alibi_slope * fabsf((float)(row + sk - sq - key));
+                    }
+                    x = y * 1.4426950408889634f;
+                }
                 if (need_mask) {
                     const int key = k0 + j * 8 + qlane * 2 + (e & 1);
                     const bool vis = (e < 2) ? (key >= lo0 && key <= hi0) : (key >= lo1 && key <= hi1);
@@ -278,9 +313,9 @@ fmha_fwd_generic_kernel(const FwdDev p) {
     }
 }
 
-template <typename T, int D>
+template <typename T, int D, bool EXTRA>
 int launch_inst(const FwdParams& p, const FwdDev& dev, cudaStream_t stream) {
-    auto kern = fmha_fwd_generic_kernel<T, D>;
+    auto kern = fmha_fwd_generic_kernel<T, D, EXTRA>;
     const size_t smem = (size_t)(BM + 4 * BN) * D * 2;
     static thread_local int configured_device = -1;
     int devid = 0;
@@ -316,9 +351,22 @@ int launch_fwd_generic(const FwdParams& p, cudaStream_t stream) {
     dev.wl = (int)(p.wl < 0 ? -1 : (p.wl > 0x3fffffff ? 0x3fffffff : p.wl));
     dev.wr = (int)(p.wr < 0 ? -1 : (p.wr > 0x3fffffff ? 0x3fffffff : p.wr));
     dev.scale_log2 = p.scale * 1.4426950408889634f;
-    if (p.dtype == FLASHCK_DTYPE_BFLOAT16)
-        return p.d == 128 ? launch_inst<__nv_bfloat16, 128>(p, dev, stream) : launch_inst<__nv_bfloat16, 64>(p, dev, stream);
-    return p.d == 128 ? launch_inst<__half, 128>(p, dev, stream) : launch_inst<__half, 64>(p, dev, stream);
+    dev.bias = p.bias; dev.bias_type = p.bias ? p.bias_type : 0; dev.bias_rank = p.bias_rank;
+    dev.bias_sk = p.seqlen_k; dev.bias_sq = p.seqstart_q ? p.total_q : p.seqlen_q;
+    dev.soft_cap = p.logits_soft_cap; dev.scale = p.scale;
+    const bool bf16 = p.dtype == FLASHCK_DTYPE_BFLOAT16;
+    if (dev.bias_type != 0 || dev.soft_cap > 0.f) {
+        FCK_REQUIRE(dev.bias_type != 1 || !(p.block_table || p.kv_indptr || p.cache_batch_idx || p.seqlen_k32 || p.seqlen_k64),
+                    FLASHCK_ERR_UNSUPPORTED, "fmha_fwd: an elementwise bias needs contiguous K/V of the stated length");
+        if (bf16)
+            return p.d == 128 ? launch_inst<__nv_bfloat16, 128, true>(p, dev, stream)
+                              : launch_inst<__nv_bfloat16, 64, true>(p, dev, stream);
+        return p.d == 128 ? launch_inst<__half, 128, true>(p, dev, stream) : launch_inst<__half, 64, true>(p, dev, stream);
+    }
+    if (bf16)
+        return p.d == 128 ? launch_inst<__nv_bfloat16, 128, false>(p, dev, stream)
+                          : launch_inst<__nv_bfloat16, 64, false>(p, dev, stream);
+    return p.d == 128 ? launch_inst<__half, 128, false>(p, dev, stream) : launch_inst<__half, 64, false>(p, dev, stream);
 }
 
 }  // namespace fck

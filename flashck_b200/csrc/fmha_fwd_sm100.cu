@@ -1222,6 +1222,7 @@ int launch_t(const FwdParams& p, const Sm100Dev& dev, cudaStream_t stream) {
 bool fwd_sm100_supported(const FwdParams& p) {
     if (!g_use_sm100.load()) return false;
     if (p.d != HD || p.dv != HD) return false;
+    if ((p.bias && p.bias_type != 0) || p.logits_soft_cap > 0.f) return false;  // instances of the general kernel
     const bool paged = p.block_table || p.kv_indptr;
     if (paged) {
         // pages of 16 .. 128 tokens that divide a 128-key tile, or whole multiples of it

@@ -90,6 +90,14 @@ struct FwdParams {
     int mask_type;
     int64_t wl, wr;
     int dtype;
+    // Additions to the scaled scores before the mask (attention_kernels/fmha_fwd/fmha_fwd_jinja.h:76,98-112,199-233):
+    // bias_type 1: `bias` holds element-dtype values, rank 0 = [1,1,sq,sk], 1 = [1,hq,sq,sk], 2 = [b,hq,sq,sk] (group
+    // mode: sq, sk are the packed totals and a sequence's block starts at its first packed row and key);
+    // bias_type 2 (ALiBi): `bias` holds fp32 slopes, rank 0 = [1,hq], 1 = [b,hq]; score += -slope * |i + sk - sq - j|.
+    // logits_soft_cap > 0: score = cap * tanh(score / cap) on the scaled score, before the bias.
+    const void* bias;
+    int bias_type, bias_rank;
+    float logits_soft_cap;
 };
 int launch_fwd_generic(const FwdParams& p, cudaStream_t stream);
 

@@ -100,13 +100,37 @@ def _as_i32(name: str, t: torch.Tensor) -> torch.Tensor:
 # --------------------------------------------------------------------------------------------
 # dense / varlen forward
 # --------------------------------------------------------------------------------------------
+def _bias_args(q: torch.Tensor, bias, alibi_slopes, batch: int, hq: int, sq: int, sk: int):
+    """(buffer, bias_enum, bias_rank_info) for the C call; the enum and rank values are those of the reference's
+    BiasEnum / BiasEnumInfo (core/profiling/attention/fmha_library.h:121-164)."""
+    if bias is not None and alibi_slopes is not None:
+        raise ValueError("bias and alibi_slopes are mutually exclusive (one bias_enum per call)")
+    if bias is not None:
+        _check_cuda("bias", bias, q.dtype)
+        if bias.dim() != 4 or bias.shape[2] != sq or bias.shape[3] != sk or bias.shape[0] not in (1, batch) \
+                or bias.shape[1] not in (1, hq) or (bias.shape[0] != 1 and bias.shape[1] != hq):
+            raise ValueError(f"bias must be [1|{batch}, 1|{hq}, {sq}, {sk}] with a full head axis under a batch axis, "
+                             f"got {tuple(bias.shape)}")
+        rank = 0 if bias.shape[0] == 1 and bias.shape[1] == 1 else (1 if bias.shape[0] == 1 else 2)
+        return bias, 1, rank
+    if alibi_slopes is not None:
+        _check_cuda("alibi_slopes", alibi_slopes, torch.float32)
+        if alibi_slopes.dim() != 2 or alibi_slopes.shape[1] != hq or alibi_slopes.shape[0] not in (1, batch):
+            raise ValueError(f"alibi_slopes must be fp32 [1|{batch}, {hq}], got {tuple(alibi_slopes.shape)}")
+        return alibi_slopes, 2, (0 if alibi_slopes.shape[0] == 1 else 1)
+    return None, 0, 0
+
+
 def fmha_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, scale: Optional[float] = None,
              causal: bool = False, window_size: Sequence[int] = (-1, -1), mask_type: Optional[int] = None,
-             return_lse: bool = False):
+             return_lse: bool = False, bias: Optional[torch.Tensor] = None,
+             alibi_slopes: Optional[torch.Tensor] = None, logits_soft_cap: float = 0.0):
     """Dense forward attention (the reference's batch mode, C symbol ``FmhaFwd``).
 
     q ``[b, sq, hq, d]``, k ``[b, sk, hkv, d]``, v ``[b, sk, hkv, dv]`` -> o ``[b, sq, hq, dv]``
-    (and LSE ``[b, hq, sq]`` when ``return_lse``)."""
+    (and LSE ``[b, hq, sq]`` when ``return_lse``).  ``bias`` ``[1|b, 1|hq, sq, sk]`` (q's dtype) is added to the scaled
+    scores; ``alibi_slopes`` fp32 ``[1|b, hq]`` adds ``-slope * |i + sk - sq - j|``; ``logits_soft_cap`` > 0 caps the
+    scaled scores with ``cap * tanh(score / cap)`` first."""
     for n, t in (("q", q), ("k", k), ("v", v)):
         _check_cuda(n, t, getattr(q, "dtype", None))
         if t.dim() != 4:
@@ -119,9 +143,11 @@ def fmha_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, scale: Option
     mt, wl, wr = _mask(causal, window_size, mask_type)
     o = torch.empty((b, sq, hq, dv), dtype=q.dtype, device=q.device)
     lse = torch.empty((b, hq, sq), dtype=torch.float32, device=q.device) if return_lse else None
+    bias_buf, bias_enum, bias_rank = _bias_args(q, bias, alibi_slopes, b, hq, sq, sk)
     with torch.cuda.device(q.device):
-        rc = _lib.lib().FmhaFwd(_ptr(q), _ptr(k), _ptr(v), None, _ptr(o), None, None, None, b, sq, sk, hq, hkv, d, dv,
-                                sq, float(scale or 0.0), wl, wr, mt, _stream(), _ptr(lse), _dtype_code(q))
+        rc = _lib.lib().FmhaFwdBias(_ptr(q), _ptr(k), _ptr(v), _ptr(bias_buf), _ptr(o), None, None, None, b, sq, sk, hq,
+                                    hkv, d, dv, sq, float(scale or 0.0), wl, wr, mt, _stream(), _ptr(lse),
+                                    _dtype_code(q), bias_enum, bias_rank, float(logits_soft_cap))
     _lib.check(rc, "FmhaFwd")
     return (o, lse) if return_lse else o
 
@@ -129,11 +155,14 @@ def fmha_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, scale: Option
 def fmha_fwd_var_len(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlens_q: torch.Tensor,
                      cu_seqlens_k: torch.Tensor, max_seqlen_q: int, max_seqlen_k: int = 0, *,
                      scale: Optional[float] = None, causal: bool = False, window_size: Sequence[int] = (-1, -1),
-                     mask_type: Optional[int] = None, return_lse: bool = False):
+                     mask_type: Optional[int] = None, return_lse: bool = False, bias: Optional[torch.Tensor] = None,
+                     alibi_slopes: Optional[torch.Tensor] = None, logits_soft_cap: float = 0.0):
     """Variable-length forward attention (the reference's group mode: packed tokens + ``seqstart`` arrays).
 
     q ``[total_q, hq, d]``, k ``[total_k, hkv, d]``, v ``[total_k, hkv, dv]``; ``cu_seqlens_*`` int64 ``[b+1]``.
-    Returns o ``[total_q, hq, dv]`` (and LSE ``[hq, total_q]``)."""
+    Returns o ``[total_q, hq, dv]`` (and LSE ``[hq, total_q]``).  ``bias`` is ``[1, 1|hq, total_q, total_k]`` here (the
+    reference's group-mode shape: one plane over the packed rows and keys, of which every sequence uses its own block);
+    ``alibi_slopes`` and ``logits_soft_cap`` as in :func:`fmha_fwd`."""
     for n, t in (("q", q), ("k", k), ("v", v)):
         _check_cuda(n, t, getattr(q, "dtype", None))
         if t.dim() != 3:
@@ -151,10 +180,13 @@ def fmha_fwd_var_len(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqle
     mt, wl, wr = _mask(causal, window_size, mask_type)
     o = torch.empty((total_q, hq, dv), dtype=q.dtype, device=q.device)
     lse = torch.empty((hq, total_q), dtype=torch.float32, device=q.device) if return_lse else None
+    bias_buf, bias_enum, bias_rank = _bias_args(q, bias, alibi_slopes, 1 if bias is not None else batch, hq, total_q,
+                                                total_k)
     with torch.cuda.device(q.device):
-        rc = _lib.lib().FmhaFwd(_ptr(q), _ptr(k), _ptr(v), None, _ptr(o), _ptr(cu_q), _ptr(cu_k), None, batch,
-                                total_q, total_k, hq, hkv, d, dv, int(max_seqlen_q), float(scale or 0.0), wl, wr, mt,
-                                _stream(), _ptr(lse), _dtype_code(q))
+        rc = _lib.lib().FmhaFwdBias(_ptr(q), _ptr(k), _ptr(v), _ptr(bias_buf), _ptr(o), _ptr(cu_q), _ptr(cu_k), None,
+                                    batch, total_q, total_k, hq, hkv, d, dv, int(max_seqlen_q), float(scale or 0.0), wl,
+                                    wr, mt, _stream(), _ptr(lse), _dtype_code(q), bias_enum, bias_rank,
+                                    float(logits_soft_cap))
     _lib.check(rc, "FmhaFwd")
     return (o, lse) if return_lse else o
 

@@ -67,13 +67,32 @@ FLASHCK_API int FlashckDeviceStatus(int* status_out);
  * declaration fmha_fwd/fmha_fwd_call.h:34-53; launcher fmha_fwd/fmha_fwd_kernel.cc:79-107).
  * Batch mode: the three seq pointers are NULL.  Group mode: q_seq_start / k_seq_start are int64 [batch+1]
  * device arrays; k_seq_len_ptr (int64 [batch], optional) overrides the key length of each sequence.
- * bias_buf_ptr must be NULL (no-bias instances only).
+ * bias_buf_ptr: NULL, or a bias read the way the instance parameters `bias_enum` (1 elementwise, 2 alibi) and
+ * `bias_rank_info` of family 0 say (the reference fixes both per compiled instance); see FmhaFwdBias.
  */
 FLASHCK_API int FmhaFwd(void* q_buf_ptr, void* k_buf_ptr, void* v_buf_ptr, void* bias_buf_ptr, void* o_buf_ptr,
             int64_t* q_seq_start_ptr, int64_t* k_seq_start_ptr, int64_t* k_seq_len_ptr, int64_t batch,
             int64_t q_seq_len, int64_t kv_seq_len, int64_t q_num_heads, int64_t kv_num_heads, int64_t qk_head_dim,
             int64_t v_head_dim, int64_t q_max_seq_len, float scale, int64_t window_left, int64_t window_right,
             uint32_t mask_type, void* stream, void* lse_ptr, int dtype);
+
+/*
+ * FmhaFwdBias -- FmhaFwd with the instance properties the reference compiles in as call arguments
+ * (core/profiling/attention/fmha_fwd/fmha_fwd_problem.h:59-81 `bias_enum`, `bias_rank_info`, `has_logits_soft_cap`;
+ * bias strides attention_kernels/fmha_fwd/fmha_fwd_jinja.h:199-233,270-293; enum core/profiling/attention/
+ * fmha_library.h:121-164).  bias_enum 1: bias_buf_ptr holds element-dtype values, bias_rank_info 0 = [1,1,sq,sk],
+ * 1 = [1,hq,sq,sk], 2 = [b,hq,sq,sk] (group mode: sq and sk are the packed totals q_seq_len / kv_seq_len and a
+ * sequence's block starts at its first packed row and key); contiguous K/V of the stated lengths only.
+ * bias_enum 2 (alibi): bias_buf_ptr holds fp32 slopes, bias_rank_info 0 = [1,hq], 1 = [b,hq]; the score of query i
+ * and key j gets -slope * |i + sk - sq - j| added.  logits_soft_cap > 0: score = cap * tanh(score / cap), applied to
+ * the scaled score before the bias.  These calls run on the general (mma.sync) instance.
+ */
+FLASHCK_API int FmhaFwdBias(void* q_buf_ptr, void* k_buf_ptr, void* v_buf_ptr, void* bias_buf_ptr, void* o_buf_ptr,
+            int64_t* q_seq_start_ptr, int64_t* k_seq_start_ptr, int64_t* k_seq_len_ptr, int64_t batch,
+            int64_t q_seq_len, int64_t kv_seq_len, int64_t q_num_heads, int64_t kv_num_heads, int64_t qk_head_dim,
+            int64_t v_head_dim, int64_t q_max_seq_len, float scale, int64_t window_left, int64_t window_right,
+            uint32_t mask_type, void* stream, void* lse_ptr, int dtype, int bias_enum, int bias_rank_info,
+            float logits_soft_cap);
 
 /*
  * FmhaFwdBatchPrefill -- varlen prefill whose K/V sit behind an SGLang-style page table.

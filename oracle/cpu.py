@@ -56,9 +56,10 @@ def _i64(x):
 
 def fmha_fwd(q, k, v, *, seqstart_q=None, seqstart_k=None, seqlen_k=None, block_table=None,
              cache_batch_idx=None, seqlen_q_shape=None, scale=0.0, window=(-1, -1), mask_type=0,
-             nthreads=0):
+             nthreads=0, bias=None, alibi_slopes=None, logits_soft_cap=0.0):
     """Returns (O, LSE).  Batch mode: q [b,sq,hq,d]; group mode (seqstart_q given): q [total_q,hq,d].
-    LSE is [b,hq,sq] (batch) or [hq,total_q] (group)."""
+    LSE is [b,hq,sq] (batch) or [hq,total_q] (group).  bias: [1|b, 1|hq, sq, sk] in q's dtype (group mode: the packed
+    totals); alibi_slopes: fp32 [1|b, hq]."""
     dt = _dt(q)
     group = seqstart_q is not None
     paged = block_table is not None
@@ -76,16 +77,25 @@ def fmha_fwd(q, k, v, *, seqstart_q=None, seqstart_k=None, seqlen_k=None, block_
         sk = 0
     else:
         page, bt_stride = 0, 0
-        sk = k.shape[1] if k.dim() == 4 else 0
+        sk = k.shape[1] if k.dim() == 4 else k.shape[0]  # (group mode: the packed total, the row length of a bias)
     o = torch.empty(q.shape[:-1] + (dv,), dtype=q.dtype)
     lse = torch.empty((hq, total_q) if group else (batch, hq, sq), dtype=torch.float32)
     if seqlen_k is not None:
         seqlen_k = seqlen_k.to(torch.int32).contiguous()
-    rc = lib().oracle_fmha_fwd(
+    bias_enum, rank, bias_buf = 0, 0, None
+    if bias is not None:
+        assert alibi_slopes is None and bias.dim() == 4 and bias.dtype == q.dtype
+        bias_enum, bias_buf = 1, bias
+        rank = 0 if bias.shape[0] == 1 and bias.shape[1] == 1 else (1 if bias.shape[0] == 1 else 2)
+    elif alibi_slopes is not None:
+        assert alibi_slopes.dim() == 2 and alibi_slopes.dtype == torch.float32
+        bias_enum, bias_buf, rank = 2, alibi_slopes, (0 if alibi_slopes.shape[0] == 1 else 1)
+    rc = lib().oracle_fmha_fwd_bias(
         _p(q), _p(k), _p(v), _p(o), _p(lse), _p(seqstart_q), _p(seqstart_k), _p(seqlen_k), _p(block_table),
         _p(cache_batch_idx), _i64(batch), _i64(sq), _i64(sk), _i64(hq), _i64(hkv), _i64(d), _i64(dv),
         _i64(bt_stride), _i64(page), ctypes.c_float(scale), _i64(window[0]), _i64(window[1]),
-        ctypes.c_uint32(mask_type), ctypes.c_int(dt), ctypes.c_int(nthreads))
+        ctypes.c_uint32(mask_type), ctypes.c_int(dt), ctypes.c_int(nthreads), _p(bias_buf), ctypes.c_int(bias_enum),
+        ctypes.c_int(rank), ctypes.c_float(logits_soft_cap))
     if rc != 0:
         raise RuntimeError(f"oracle_fmha_fwd failed with status {rc}")
     return o, lse

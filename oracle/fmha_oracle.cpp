@@ -128,7 +128,9 @@ struct KvView {
 void attend_head(const uint16_t* q, int64_t q_row_stride, const KvView& kv, int64_t b_phys, int64_t kvh,
                  int64_t sq, int64_t sk, int64_t d, int64_t dv, float scale, uint32_t mask_type, int64_t wl,
                  int64_t wr, int dtype, uint16_t* o, int64_t o_row_stride, float* lse, int64_t lse_stride,
-                 const float* kf, const float* vf /* fp32 copies of this kv head: [sk,d], [sk,dv] */) {
+                 const float* kf, const float* vf /* fp32 copies of this kv head: [sk,d], [sk,dv] */,
+                 const uint16_t* bias /* first element of this (sequence, head) block, or nullptr */,
+                 int64_t bias_row_stride, float alibi_slope, float soft_cap) {
     std::vector<float> s(static_cast<size_t>(std::max<int64_t>(sk, 1)));
     std::vector<float> qf(d), acc(dv);
     for (int64_t i = 0; i < sq; ++i) {
@@ -141,6 +143,11 @@ void attend_head(const uint16_t* q, int64_t q_row_stride, const KvView& kv, int6
             float a = 0.f;
             for (int64_t x = 0; x < d; ++x) a += qf[x] * kr[x];
             a *= scale;
+            // has_logits_soft_cap (fmha_fwd/fmha_fwd_problem.h:81): the scaled score is capped, then the bias is added
+            if (soft_cap > 0.f) a = soft_cap * std::tanh(a / soft_cap);
+            if (bias) a += to_f32(bias[i * bias_row_stride + j], dtype);  // ELEMENTWISE_BIAS (fmha_library.h:123)
+            // ALIBI (fmha_library.h:124): distance from the diagonal that ends at the last query and the last key
+            if (alibi_slope != 0.f) a -= alibi_slope * std::fabs(static_cast<float>(i + sk - sq - j));
             s[j] = a;
             m = std::max(m, a);
         }
@@ -180,12 +187,18 @@ extern "C" {
 //   seqstart_k == nullptr in group mode, batch-strided [b,sk,hkv,d] with per-batch seqlen_k.
 //   K/V paged (block_table != nullptr): pool [pages,page,hkv,d]; per-batch lengths in seqlen_k (int32).
 //   cache_batch_idx (int64 [b], optional) remaps the batch row used for K/V and the block table.
-int oracle_fmha_fwd(const uint16_t* q, const uint16_t* k, const uint16_t* v, uint16_t* o, float* lse,
-                    const int64_t* seqstart_q, const int64_t* seqstart_k, const int32_t* seqlen_k_ptr,
-                    const int32_t* block_table, const int64_t* cache_batch_idx, int64_t batch, int64_t seqlen_q,
-                    int64_t seqlen_k, int64_t hq, int64_t hkv, int64_t d, int64_t dv, int64_t bt_stride,
-                    int64_t page_block_size, float scale, int64_t window_left, int64_t window_right,
-                    uint32_t mask_type, int dtype, int nthreads) {
+// bias_enum / bias_rank_info as in fmha_library.h:121-164 and the strides of fmha_fwd/fmha_fwd_jinja.h:199-233,
+// 270-293: elementwise bias in the element dtype, rank 0 = [1,1,sq,sk], 1 = [1,hq,sq,sk], 2 = [b,hq,sq,sk] (group
+// mode: sq, sk are the packed totals, a sequence's block starts at its first packed row and key); ALiBi slopes fp32,
+// rank 0 = [1,hq], 1 = [b,hq].  The ALiBi term itself is computed inside ck_tile, which is not part of the reference
+// tree: the form used here is the published one with the diagonal aligned bottom-right.
+int oracle_fmha_fwd_bias(const uint16_t* q, const uint16_t* k, const uint16_t* v, uint16_t* o, float* lse,
+                         const int64_t* seqstart_q, const int64_t* seqstart_k, const int32_t* seqlen_k_ptr,
+                         const int32_t* block_table, const int64_t* cache_batch_idx, int64_t batch, int64_t seqlen_q,
+                         int64_t seqlen_k, int64_t hq, int64_t hkv, int64_t d, int64_t dv, int64_t bt_stride,
+                         int64_t page_block_size, float scale, int64_t window_left, int64_t window_right,
+                         uint32_t mask_type, int dtype, int nthreads, const void* bias, int bias_enum,
+                         int bias_rank_info, float logits_soft_cap) {
     if (hq % hkv != 0 || (dtype != kFloat16 && dtype != kBFloat16)) return 1;
     if (scale == 0.f) scale = 1.f / std::sqrt(static_cast<float>(d));  // fmha_fwd_jinja.h:57-59
     const int64_t ratio = hq / hkv;
@@ -219,13 +232,36 @@ int oracle_fmha_fwd(const uint16_t* q, const uint16_t* k, const uint16_t* v, uin
                 float* lse_h = nullptr;
                 int64_t lse_stride = 1;
                 if (lse) lse_h = seqstart_q ? lse + h * total_q + q0 : lse + (b * hq + h) * seqlen_q;
+                const uint16_t* bias_blk = nullptr;
+                float slope = 0.f;
+                const int64_t plane_sq = seqstart_q ? total_q : seqlen_q, plane_sk = seqlen_k;
+                if (bias && bias_enum == 1) {
+                    const int64_t plane = plane_sq * plane_sk;
+                    int64_t off = bias_rank_info >= 1 ? h * plane : 0;
+                    if (bias_rank_info == 2 && !seqstart_q) off += b * hq * plane;
+                    if (seqstart_q) off += q0 * plane_sk + (seqstart_k ? seqstart_k[b] : 0);
+                    bias_blk = static_cast<const uint16_t*>(bias) + off;
+                } else if (bias && bias_enum == 2) {
+                    slope = static_cast<const float*>(bias)[(bias_rank_info >= 1 ? b * hq : 0) + h];
+                }
                 attend_head(q + (q0 * hq + h) * d, hq * d, kv, b_phys, kh, sq, sk, d, dv, scale, mask_type,
                             window_left, window_right, dtype, o + (q0 * hq + h) * dv, hq * dv, lse_h, lse_stride,
-                            kf.data(), vf.data());
+                            kf.data(), vf.data(), bias_blk, plane_sk, slope, logits_soft_cap);
             }
         }
     }
     return 0;
+}
+
+int oracle_fmha_fwd(const uint16_t* q, const uint16_t* k, const uint16_t* v, uint16_t* o, float* lse,
+                    const int64_t* seqstart_q, const int64_t* seqstart_k, const int32_t* seqlen_k_ptr,
+                    const int32_t* block_table, const int64_t* cache_batch_idx, int64_t batch, int64_t seqlen_q,
+                    int64_t seqlen_k, int64_t hq, int64_t hkv, int64_t d, int64_t dv, int64_t bt_stride,
+                    int64_t page_block_size, float scale, int64_t window_left, int64_t window_right,
+                    uint32_t mask_type, int dtype, int nthreads) {
+    return oracle_fmha_fwd_bias(q, k, v, o, lse, seqstart_q, seqstart_k, seqlen_k_ptr, block_table, cache_batch_idx, batch,
+                                seqlen_q, seqlen_k, hq, hkv, d, dv, bt_stride, page_block_size, scale, window_left,
+                                window_right, mask_type, dtype, nthreads, nullptr, 0, 0, 0.f);
 }
 
 // LSE-weighted combine of split-KV partials (fmha_fwd_split_kv_combine_jinja.h:125-140):

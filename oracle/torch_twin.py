@@ -27,8 +27,10 @@ def visible_mask(sq: int, sk: int, mask_type: int, window=(-1, -1)) -> torch.Ten
     return ok
 
 
-def attend(q, k, v, scale=0.0, mask_type=0, window=(-1, -1)):
-    """q [sq,hq,d], k [sk,hkv,d], v [sk,hkv,dv] -> (o [sq,hq,dv] in q.dtype, lse [hq,sq] fp32)."""
+def attend(q, k, v, scale=0.0, mask_type=0, window=(-1, -1), bias=None, alibi_slopes=None, logits_soft_cap=0.0):
+    """q [sq,hq,d], k [sk,hkv,d], v [sk,hkv,dv] -> (o [sq,hq,dv] in q.dtype, lse [hq,sq] fp32).
+    bias [1|hq, sq, sk] is added to the scaled scores, alibi_slopes [hq] add -slope * |i + sk - sq - j|, a soft cap
+    bounds the scaled scores with cap * tanh(score / cap) before either."""
     sq, hq, d = q.shape
     sk, hkv, _ = k.shape
     if scale == 0.0:
@@ -38,6 +40,13 @@ def attend(q, k, v, scale=0.0, mask_type=0, window=(-1, -1)):
     kf = k.float().permute(1, 0, 2).repeat_interleave(ratio, dim=0)  # [hq,sk,d]
     vf = v.float().permute(1, 0, 2).repeat_interleave(ratio, dim=0)
     s = torch.matmul(qf, kf.transpose(1, 2)) * scale
+    if logits_soft_cap > 0:
+        s = logits_soft_cap * torch.tanh(s / logits_soft_cap)
+    if bias is not None:
+        s = s + bias.float()
+    if alibi_slopes is not None:
+        dist = (torch.arange(sq)[:, None] + (sk - sq) - torch.arange(sk)[None, :]).abs().float()
+        s = s - alibi_slopes.float()[:, None, None] * dist[None]
     s = s.masked_fill(~visible_mask(sq, sk, mask_type, window)[None], float("-inf"))
     lse = torch.logsumexp(s, dim=-1)
     p = torch.exp(s - lse[..., None])

@@ -452,6 +452,81 @@ def test_splitkv_many_query_rows_long_stream_and_few_splits(num_splits, sq):
     assert_lse_close(lse, lse_ref)
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("d", [64, 128])
+@pytest.mark.parametrize("kind", ["bias0", "bias1", "bias2", "alibi0", "alibi1", "softcap", "softcap+bias2"])
+def test_fmha_fwd_bias_alibi_and_soft_cap(dtype, d, kind):
+    """The score additions of the reference's instance schema (bias_enum, bias_rank_info, has_logits_soft_cap) in batch
+    mode, with a bottom-right causal mask, GQA, ragged sizes that end inside a tile."""
+    b, sq, sk, hq, hkv = 2, 100, 171, 8, 2
+    q, k, v = (normal_tensor(sh, dtype, sd) for sh, sd in (((b, sq, hq, d), 1), ((b, sk, hkv, d), 2), ((b, sk, hkv, d), 3)))
+    bias = slopes = None
+    cap = 0.0
+    if "bias" in kind:
+        bias = normal_tensor(((1, 1), (1, hq), (b, hq))[int(kind[-1])] + (sq, sk), dtype, 4)
+    if "alibi" in kind:
+        slopes = torch.rand((b if kind.endswith("1") else 1, hq), generator=torch.Generator().manual_seed(5)) * 0.5
+    if "softcap" in kind:
+        cap = 2.0
+    o_ref, lse_ref = oracle.fmha_fwd(q, k, v, mask_type=2, window=(-1, 0), bias=bias, alibi_slopes=slopes,
+                                     logits_soft_cap=cap)
+    o, lse = ops.fmha_fwd(_cu(q), _cu(k), _cu(v), causal=True, return_lse=True, bias=_cu(bias) if bias is not None else None,
+                          alibi_slopes=_cu(slopes) if slopes is not None else None, logits_soft_cap=cap)
+    assert_o_close(o, o_ref, kind)
+    assert_lse_close(lse, lse_ref, kind)
+    # the additions change the result (the test would pass vacuously if they were dropped on both sides)
+    o_plain, _ = oracle.fmha_fwd(q, k, v, mask_type=2, window=(-1, 0))
+    assert (o_plain.float() - o_ref.float()).abs().max() > 0.05
+
+
+def test_fmha_fwd_var_len_bias_plane_and_alibi():
+    """Group mode: the bias is one [1, hq, total_q, total_k] plane of which every sequence uses its own block; ALiBi
+    slopes per (sequence, head)."""
+    dtype = torch.bfloat16
+    hq, hkv, d = 8, 4, 128
+    lens_q, lens_k = [5, 130, 64], [77, 130, 300]
+    cu_q, cu_k = to_seqstarts(lens_q), to_seqstarts(lens_k)
+    tq, tk = int(cu_q[-1]), int(cu_k[-1])
+    q, k, v = normal_tensor((tq, hq, d), dtype, 11), normal_tensor((tk, hkv, d), dtype, 12), normal_tensor((tk, hkv, d), dtype, 13)
+    bias = normal_tensor((1, hq, tq, tk), dtype, 14)
+    o_ref, lse_ref = oracle.fmha_fwd(q, k, v, seqstart_q=cu_q, seqstart_k=cu_k, mask_type=2, window=(-1, 0), bias=bias)
+    o, lse = ops.fmha_fwd_var_len(_cu(q), _cu(k), _cu(v), _cu(cu_q), _cu(cu_k), max(lens_q), causal=True, return_lse=True,
+                                  bias=_cu(bias))
+    assert_o_close(o, o_ref)
+    assert_lse_close(lse, lse_ref)
+    slopes = torch.rand((len(lens_q), hq), generator=torch.Generator().manual_seed(6)) * 0.3
+    o_ref, lse_ref = oracle.fmha_fwd(q, k, v, seqstart_q=cu_q, seqstart_k=cu_k, mask_type=2, window=(-1, 0),
+                                     alibi_slopes=slopes)
+    o, lse = ops.fmha_fwd_var_len(_cu(q), _cu(k), _cu(v), _cu(cu_q), _cu(cu_k), max(lens_q), causal=True, return_lse=True,
+                                  alibi_slopes=_cu(slopes))
+    assert_o_close(o, o_ref)
+    assert_lse_close(lse, lse_ref)
+
+
+def test_fmha_fwd_bias_pointer_read_as_the_instance_parameters_say():
+    """The reference's FmhaFwd symbol has a bias pointer and fixes its meaning per compiled instance; here the instance
+    parameters bias_enum / bias_rank_info of the family do, and an inconsistent request is refused."""
+    dtype = torch.float16
+    b, s, h, d = 1, 48, 4, 64
+    q, k, v = (normal_tensor((b, s, h, d), dtype, sd) for sd in (1, 2, 3))
+    slopes = torch.tensor([[0.5, 0.25, 0.125, 0.0625]], dtype=torch.float32)
+    o_ref, _ = oracle.fmha_fwd(q, k, v, alibi_slopes=slopes)
+    qc, kc, vc, sc = _cu(q), _cu(k), _cu(v), _cu(slopes)
+    o = torch.empty_like(qc)
+    _lib.set_instance_param(0, "bias_enum", 2)
+    try:
+        assert _lib.get_instance_param(0, "bias_enum") == 2
+        rc = _lib.lib().FmhaFwd(qc.data_ptr(), kc.data_ptr(), vc.data_ptr(), sc.data_ptr(), o.data_ptr(), None, None, None,
+                                b, s, s, h, h, d, d, s, 0.0, -1, -1, 0, torch.cuda.current_stream().cuda_stream, None, 3)
+        _lib.check(rc, "FmhaFwd")
+    finally:
+        _lib.set_instance_param(0, "bias_enum", 1)
+    assert_o_close(o, o_ref)
+    with pytest.raises(RuntimeError):  # bias_enum without a buffer
+        _lib.check(_lib.lib().FmhaFwdBias(qc.data_ptr(), kc.data_ptr(), vc.data_ptr(), None, o.data_ptr(), None, None, None,
+                                          b, s, s, h, h, d, d, s, 0.0, -1, -1, 0, None, None, 3, 1, 0, 0.0), "FmhaFwdBias")
+
+
 def test_splitkv_config3_small():
     # BASELINE config 3 geometry (32/8 heads, hdim 128, page 16, shuffled block table) at reduced batch/context
     dtype = torch.bfloat16

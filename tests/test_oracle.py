@@ -10,6 +10,7 @@ import torch
 from flashck_b200.utils.inputs import make_paged_cache, normal_tensor, rotary_cos_sin, to_seqstarts
 from oracle import cpu as oracle
 from oracle import torch_twin as twin
+from helpers import assert_lse_close, assert_o_close
 
 GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
 
@@ -37,6 +38,49 @@ def test_oracle_matches_torch_twin(dtype, mask, sq, sk):
         fin = ~torch.isinf(l2)
         assert torch.equal(torch.isinf(lse[bi]), torch.isinf(l2))
         assert torch.allclose(lse[bi][fin], l2[fin], atol=1e-4, rtol=1e-5)
+
+
+@pytest.mark.parametrize("kind", ["bias0", "bias1", "bias2", "alibi0", "alibi1", "softcap", "softcap+alibi"])
+def test_oracle_bias_alibi_softcap_match_twin(kind):
+    """The score additions of the reference's instance schema (bias_enum / bias_rank_info / has_logits_soft_cap):
+    both statements of the math agree, in batch mode for every rank of the bias."""
+    dtype = torch.bfloat16
+    b, sq, sk, hq, hkv, d = 2, 37, 70, 4, 2, 64
+    q, k, v = (normal_tensor(sh, dtype, sd) for sh, sd in (((b, sq, hq, d), 1), ((b, sk, hkv, d), 2), ((b, sk, hkv, d), 3)))
+    bias = slopes = None
+    cap = 0.0
+    if kind.startswith("bias"):
+        rank = int(kind[-1])
+        bias = normal_tensor(((1, 1), (1, hq), (b, hq))[rank] + (sq, sk), dtype, 4)
+    if "alibi" in kind:
+        slopes = torch.rand((b if kind.endswith("1") else 1, hq), generator=torch.Generator().manual_seed(5)) * 0.5
+    if "softcap" in kind:
+        cap = 1.5
+    o, lse = oracle.fmha_fwd(q, k, v, mask_type=2, window=(-1, 0), bias=bias, alibi_slopes=slopes, logits_soft_cap=cap)
+    for bi in range(b):
+        bb = None if bias is None else bias[bi if bias.shape[0] > 1 else 0]
+        ss = None if slopes is None else slopes[bi if slopes.shape[0] > 1 else 0]
+        o2, l2 = twin.attend(q[bi], k[bi], v[bi], mask_type=2, window=(-1, 0), bias=bb, alibi_slopes=ss,
+                             logits_soft_cap=cap)
+        assert_o_close(o[bi], o2, kind)
+        assert_lse_close(lse[bi], l2, kind)
+
+
+def test_oracle_group_mode_bias_uses_the_block_of_each_sequence():
+    """Group mode: one [1, hq, total_q, total_k] plane; sequence b reads rows seqstart_q[b].. and keys seqstart_k[b].."""
+    dtype = torch.float16
+    hq, hkv, d = 4, 4, 64
+    lens_q, lens_k = [5, 33, 17], [40, 33, 90]
+    cu_q, cu_k = to_seqstarts(lens_q), to_seqstarts(lens_k)
+    tq, tk = int(cu_q[-1]), int(cu_k[-1])
+    q, k, v = normal_tensor((tq, hq, d), dtype, 11), normal_tensor((tk, hkv, d), dtype, 12), normal_tensor((tk, hkv, d), dtype, 13)
+    bias = normal_tensor((1, hq, tq, tk), dtype, 14)
+    o, lse = oracle.fmha_fwd(q, k, v, seqstart_q=cu_q, seqstart_k=cu_k, bias=bias)
+    for bi in range(len(lens_q)):
+        qs, ks = slice(int(cu_q[bi]), int(cu_q[bi + 1])), slice(int(cu_k[bi]), int(cu_k[bi + 1]))
+        o2, l2 = twin.attend(q[qs], k[ks], v[ks], bias=bias[0, :, qs, ks])
+        assert_o_close(o[qs], o2)
+        assert_lse_close(lse[:, qs], l2)
 
 
 def test_oracle_paged_group_mode_matches_twin():
