@@ -577,9 +577,9 @@ def main():
                        "algorithmic_bytes_per_gpu_step": a_bytes, "num_splits": S4},
             "roofline": {"bound": "hbm", "achieved": a_bytes * asteps / (ms_a * 1e-3) / 1e9, "peak": peaks["hbm_gbs"],
                          "unit": "GB/s", "frac": a_bytes * asteps / (ms_a * 1e-3) / 1e9 / peaks["hbm_gbs"],
-                         # DRAM bytes of the split-KV launch: an ncu capture of 8 sequences (79 056 cached tokens: 335.3 MB
+                         # DRAM bytes of the split-KV launch: an ncu capture of 8 sequences (79 056 cached tokens: 330.4 MB
                          # read + written, profiles/fmha_fwd_sm100_splitkv_append_decode_bf16.md) scaled by the token count
-                         "traffic": 335.3e6 / 79056 * sum(wa["lens"]),
+                         "traffic": 330.4e6 / 79056 * sum(wa["lens"]),
                          "peak_source": peaks["source"], "note": "append-KV + split-KV + combine kernels timed together"},
             "gpu_launches": 3 * asteps,
         }
