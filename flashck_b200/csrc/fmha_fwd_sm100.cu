@@ -202,6 +202,7 @@ constexpr int kMaxBatch = 256;    // sequences the on-chip schedule can hold (la
 constexpr int kMaxLevels = 512;   // row blocks per sequence the on-chip schedule can hold
 constexpr int STAGE_BYTES = 32 * 32 * 2;  // per softmax warp: 32 rows x 32 columns of O on their way to a TMA store
 constexpr int kMaxRounds = 1024;  // work items per CTA (the host sends larger problems to the general instance)
+constexpr int kSplitItems = 2560; // the same for the split modes (their list needs one word per item)
 
 // One work item = two 128-row Q tiles that share their K/V tiles.  With an even GQA ratio the tiles are the same
 // 128 rows of two neighbouring q heads of one kv group: both see the same keys, so they run the same number of
@@ -228,9 +229,12 @@ struct Ctrl {
     int level_start[kMaxLevels + 1];    // first work item of each level; level 0 = highest block index
     int nblk[kMaxBatch];                // row blocks of each sequence
     int seq_q0[kMaxBatch], seq_sq[kMaxBatch], seq_k0[kMaxBatch], seq_sk[kMaxBatch];  // first row / length, Q and K
-    uint32_t items[kMaxRounds];         // this CTA's work list: valid << 31 | sequence << 22 | head index << 12 | row block
-    uint32_t items2[kMaxRounds];        // split modes: first key tile << 16 | key tiles of the item
+    // this CTA's work list: valid << 31 | sequence << 22 | head index << 12 | row block (split modes: split << 4 | block)
+    uint32_t items[kSplitItems];
     int split_w, split_items;           // split modes: length of a CTA's piece of the work stream; items of this CTA
+    // split modes: every item takes all key tiles of its stream, except that the first item of the list may start
+    // inside its stream (at this tile) and the last one may end inside it (before this tile)
+    int split_first_lo, split_last_hi;
 };
 
 // Item taken by CTA `cta` in round `rnd` of a grid of `g` CTAs: rounds alternate direction (snake order), so that
@@ -242,6 +246,9 @@ __device__ __forceinline__ int item_of_round(int rnd, int cta, int g) {
 // Work items are ordered by decreasing row-block index (under a causal mask: decreasing cost), then by sequence,
 // then by head, so that the q heads of a GQA group -- which read the same K/V -- run at the same time on
 // neighbouring SMs and share those tiles through L2.  Warp-collective.
+static_assert(1024 + (2 + 2 * KV_SLOTS) * TILE_BYTES + 8 * STAGE_BYTES + sizeof(Ctrl) <= 227 * 1024,
+              "tiles, staging buffers and the control block must fit the 227 KB a CTA can have");
+
 // Split modes.  A stream is the key tiles one (sequence, 128-row block of the packed rows, kv head) needs; all streams,
 // in that order, each preceded by kItemCost units that stand for an item's fixed cost (Q load, pipeline fill, epilogue),
 // form one line that is cut into equal pieces of split_w units, one per CTA, so that the SMs finish together whatever
@@ -268,7 +275,7 @@ __device__ __forceinline__ int split_stream_pieces(int g0, int n, int w, int max
     return (g0 + kItemCost + n - 1) / w - (g0 + kItemCost) / w + 1;
 }
 
-__device__ __forceinline__ void expand_item_split(const Ctrl* ctrl, const Sm100Dev& p, uint32_t packed, uint32_t packed2, Item& it) {
+__device__ __forceinline__ void expand_item_split(const Ctrl* ctrl, const Sm100Dev& p, uint32_t packed, int rnd, Item& it) {
     it.valid = packed >> 31;
     const int b = (packed >> 22) & 0x1ff, kh = (packed >> 12) & 0x3ff, piece = (packed >> 4) & 0xff, rb = packed & 0xf;
     it.b = b;
@@ -282,8 +289,10 @@ __device__ __forceinline__ void expand_item_split(const Ctrl* ctrl, const Sm100D
     it.row0[0] = rb * BM;    // first packed row (token * group + group head)
     it.row0[1] = 0x3fffffff; // tile 1 does not exist
     it.shift = (p.causal == 2) ? it.sk - it.sq : 0;
-    it.n0 = (int)(packed2 >> 16);
-    it.nt[0] = (int)(packed2 & 0xffffu);
+    const int lo = rnd == 0 ? ctrl->split_first_lo : 0;
+    const int hi = rnd == ctrl->split_items - 1 ? ctrl->split_last_hi : split_stream_tiles(p, it.sq, it.sk, rb);
+    it.n0 = lo;
+    it.nt[0] = hi - lo;
     it.nt[1] = 0;
     it.N = it.nt[0];
 }
@@ -361,7 +370,7 @@ __device__ __forceinline__ void expand_item(const Ctrl* ctrl, const Sm100Dev& p,
 // The work item of round `rnd` of this CTA, from the table filled at start-up.
 template <int SPLIT = 0>
 __device__ __forceinline__ void get_item(const Ctrl* ctrl, const Sm100Dev& p, int rnd, int total_items, int lane, Item& it) {
-    if (SPLIT) expand_item_split(ctrl, p, ctrl->items[rnd], ctrl->items2[rnd], it);
+    if (SPLIT) expand_item_split(ctrl, p, ctrl->items[rnd], rnd, it);
     else expand_item(ctrl, p, ctrl->items[rnd], it);
 }
 
@@ -461,7 +470,7 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                 nmax = max(nmax, n);
             }
             ctrl->nblk[b] = cost * p.hkv;
-            ctrl->items2[b] = (uint32_t)nmax;  // (scratch until the work list is written)
+            ctrl->items[b] = (uint32_t)nmax;  // (scratch until the work list is written)
         }
         else ctrl->nblk[b] = min(p.num_levels, (sq + rows_per_block - 1) / rows_per_block);
     }
@@ -474,7 +483,7 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
             for (int b = 0; b < p.batch; ++b) {
                 ctrl->level_start[b] = run;
                 run += ctrl->nblk[b];
-                nmax = max(nmax, (int)ctrl->items2[b]);
+                nmax = max(nmax, (int)ctrl->items[b]);
             }
             ctrl->level_start[p.batch] = run;
             int w = max((run + (int)gridDim.x - 1) / (int)gridDim.x, p.piece_tiles + kItemCost);
@@ -512,9 +521,10 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                                 if (t_hi <= t_lo) continue;
                                 piece = (int)blockIdx.x - (g0 + kItemCost) / w;
                             }
-                            if (cnt >= kMaxRounds) { overflow = true; break; }
+                            if (cnt >= kSplitItems) { overflow = true; break; }
                             ctrl->items[cnt] = 0x80000000u | ((uint32_t)b << 22) | ((uint32_t)kh << 12) | ((uint32_t)piece << 4) | (uint32_t)rb;
-                            ctrl->items2[cnt] = ((uint32_t)t_lo << 16) | (uint32_t)(t_hi - t_lo);
+                            if (cnt == 0) ctrl->split_first_lo = t_lo;  // (only the first item can start inside its stream)
+                            ctrl->split_last_hi = t_hi;                 // (and only the last one end inside it)
                             ++cnt;
                         }
                         seg0 += p.hkv * c;
@@ -548,7 +558,7 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     const uint32_t tmem = ctrl->tmem_base;
     const int total_items = SPLIT ? 0 : ctrl->level_start[p.num_levels];
     int rounds = SPLIT ? ctrl->split_items : (total_items + (int)gridDim.x - 1) / (int)gridDim.x;
-    if (rounds > kMaxRounds) {  // the host checks an upper bound of this; never silently drop work
+    if (!SPLIT && rounds > kMaxRounds) {  // the host checks an upper bound of this; never silently drop work
         if (threadIdx.x == 0) atomicOr(p.status, 0x20000000);
         rounds = 0;
     }
@@ -1352,13 +1362,17 @@ bool splitkv_sm100_supported(const SplitKVParams& p) {
     }
     if (p.num_splits > 1 && !p.lse_acc) return false;
     if (p.num_splits > 255) return false;  // the split index of a work item has 8 bits
-    // The work line (see kItemCost) is indexed with 31 bits, an item's first tile and tile count with 16 each, and a
-    // CTA's work list holds kMaxRounds items: a CTA's piece of w units reaches into at most w / kItemCost + 2 streams.
+    // The work line (see kItemCost) is indexed with 31 bits, and a CTA's work list holds kSplitItems items: a CTA's
+    // piece of w units reaches into at most w / kItemCost + 2 streams, and w is at most the larger of the line's
+    // 148th, the shortest piece, and what keeps the longest possible stream within the workspace's splits.
     const int64_t cap_tiles = split_cap_tiles(p);
     const int64_t streams = p.batch * p.hkv * ((p.max_seqlen_q * group + BM - 1) / BM);
     const int64_t line = streams * (cap_tiles + kItemCost);
-    if (cap_tiles > 0xffff || line >= (1ll << 31)) return false;
-    if (streams > kMaxRounds - 2 && (line / sm_count() + 1) / kItemCost + 2 > kMaxRounds) return false;
+    if (line >= (1ll << 31)) return false;
+    const int64_t max_pieces = std::max<int64_t>(1, split_duplicates_rows(p) ? p.num_splits / 2 : p.num_splits);
+    int64_t w_max = std::max<int64_t>(line / sm_count() + 1, kMinPieceTiles + kItemCost);
+    if (max_pieces >= 2) w_max = std::max(w_max, cap_tiles / (max_pieces - 1) + 1);
+    if (std::min(streams, w_max / kItemCost + 2) > kSplitItems) return false;
     const int64_t tokens = p.seqstart_q ? p.total_q : p.batch * p.seqlen_q;
     if (tokens >= (1ll << 31) || (!p.block_table && p.batch * p.seqlen_k_cap >= (1ll << 31))) return false;
     return true;

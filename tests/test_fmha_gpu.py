@@ -527,6 +527,24 @@ def test_fmha_fwd_bias_pointer_read_as_the_instance_parameters_say():
                                           b, s, s, h, h, d, d, s, 0.0, -1, -1, 0, None, None, 3, 1, 0, 0.0), "FmhaFwdBias")
 
 
+def test_splitkv_many_query_rows_many_short_streams():
+    """Many more streams than SMs, most of them one or two key tiles long, some empty, one long: every CTA's piece of the
+    work then holds a list of whole streams between two cut ones."""
+    dtype = torch.bfloat16
+    hq, hkv, d, page, sq = 16, 4, 128, 16, 6
+    lens_k = [(37 * i) % 290 for i in range(150)]
+    lens_k[7] = 9000
+    lens_k[60] = 0
+    cache = make_paged_cache(lens_k, hkv, d, d, page, dtype, seed=31)
+    q = normal_tensor((len(lens_k), sq, hq, d), dtype, 99)
+    o_ref, lse_ref = oracle.fmha_fwd(q, cache.k, cache.v, seqlen_k=cache.seqlen_k, block_table=cache.block_table)
+    o, lse = ops.fmha_fwd_splitkv(_cu(q), _cu(cache.k), _cu(cache.v), seqlen_k=_cu(cache.seqlen_k),
+                                  block_table=_cu(cache.block_table), num_splits=8, return_lse=True)
+    assert _lib.device_status() == 0
+    assert_o_close(o, o_ref)
+    assert_lse_close(lse, lse_ref)
+
+
 def test_splitkv_config3_small():
     # BASELINE config 3 geometry (32/8 heads, hdim 128, page 16, shuffled block table) at reduced batch/context
     dtype = torch.bfloat16
