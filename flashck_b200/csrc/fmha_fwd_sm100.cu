@@ -15,7 +15,7 @@
 //   warp 9      TMA producer: Q tiles of the item (4 boxes of 64 x 128, 128-byte swizzle), then K and V tiles of
 //               128 keys into two-slot rings that run on across work items; mbarrier expect-tx.  Paged K/V: one box
 //               per page chunk and 64-column half, each lane issuing its own chunk's boxes; the tail of a sequence's
-//               last page is kept out of V (copied by hand with zeros behind the end).
+//               last page is kept out of V (its rows are overwritten with zeros once the copy has landed).
 //   warp 8      MMA issuer (one elected thread): S_i = Q_i K^T with tcgen05.mma (both operands in shared
 //               memory, K-major), O_i += P_i V with the A operand P_i read from tensor memory and V taken
 //               MN-major straight from its [key][hdim] tile.  Accumulators live in TMEM: S0,S1 (128 columns
@@ -223,6 +223,7 @@ struct Ctrl {
     uint64_t k_full[3], k_empty[3], v_full[KV_SLOTS], v_empty[KV_SLOTS];  // (the split modes use a third K slot)
     uint64_t s_full[2], p_full[2], o_full[2];
     uint64_t pv_done[2];  // split modes: the PV that read S/P buffer b is complete (buffer b may take the next S)
+    uint64_t v_tail;      // paged V: the copies of a tile that holds the end of its sequence (cleaned up before v_full)
     uint32_t tmem_base;
     int abort_flag;
     int num_levels;                     // row-block indices 0 .. num_levels-1
@@ -255,7 +256,7 @@ static_assert(1024 + (2 + 2 * KV_SLOTS) * TILE_BYTES + 8 * STAGE_BYTES + sizeof(
 // the lengths are.  The part of a stream inside one CTA's piece is a work item and one split of the result; a stream
 // cut k times uses splits 0..k.  split_w is raised where needed so that no stream needs more splits than the
 // workspace has; with a single split per stream the whole stream goes to the CTA its start falls to.
-constexpr int kItemCost = 3;
+constexpr int kItemCost = 6;
 
 // key tiles the rows of row block `rb` of a sequence see
 __device__ __forceinline__ int split_stream_tiles(const Sm100Dev& p, int sq, int sk, int rb) {
@@ -408,6 +409,7 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     if (threadIdx.x == 0) {
         mbar_init(&ctrl->q_full, 1);
         mbar_init(&ctrl->q_empty, 1);
+        mbar_init(&ctrl->v_tail, 1);
         for (int s = 0; s < 3; ++s) {
             mbar_init(&ctrl->k_full[s], 1);
             mbar_init(&ctrl->k_empty[s], 1);
@@ -587,12 +589,14 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                 tma_prefetch_desc(&map_v);
             }
             uint32_t kv_cnt = 0, q_cnt = 0;  // K/V tiles and Q loads issued so far (ring positions)
+            uint32_t tail_cnt = 0;           // tiles that went through v_tail (its parity)
             // Paged pools are read in chunks of min(page, 128) tokens: one TMA box per chunk and 64-column half.
             // A chunk that the sequence only partly fills is the tail of its last page, and what lies behind the
             // sequence end there is whatever the allocator left: for K that is harmless (those scores are masked by
-            // index), but P = 0 times a NaN in V is NaN, so the V rows of such a chunk are copied by the warp with
-            // zeros behind the sequence end.  Chunks wholly behind the end are not loaded at all; the slot then
-            // keeps rows of earlier tiles (real data, or the zeros the slots start with).
+            // index), but P = 0 times a NaN in V is NaN, so the V rows behind the sequence end are overwritten with zeros
+            // when such a chunk has landed (a copy of those rows by hand, one 16-byte load after the other, cost up to
+            // 16 us per sequence end with pages of 128 tokens).  Chunks wholly behind the end are not loaded at all; the
+            // slot then keeps rows of earlier tiles (real data, or the zeros the slots start with).
             const int chunk = p.page > 0 ? min(p.page, BN) : BN;
             const int chunks = BN / chunk;
             for (int rnd = 0; rnd < rounds; ++rnd) {
@@ -687,26 +691,38 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                     if (!ok) break;
                     const uint32_t part_mask = any_mask & ~full_mask;  // at most one chunk: the tail of the last page
                     if (part_mask) {
+                        // The tile holds the end of the sequence.  Its copies complete on a barrier of their own; when
+                        // they have landed the rows behind the end are overwritten with zeros (shared-memory stores
+                        // only), and only then is the slot handed to the MMA thread.
+                        if (lane == 0) mbar_expect_tx(&ctrl->v_tail, __popc(any_mask) * chunk * HD * 2);
+                        __syncwarp();
+                        if (my_valid > 0)
+                            for (int hb = 0; hb < 2; ++hb)
+                                tma_load_3d(sV + s * TILE_BYTES + hb * HALF_BYTES + lane * chunk * 128, &map_v, &ctrl->v_tail,
+                                            hb * 64, it.kh, my_row);
+                        if (lane == 0) ok = mbar_wait_bounded(&ctrl->v_tail, tail_cnt & 1u, abort_flag, p.status, 0x21);
+                        ++tail_cnt;
+                        ok = __shfl_sync(0xffffffffu, ok, 0);
+                        if (!ok) break;
                         const int c = __ffs(part_mask) - 1;
-                        const int v = __shfl_sync(0xffffffffu, my_valid, c), row = __shfl_sync(0xffffffffu, my_row, c);
-                        const uint4* src = reinterpret_cast<const uint4*>((const T*)p.v + ((int64_t)row * p.hkv + it.kh) * HD);
-                        const int64_t row_pieces = (int64_t)p.hkv * HD * 2 / 16;  // 16-byte pieces between two tokens
+                        const int v = __shfl_sync(0xffffffffu, my_valid, c);
                         uint8_t* dst = sV + s * TILE_BYTES + c * chunk * 128;
-                        for (int idx = lane; idx < chunk * 16; idx += 32) {
-                            const int r = idx >> 4, piece = idx & 15, hb = piece >> 3, ch = piece & 7;
-                            const int t = c * chunk + r;  // token inside the tile: selects the swizzle phase
-                            uint4 val = make_uint4(0u, 0u, 0u, 0u);
-                            if (r < v) val = src[r * row_pieces + piece];
-                            *reinterpret_cast<uint4*>(dst + hb * HALF_BYTES + r * 128 + ((ch ^ (t & 7)) << 4)) = val;
+                        for (int idx = lane; idx < (chunk - v) * 16; idx += 32) {  // a row is 128 bytes in either half
+                            const int r = v + (idx >> 4), piece = idx & 15;
+                            *reinterpret_cast<uint4*>(dst + (piece >> 3) * HALF_BYTES + r * 128 + ((piece & 7) << 4)) =
+                                make_uint4(0u, 0u, 0u, 0u);
                         }
                         fence_proxy_async_smem();  // the MMAs read these rows through the async proxy
                         __syncwarp();
+                        if (lane == 0) mbar_arrive(&ctrl->v_full[s]);
+                    } else {
+                        if (lane == 0) mbar_expect_tx(&ctrl->v_full[s], __popc(full_mask) * chunk * HD * 2);
+                        __syncwarp();
+                        if (my_valid == chunk)
+                            for (int hb = 0; hb < 2; ++hb)
+                                tma_load_3d(sV + s * TILE_BYTES + hb * HALF_BYTES + lane * chunk * 128, &map_v, &ctrl->v_full[s],
+                                            hb * 64, it.kh, my_row);
                     }
-                    if (lane == 0) mbar_expect_tx(&ctrl->v_full[s], __popc(full_mask) * chunk * HD * 2);
-                    if (my_valid == chunk)
-                        for (int hb = 0; hb < 2; ++hb)
-                            tma_load_3d(sV + s * TILE_BYTES + hb * HALF_BYTES + lane * chunk * 128, &map_v, &ctrl->v_full[s],
-                                        hb * 64, it.kh, my_row);
                     my_row = next_row;
                     my_valid = next_valid;
                 }
@@ -1327,8 +1343,12 @@ int launch_split_t(const SplitKVParams& p, const Sm100Dev& dev, cudaStream_t str
     CUtensorMap mq, mk, mv;
     int rc;
     if ((rc = make_map_q_packed(&mq, p.q, p.dtype, tokens, p.hkv, p.hq / p.hkv, SPLIT == 2 ? 64 : BM))) return rc;
-    if ((rc = make_map_3d(&mk, p.k, p.dtype, 0x7fffff00ll, p.hkv, box_k))) return rc;  // cache rows are trusted
-    if ((rc = make_map_3d(&mv, p.v, p.dtype, 0x7fffff00ll, p.hkv, box_k))) return rc;
+    // Paged pools: the page ids are trusted like pointers, and a copy never leaves its page.  Contiguous cache
+    // [batch, capacity, hkv, 128]: the last 128-token chunk of a row reaches past the row's end, and past the end of the
+    // buffer in the last row; the map carries the true row count so that those rows are not read (they come as zeros).
+    const int64_t cache_rows = p.block_table ? 0x7fffff00ll : p.batch * p.seqlen_k_cap;
+    if ((rc = make_map_3d(&mk, p.k, p.dtype, cache_rows, p.hkv, box_k))) return rc;
+    if ((rc = make_map_3d(&mv, p.v, p.dtype, cache_rows, p.hkv, box_k))) return rc;
     auto kern = fmha_fwd_sm100_kernel<T, 0, false, SPLIT>;
     const size_t smem = 1024 + (size_t)(2 + 2 * KV_SLOTS) * TILE_BYTES + 8 * STAGE_BYTES + sizeof(Ctrl);
     static thread_local int configured_device = -1;
@@ -1357,8 +1377,8 @@ bool splitkv_sm100_supported(const SplitKVParams& p) {
     if (p.mask_type > 2 || (p.mask_type != 0 && !(p.wl < 0 && p.wr == 0))) return false;  // none or causal
     if (p.block_table) {
         if (p.page < 16 || !((BN % p.page == 0) || (p.page % BN == 0)) || p.cache_batch_idx) return false;
-    } else if (p.seqlen_k_cap <= 0) {
-        return false;
+    } else if (p.seqlen_k_cap <= 0 || p.cache_batch_idx) {
+        return false;  // (with cache_batch_idx the number of cache rows is not known here: see the K/V maps)
     }
     if (p.num_splits > 1 && !p.lse_acc) return false;
     if (p.num_splits > 255) return false;  // the split index of a work item has 8 bits

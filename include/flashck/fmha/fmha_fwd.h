@@ -58,6 +58,24 @@ T* fmha_fwd(T* q, T* k, T* v, T* o, float* lse, int64_t* seqstart_q, int64_t* se
     return o;
 }
 
+// The same with the score additions of the reference's instance schema: `bias` is an elementwise bias in T
+// (bias_rank_info 0 = [1,1,sq,sk], 1 = [1,hq,sq,sk], 2 = [b,hq,sq,sk]) or fp32 ALiBi slopes (0 = [1,hq], 1 = [b,hq]),
+// as `bias_enum` says; logits_soft_cap > 0 caps the scaled scores first.  Returns `o`.
+template <typename T>
+T* fmha_fwd_bias(T* q, T* k, T* v, const void* bias, BiasEnum bias_enum, int bias_rank_info, float logits_soft_cap, T* o,
+                 float* lse, int64_t* seqstart_q, int64_t* seqstart_k, int64_t* seqlen_k, int64_t batch, int64_t seqlen_q,
+                 int64_t seqlen_k_max, int64_t q_num_heads, int64_t kv_num_heads, int64_t qk_head_dim, int64_t v_head_dim,
+                 int64_t max_seqlen_q, float scale = 0.f, std::array<int64_t, 2> window_size = {-1, -1},
+                 GenericAttentionMaskEnum mask = GenericAttentionMaskEnum::NO_MASK, void* stream = nullptr,
+                 int dtype = detail::dtype_code<T>()) {
+    detail::check(FmhaFwdBias(q, k, v, const_cast<void*>(bias), o, seqstart_q, seqstart_k, seqlen_k, batch, seqlen_q,
+                              seqlen_k_max, q_num_heads, kv_num_heads, qk_head_dim, v_head_dim, max_seqlen_q, scale,
+                              window_size[0], window_size[1], static_cast<uint32_t>(mask), stream, lse, dtype,
+                              static_cast<int>(bias_enum), bias_rank_info, logits_soft_cap),
+                  "fmha_fwd_bias");
+    return o;
+}
+
 // Split-KV attention over a contiguous or paged cache followed by the combine.  Workspaces are caller-owned:
 // lse_acc [b,hq,num_splits,sq], o_acc [b,hq,num_splits,sq,dv] fp32.  Returns `o`.
 template <typename T>

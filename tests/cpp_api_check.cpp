@@ -22,6 +22,15 @@ int main() {
         AttentionLayer<_Float16> layer(FmhaOperationMode::Batch, 2, 2, 64, 64, 1.f, BiasEnum::ALIBI);
         ++failures;
     } catch (const std::runtime_error&) {}
+    try {  // a bias kind without a bias buffer is refused before any CUDA work
+        bf16 dummy[8] = {0};
+        naive::fmha_fwd_bias<bf16>(dummy, dummy, dummy, nullptr, BiasEnum::ELEMENTWISE_BIAS, 0, 0.f, dummy, nullptr, nullptr,
+                                   nullptr, nullptr, 1, 1, 1, 2, 2, 64, 64, 1);
+        std::printf("expected a throw for bias_enum without a buffer\n");
+        ++failures;
+    } catch (const std::runtime_error& e) {
+        if (!std::strstr(e.what(), "bias")) { std::printf("unexpected message: %s\n", e.what()); ++failures; }
+    }
     static_assert(detail::dtype_code<bf16>() == 4 && detail::dtype_code<_Float16>() == 3, "dtype codes");
     std::printf(failures ? "FAIL\n" : "OK\n");
     return failures;
