@@ -95,6 +95,20 @@ int check_common(const char* fn, int dtype, int64_t hq, int64_t hkv, int64_t d, 
     return FLASHCK_OK;
 }
 
+// The paged and split-KV entry points take a bias pointer only as ALiBi slopes (instance parameter bias_enum = 2;
+// bias_rank_info 0 = [1,hq], 1 = [batch,hq]); an elementwise bias has no defined layout over pages.
+int alibi_from_bias(const char* fn, const void* bias, const float** slopes, int* rank) {
+    *slopes = nullptr;
+    *rank = 0;
+    if (!bias) return FLASHCK_OK;
+    FCK_REQUIRE(g_bias_enum.load() == 2, FLASHCK_ERR_UNSUPPORTED,
+                "%s: a bias pointer is read as ALiBi slopes only (set the instance parameter bias_enum of family 0 to 2)", fn);
+    FCK_REQUIRE(g_bias_rank_info.load() <= 1, FLASHCK_ERR_INVALID_ARGUMENT, "%s: bias_rank_info must be 0 or 1 for ALiBi", fn);
+    *slopes = (const float*)bias;
+    *rank = (int)g_bias_rank_info.load();
+    return FLASHCK_OK;
+}
+
 inline float resolve_scale(float scale, int64_t d) {
     return scale == 0.f ? 1.f / sqrtf((float)d) : scale;  // fmha_fwd_jinja.h:57-59
 }
@@ -176,8 +190,11 @@ int FmhaFwdBatchPrefill(void* q, void* k, void* v, void* bias, void* o, int64_t*
                         int64_t hkv, int64_t d, int64_t dv, int64_t q_max_seq_len, int64_t num_total_pages,
                         int64_t paged_block_size, float scale, int64_t window_left, int64_t window_right,
                         uint32_t mask_type, void* stream, void* lse, int dtype) {
-    int rc = check_common("FmhaFwdBatchPrefill", dtype, hq, hkv, d, dv, bias);
+    int rc = check_common("FmhaFwdBatchPrefill", dtype, hq, hkv, d, dv, nullptr);
     if (rc) return rc;
+    const float* slopes = nullptr;
+    int slope_rank = 0;
+    if ((rc = alibi_from_bias("FmhaFwdBatchPrefill", bias, &slopes, &slope_rank))) return rc;
     FCK_REQUIRE(q && k && v && o && q_seq_start && kv_indptr && kv_page_indices && kv_last_page_len,
                 FLASHCK_ERR_INVALID_ARGUMENT, "FmhaFwdBatchPrefill: null pointer argument");
     FCK_REQUIRE(paged_block_size > 0 && num_total_pages >= 0 && batch >= 0 && q_max_seq_len >= 0,
@@ -194,6 +211,7 @@ int FmhaFwdBatchPrefill(void* q, void* k, void* v, void* bias, void* o, int64_t*
     p.num_pages = num_total_pages;
     p.scale = resolve_scale(scale, d);
     p.mask_type = (int)mask_type; p.wl = window_left; p.wr = window_right; p.dtype = dtype;
+    if (slopes) { p.bias = slopes; p.bias_type = 2; p.bias_rank = slope_rank; }
     return run_fwd(p, (cudaStream_t)stream);
 }
 
@@ -202,8 +220,11 @@ int FmhaFwdPagedKVPrefill(void* q, void* k, void* v, void* bias, void* o, int64_
                           int64_t hkv, int64_t d, int64_t dv, int64_t q_max_seq_len, int64_t max_num_page_blocks,
                           int64_t paged_block_size, float scale, int64_t window_left, int64_t window_right,
                           uint32_t mask_type, void* stream, void* lse, int dtype) {
-    int rc = check_common("FmhaFwdPagedKVPrefill", dtype, hq, hkv, d, dv, bias);
+    int rc = check_common("FmhaFwdPagedKVPrefill", dtype, hq, hkv, d, dv, nullptr);
     if (rc) return rc;
+    const float* slopes = nullptr;
+    int slope_rank = 0;
+    if ((rc = alibi_from_bias("FmhaFwdPagedKVPrefill", bias, &slopes, &slope_rank))) return rc;
     FCK_REQUIRE(q && k && v && o && k_seq_len && block_table, FLASHCK_ERR_INVALID_ARGUMENT,
                 "FmhaFwdPagedKVPrefill: null pointer argument");
     FCK_REQUIRE(batch > 0 && paged_block_size > 0 && max_num_page_blocks % batch == 0, FLASHCK_ERR_INVALID_ARGUMENT,
@@ -221,6 +242,7 @@ int FmhaFwdPagedKVPrefill(void* q, void* k, void* v, void* bias, void* o, int64_
     p.num_pages = max_num_page_blocks;  // the pools hold max_num_page_blocks pages (fmha_fwd_split_kv_jinja.h:512-519)
     p.scale = resolve_scale(scale, d);
     p.mask_type = (int)mask_type; p.wl = window_left; p.wr = window_right; p.dtype = dtype;
+    if (slopes) { p.bias = slopes; p.bias_type = 2; p.bias_rank = slope_rank; }
     return run_fwd(p, (cudaStream_t)stream);
 }
 
@@ -230,8 +252,11 @@ int FmhaFwdSplitKV(void* q, void* k, void* v, void* bias, void* lse_acc, void* o
                    int64_t q_max_seq_len, int64_t num_splits, int64_t max_num_page_blocks, int64_t paged_block_size,
                    float scale, int64_t window_left, int64_t window_right, uint32_t mask_type, void* stream,
                    int dtype) {
-    int rc = check_common("FmhaFwdSplitKV", dtype, hq, hkv, d, dv, bias);
+    int rc = check_common("FmhaFwdSplitKV", dtype, hq, hkv, d, dv, nullptr);
     if (rc) return rc;
+    const float* slopes = nullptr;
+    int slope_rank = 0;
+    if ((rc = alibi_from_bias("FmhaFwdSplitKV", bias, &slopes, &slope_rank))) return rc;
     FCK_REQUIRE(q && k && v && o_acc, FLASHCK_ERR_INVALID_ARGUMENT, "FmhaFwdSplitKV: q, k, v and o_acc must not be null");
     FCK_REQUIRE(num_splits >= 1 && num_splits <= 1024, FLASHCK_ERR_INVALID_ARGUMENT,
                 "FmhaFwdSplitKV: num_splits must be in [1,1024] (got %lld)", (long long)num_splits);
@@ -242,6 +267,7 @@ int FmhaFwdSplitKV(void* q, void* k, void* v, void* bias, void* lse_acc, void* o
     FCK_REQUIRE(!block_table || (paged_block_size > 0 && max_num_page_blocks % batch == 0), FLASHCK_ERR_INVALID_ARGUMENT,
                 "FmhaFwdSplitKV: max_num_page_blocks must be batch * pages_per_sequence");
     SplitKVParams p{};
+    p.alibi_slopes = slopes; p.alibi_rank = slope_rank;
     p.q = q; p.k = k; p.v = v; p.o_acc = (float*)o_acc; p.lse_acc = (float*)lse_acc;
     p.seqstart_q = q_seq_start; p.seqstart_k = block_table ? nullptr : kv_seq_start;
     p.seqlen_k = (const int32_t*)k_seq_len; p.block_table = (const int32_t*)block_table;

@@ -1367,6 +1367,7 @@ int launch_split_t(const SplitKVParams& p, const Sm100Dev& dev, cudaStream_t str
 
 bool splitkv_sm100_supported(const SplitKVParams& p) {
     if (!g_use_sm100_splitkv.load()) return false;
+    if (p.alibi_slopes) return false;  // ALiBi runs on the mma.sync decode kernel
     if (p.d != HD || p.dv != HD || p.batch <= 0 || p.batch > kMaxBatch || p.hq > 1023) return false;
     const int64_t group = p.hq / p.hkv;
     if (group > BM || BM % group != 0) return false;

@@ -60,6 +60,10 @@ struct SplitKVParams {
     int mask_type;
     int64_t wl, wr;
     int dtype;
+    // ALiBi (bias_enum 2 of the reference's schema): fp32 slopes [1,hq] (rank 0) or [batch,hq] (rank 1), or nullptr;
+    // the score of query i and key j gets -slope * |i + sk - sq - j| added
+    const float* alibi_slopes;
+    int alibi_rank;
 };
 int launch_splitkv_decode(const SplitKVParams& p, cudaStream_t stream);
 // instance parameters (see FlashckSetInstanceParam): "stages", "ctas_per_sm_x100" ...

@@ -47,6 +47,9 @@ struct DecodeDev {
     int* status;
     int batch, seqlen_q, seqlen_k_cap, hq, hkv, num_splits, total_q, bt_stride, page;
     int mask_type, wl, wr;
+    const float* alibi;  // slopes (see SplitKVParams) or nullptr
+    int alibi_rank;
+    float scale;
     int stages;
     float scale_log2;
 };
@@ -323,6 +326,13 @@ splitkv_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
                 qa[ks][2] = v0 ? *reinterpret_cast<const uint32_t*>(q0p + c + 8) : 0u;
                 qa[ks][3] = v1 ? *reinterpret_cast<const uint32_t*>(q1p + c + 8) : 0u;
             }
+            // ALiBi: slope of the head of each of this thread's two rows, and the key its diagonal ends at
+            float slope0 = 0.f, slope1 = 0.f;
+            if (p.alibi) {
+                const float* sl = p.alibi + (p.alibi_rank ? (int64_t)b * p.hq : 0) + kh * G;
+                slope0 = v0 ? sl[r0 - i0 * G] : 0.f;
+                slope1 = v1 ? sl[r1 - i1 * G] : 0.f;
+            }
             // visible key range of the two rows of this thread
             int lo0, hi0, lo1, hi1;
             visible_range(i0, sq, len, p.mask_type, p.wl, p.wr, lo0, hi0);
@@ -389,6 +399,11 @@ splitkv_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
                         float x = sacc[n][e] * p.scale_log2;
+                        if (p.alibi) {  // (warp-uniform; the common instances pay one predicate per element)
+                            const int key = tok0 + n * 8 + qlane * 2 + (e & 1);
+                            const float dist = fabsf((float)(((e < 2) ? i0 : i1) + len - sq - key));
+                            x = (sacc[n][e] * p.scale - ((e < 2) ? slope0 : slope1) * dist) * 1.4426950408889634f;
+                        }
                         if (need_mask) {
                             const int key = tok0 + n * 8 + qlane * 2 + (e & 1);
                             const bool vis = (e < 2) ? (key >= lo0 && key <= hi0) : (key >= lo1 && key <= hi1);
@@ -624,6 +639,7 @@ int launch_splitkv_decode(const SplitKVParams& p, cudaStream_t stream) {
     dev.wr = (int)(p.wr < 0 ? -1 : (p.wr > 0x3fffffff ? 0x3fffffff : p.wr));
     dev.stages = 0;
     dev.scale_log2 = p.scale * 1.4426950408889634f;
+    dev.alibi = p.alibi_slopes; dev.alibi_rank = p.alibi_rank; dev.scale = p.scale;
     if (p.dtype == FLASHCK_DTYPE_BFLOAT16)
         return p.d == 128 ? launch_mt<__nv_bfloat16, 128>(p, dev, stream) : launch_mt<__nv_bfloat16, 64>(p, dev, stream);
     return p.d == 128 ? launch_mt<__half, 128>(p, dev, stream) : launch_mt<__half, 64>(p, dev, stream);

@@ -13,7 +13,9 @@ functions take packed ``[total, h, d]`` tensors plus ``cu_seqlens`` (int64 ``[b+
 """
 from __future__ import annotations
 
+import contextlib
 import ctypes
+import threading
 from typing import Optional, Sequence, Tuple
 
 import torch
@@ -100,6 +102,31 @@ def _as_i32(name: str, t: torch.Tensor) -> torch.Tensor:
 # --------------------------------------------------------------------------------------------
 # dense / varlen forward
 # --------------------------------------------------------------------------------------------
+_ALIBI_LOCK = threading.Lock()
+
+
+@contextlib.contextmanager
+def _alibi_instance(alibi_slopes: Optional[torch.Tensor], batch: int, hq: int):
+    """The paged and split-KV symbols keep the reference's argument lists, in which the kind of bias is a property of
+    the compiled instance: while the call is made the instance parameters of the family say that the bias pointer holds
+    ALiBi slopes (fp32 ``[1|batch, hq]``).  Yields the pointer to pass as ``bias_buf_ptr``."""
+    if alibi_slopes is None:
+        yield ctypes.c_void_p(0)
+        return
+    _check_cuda("alibi_slopes", alibi_slopes, torch.float32)
+    if alibi_slopes.dim() != 2 or alibi_slopes.shape[1] != hq or alibi_slopes.shape[0] not in (1, batch):
+        raise ValueError(f"alibi_slopes must be fp32 [1|{batch}, {hq}], got {tuple(alibi_slopes.shape)}")
+    with _ALIBI_LOCK:
+        old = (_lib.get_instance_param(0, "bias_enum"), _lib.get_instance_param(0, "bias_rank_info"))
+        _lib.set_instance_param(0, "bias_enum", 2)
+        _lib.set_instance_param(0, "bias_rank_info", 0 if alibi_slopes.shape[0] == 1 else 1)
+        try:
+            yield _ptr(alibi_slopes)
+        finally:
+            _lib.set_instance_param(0, "bias_enum", old[0])
+            _lib.set_instance_param(0, "bias_rank_info", old[1])
+
+
 def _bias_args(q: torch.Tensor, bias, alibi_slopes, batch: int, hq: int, sq: int, sk: int):
     """(buffer, bias_enum, bias_rank_info) for the C call; the enum and rank values are those of the reference's
     BiasEnum / BiasEnumInfo (core/profiling/attention/fmha_library.h:121-164)."""
@@ -194,7 +221,8 @@ def fmha_fwd_var_len(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqle
 def batch_prefill(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, cu_seqlens_q: torch.Tensor,
                   kv_indptr: torch.Tensor, kv_page_indices: torch.Tensor, kv_last_page_len: torch.Tensor,
                   max_seqlen_q: int, *, scale: Optional[float] = None, causal: bool = True,
-                  window_size: Sequence[int] = (-1, -1), mask_type: Optional[int] = None, return_lse: bool = False):
+                  window_size: Sequence[int] = (-1, -1), mask_type: Optional[int] = None, return_lse: bool = False,
+                  alibi_slopes: Optional[torch.Tensor] = None):
     """Varlen prefill over an SGLang-style page table (``fmha_fwd_batch_prefill``).
 
     q ``[total_q, hq, d]``; pools ``[num_total_pages, page, hkv, d|dv]``; ``kv_indptr`` int32 ``[b+1]``,
@@ -219,8 +247,8 @@ def batch_prefill(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, c
     mt, wl, wr = _mask(causal, window_size, mask_type)
     o = torch.empty((total_q, hq, dv), dtype=q.dtype, device=q.device)
     lse = torch.empty((hq, total_q), dtype=torch.float32, device=q.device) if return_lse else None
-    with torch.cuda.device(q.device):
-        rc = _lib.lib().FmhaFwdBatchPrefill(_ptr(q), _ptr(k_pool), _ptr(v_pool), None, _ptr(o), _ptr(cu_q),
+    with torch.cuda.device(q.device), _alibi_instance(alibi_slopes, batch, hq) as bias_ptr:
+        rc = _lib.lib().FmhaFwdBatchPrefill(_ptr(q), _ptr(k_pool), _ptr(v_pool), bias_ptr, _ptr(o), _ptr(cu_q),
                                             _ptr(indptr), _ptr(indices), _ptr(last), batch, total_q, hq, hkv, d, dv,
                                             int(max_seqlen_q), pages, page, float(scale or 0.0), wl, wr, mt,
                                             _stream(), _ptr(lse), _dtype_code(q))
@@ -233,7 +261,8 @@ def fmha_fwd_paged_kv_prefill(q: torch.Tensor, k_pool: torch.Tensor, v_pool: tor
                               cu_seqlens_q: Optional[torch.Tensor] = None, max_seqlen_q: int = 0,
                               cache_batch_idx: Optional[torch.Tensor] = None, scale: Optional[float] = None,
                               causal: bool = True, window_size: Sequence[int] = (-1, -1),
-                              mask_type: Optional[int] = None, return_lse: bool = False):
+                              mask_type: Optional[int] = None, return_lse: bool = False,
+                              alibi_slopes: Optional[torch.Tensor] = None):
     """Prefill reading K/V through a block table (``fmha_fwd_paged_kv_prefill``).
 
     q ``[b, sq, hq, d]`` or packed ``[total_q, hq, d]`` with ``cu_seqlens_q``; pools ``[pages, page, hkv, *]``;
@@ -262,8 +291,8 @@ def fmha_fwd_paged_kv_prefill(q: torch.Tensor, k_pool: torch.Tensor, v_pool: tor
     mt, wl, wr = _mask(causal, window_size, mask_type)
     o = torch.empty(o_shape + (dv,), dtype=q.dtype, device=q.device)
     lse = torch.empty(lse_shape, dtype=torch.float32, device=q.device) if return_lse else None
-    with torch.cuda.device(q.device):
-        rc = _lib.lib().FmhaFwdPagedKVPrefill(_ptr(q), _ptr(k_pool), _ptr(v_pool), None, _ptr(o), _ptr(cu_q), _ptr(sl),
+    with torch.cuda.device(q.device), _alibi_instance(alibi_slopes, batch, hq) as bias_ptr:
+        rc = _lib.lib().FmhaFwdPagedKVPrefill(_ptr(q), _ptr(k_pool), _ptr(v_pool), bias_ptr, _ptr(o), _ptr(cu_q), _ptr(sl),
                                               _ptr(bt), _ptr(cbi), batch, shape_sq, hq, hkv, d, dv, max_sq,
                                               batch * bt.shape[1], page, float(scale or 0.0), wl, wr, mt, _stream(),
                                               _ptr(lse), _dtype_code(q))
@@ -377,7 +406,8 @@ def fmha_fwd_splitkv(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
                      cu_seqlens_k: Optional[torch.Tensor] = None, max_seqlen_q: int = 0, num_splits: int = 0,
                      scale: Optional[float] = None, causal: bool = False, window_size: Sequence[int] = (-1, -1),
                      mask_type: Optional[int] = None, return_lse: bool = False,
-                     workspace: Optional[Tuple[torch.Tensor, torch.Tensor]] = None, combine: bool = True):
+                     workspace: Optional[Tuple[torch.Tensor, torch.Tensor]] = None, combine: bool = True,
+                     alibi_slopes: Optional[torch.Tensor] = None):
     """Split-KV attention (decode) over a contiguous or paged KV cache, followed by the combine.
 
     q ``[b, sq, hq, d]`` (or packed ``[total_q, hq, d]`` with ``cu_seqlens_q``).
@@ -428,8 +458,8 @@ def fmha_fwd_splitkv(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
         lse_acc, o_acc = workspace
         S = o_acc.shape[2]
     mt, wl, wr = _mask(causal, window_size, mask_type)
-    with torch.cuda.device(q.device):
-        rc = _lib.lib().FmhaFwdSplitKV(_ptr(q), _ptr(k_cache), _ptr(v_cache), None, _ptr(lse_acc), _ptr(o_acc),
+    with torch.cuda.device(q.device), _alibi_instance(alibi_slopes, batch, hq) as bias_ptr:
+        rc = _lib.lib().FmhaFwdSplitKV(_ptr(q), _ptr(k_cache), _ptr(v_cache), bias_ptr, _ptr(lse_acc), _ptr(o_acc),
                                        _ptr(cu_q), _ptr(cu_k), _ptr(sl), _ptr(bt), _ptr(cbi), batch, shape_sq,
                                        shape_sk, hq, hkv, d, dv, max_sq, S,
                                        max_pages, page,

@@ -545,6 +545,42 @@ def test_splitkv_many_query_rows_many_short_streams():
     assert_lse_close(lse, lse_ref)
 
 
+@pytest.mark.parametrize("rank", [0, 1])
+@pytest.mark.parametrize("sq", [1, 5, 24])
+def test_splitkv_and_paged_prefill_with_alibi(rank, sq):
+    """ALiBi slopes through the bias pointer of the paged entry points (decode with one and several query tokens, the
+    latter beyond one 16-row tile too; paged prefill through a block table and through an SGLang-style page list)."""
+    dtype = torch.bfloat16
+    hq, hkv, d, page = 8, 2, 128, 16
+    lens_k = [700, 45, 1290]
+    b = len(lens_k)
+    cache = make_paged_cache(lens_k, hkv, d, d, page, dtype, seed=41)
+    q = normal_tensor((b, sq, hq, d), dtype, 42)
+    slopes = torch.rand((b if rank else 1, hq), generator=torch.Generator().manual_seed(7)) * 0.2
+    o_ref, lse_ref = oracle.fmha_fwd(q, cache.k, cache.v, seqlen_k=cache.seqlen_k, block_table=cache.block_table,
+                                     mask_type=2, window=(-1, 0), alibi_slopes=slopes)
+    o_plain, _ = oracle.fmha_fwd(q, cache.k, cache.v, seqlen_k=cache.seqlen_k, block_table=cache.block_table,
+                                 mask_type=2, window=(-1, 0))
+    assert (o_plain.float() - o_ref.float()).abs().max() > 0.05
+    o, lse = ops.fmha_fwd_splitkv(_cu(q), _cu(cache.k), _cu(cache.v), seqlen_k=_cu(cache.seqlen_k),
+                                  block_table=_cu(cache.block_table), num_splits=4, causal=True, return_lse=True,
+                                  alibi_slopes=_cu(slopes))
+    assert _lib.device_status() == 0
+    assert_o_close(o, o_ref, "split-KV with ALiBi")
+    assert_lse_close(lse, lse_ref, "split-KV with ALiBi")
+    o, lse = ops.fmha_fwd_paged_kv_prefill(_cu(q), _cu(cache.k), _cu(cache.v), _cu(cache.block_table), _cu(cache.seqlen_k),
+                                           causal=True, return_lse=True, alibi_slopes=_cu(slopes))
+    assert_o_close(o, o_ref, "paged prefill with ALiBi")
+    assert_lse_close(lse, lse_ref, "paged prefill with ALiBi")
+    # the instance parameters are back at their defaults, and a bias pointer without them is refused
+    assert _lib.get_instance_param(0, "bias_enum") == 1
+    with pytest.raises(RuntimeError):
+        qc = _cu(q)
+        _lib.check(_lib.lib().FmhaFwdSplitKV(qc.data_ptr(), qc.data_ptr(), qc.data_ptr(), qc.data_ptr(), None, qc.data_ptr(),
+                                             None, None, None, None, None, b, sq, 16, hq, hkv, d, d, sq, 1, 0, 0, 0.0, -1, -1,
+                                             0, None, 4), "FmhaFwdSplitKV")
+
+
 def test_splitkv_config3_small():
     # BASELINE config 3 geometry (32/8 heads, hdim 128, page 16, shuffled block table) at reduced batch/context
     dtype = torch.bfloat16
