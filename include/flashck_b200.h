@@ -101,6 +101,8 @@ FLASHCK_API int FmhaFwdBias(void* q_buf_ptr, void* k_buf_ptr, void* v_buf_ptr, v
  * files (attention_kernels/fmha_fwd_batch_prefill/...) are empty, so the argument list is defined here:
  * Q [total_q,hq,d] with q_seq_start int64 [batch+1] and q_seq_len = total_q; K/V pools [num_total_pages,page,hkv,d|dv];
  * kv_indptr int32 [batch+1], kv_page_indices int32 [kv_indptr[batch]], kv_last_page_len int32 [batch].
+ * bias_buf_ptr: NULL, or fp32 ALiBi slopes ([1,hq] / [batch,hq] by `bias_rank_info`) while the instance parameter
+ * `bias_enum` of family 0 is 2; any other bias is refused (this holds for FmhaFwdPagedKVPrefill and FmhaFwdSplitKV too).
  */
 FLASHCK_API int FmhaFwdBatchPrefill(void* q_buf_ptr, void* k_buf_ptr, void* v_buf_ptr, void* bias_buf_ptr, void* o_buf_ptr,
                         int64_t* q_seq_start_ptr, void* kv_indptr, void* kv_page_indices, void* kv_last_page_len,
