@@ -306,9 +306,11 @@ def fmha_fwd_paged_kv_prefill(q: torch.Tensor, k_pool: torch.Tensor, v_pool: tor
 def default_num_splits(batch: int, sm_count: int = 148, max_splits: int = 128, rows_per_kv_head: int = 1) -> int:
     """Workspace depth for ``fmha_fwd_splitkv`` when the caller passes ``num_splits=0``.
 
-    With more than 16 query rows per kv head (``seqlen_q * hq / hkv``) the call runs on the tcgen05 instance, whose
-    work items are pieces of at least 1024 keys, each one split (two with at most 64 rows): 16 splits keep its
-    148 CTAs evenly loaded for contexts up to 8k-16k keys.  Otherwise:
+    With more than 16 query rows per kv head (``seqlen_q * hq / hkv``) the call runs on the tcgen05 instance, which
+    cuts the key tiles of all (sequence, kv head) streams into one equal piece per SM; a stream cut k times uses k + 1
+    splits (twice that with at most 64 rows), and the piece is lengthened when the workspace has fewer.  16 splits
+    leave room for seven cuts of the longest stream, which measured the same as 8 and 32 on 32 sequences of 2k-16k
+    keys.  Otherwise:
 
     The kernel cuts the concatenated key stream of all sequences into one equal piece per SM, so a sequence of
     average length is touched by about ``sm_count / batch`` pieces; twice that (plus one for a piece boundary)
