@@ -1,0 +1,119 @@
+"""GPU tests at the full sizes of the BASELINE configurations, through properties that do not need the oracle on
+the whole problem: two independent kernel instances agree, the number of splits does not change the merged
+result, and the oracle confirms the shortest sequences (which it finishes in a second or two)."""
+import os
+import sys
+
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+from flashck_b200 import _lib, ops  # noqa: E402
+from helpers import assert_lse_close, assert_o_close  # noqa: E402
+from oracle import cpu as oracle  # noqa: E402
+
+pytestmark = pytest.mark.gpu
+
+
+def _bench():
+    import bench  # the workload generators of the benchmark: the same seeded shapes and value distributions
+    return bench
+
+
+def _shortest(lens, n):
+    return sorted(range(len(lens)), key=lambda i: lens[i])[:n]
+
+
+def _gather_pages(w, b):
+    """The K/V rows of sequence b of a paged workload, in token order, on the CPU."""
+    n, page = w["lens"][b], w["page"]
+    ids = w["table"][b, :-(-n // page)].long()
+    k = w["k"][ids].reshape(-1, w["hkv"], w["k"].shape[-1])[:n].cpu()
+    v = w["v"][ids].reshape(-1, w["hkv"], w["v"].shape[-1])[:n].cpu()
+    return k, v
+
+
+def test_config2_full_size_instances_agree_and_shortest_sequences_match_the_oracle():
+    bench = _bench()
+    dev = torch.device("cuda:0")
+    w = bench.make_prefill(1234, dev)
+
+    def run():
+        return ops.fmha_fwd_var_len(w["q"], w["k"], w["v"], w["cu"], w["cu"], w["max_len"], causal=True, return_lse=True)
+    o, lse = run()
+    _lib.set_instance_param(0, "use_sm100", 0)
+    try:
+        o_gen, lse_gen = run()
+    finally:
+        _lib.set_instance_param(0, "use_sm100", 1)
+    assert _lib.device_status() == 0
+    assert_o_close(o, o_gen, "tcgen05 instance against the general instance, config 2")
+    assert_lse_close(lse, lse_gen, "LSE, tcgen05 against general, config 2")
+    cu = w["cu"].cpu()
+    for b in _shortest(w["lens"], 3):
+        sl = slice(int(cu[b]), int(cu[b + 1]))
+        o_ref, lse_ref = oracle.fmha_fwd(w["q"][sl].cpu()[None], w["k"][sl].cpu()[None], w["v"][sl].cpu()[None],
+                                         mask_type=2, window=(-1, 0))
+        assert_o_close(o[sl], o_ref[0], f"sequence {b} against the oracle")
+        assert_lse_close(lse[:, sl], lse_ref[0], f"LSE of sequence {b} against the oracle")
+
+
+def test_config3_full_size_split_count_does_not_change_the_result_and_oracle_on_shortest():
+    bench = _bench()
+    dev = torch.device("cuda:0")
+    w = bench.make_decode(4321, dev)
+
+    def run(splits):
+        return ops.fmha_fwd_splitkv(w["q"], w["k"], w["v"], seqlen_k=w["seqlen"], block_table=w["table"],
+                                    num_splits=splits, return_lse=True)
+    o, lse = run(0)      # the default depth
+    o1, lse1 = run(1)    # one split per sequence: no merge arithmetic at all
+    o9, lse9 = run(9)
+    assert _lib.device_status() == 0
+    assert_o_close(o, o1, "default splits against one split, config 3")
+    assert_lse_close(lse, lse1, "LSE, default splits against one split")
+    assert_o_close(o9, o1, "nine splits against one split, config 3")
+    assert_lse_close(lse9, lse1, "LSE, nine splits against one split")
+    for b in _shortest(w["lens"], 3):
+        k, v = _gather_pages(w, b)
+        o_ref, lse_ref = oracle.fmha_fwd(w["q"][b:b + 1].cpu(), k[None], v[None])
+        assert_o_close(o[b:b + 1], o_ref, f"sequence {b} against the oracle")
+        assert_lse_close(lse[b:b + 1], lse_ref, f"LSE of sequence {b} against the oracle")
+
+
+def test_config4_full_size_append_then_decode_both_instances_and_oracle_on_shortest():
+    bench = _bench()
+    dev = torch.device("cuda:0")
+    w = bench.make_append_decode(777, dev)
+    cu_n, max_new = w["cu_new"], max(w["new"])
+    k_before = w["k"].clone()
+    q_rot = w["qn"].clone()
+    ops.fmha_fwd_append_kv(q_rot, w["k"], w["v"], w["kn"], w["vn"], w["ctx_len"], w["cos"], w["sin"],
+                           block_table=w["table"], cu_seqlens_q=cu_n, cu_seqlens_knew=cu_n)
+    # the append touched exactly the new tokens' slots: every other row of the K pool is bit for bit what it was
+    changed = (w["k"] != k_before).flatten(2).any(dim=2)  # [pages, page]
+    assert int(changed.sum()) <= sum(w["new"])
+    del k_before, changed
+
+    def run():
+        return ops.fmha_fwd_splitkv(q_rot, w["k"], w["v"], seqlen_k=w["seqlen"], block_table=w["table"], cu_seqlens_q=cu_n,
+                                    max_seqlen_q=max_new, causal=True, return_lse=True)
+    o, lse = run()
+    _lib.set_instance_param(0, "use_sm100_splitkv", 0)
+    try:
+        o_mma, lse_mma = run()
+    finally:
+        _lib.set_instance_param(0, "use_sm100_splitkv", 1)
+    assert _lib.device_status() == 0
+    assert_o_close(o, o_mma, "tcgen05 split modes against the mma.sync decode kernel, config 4")
+    assert_lse_close(lse, lse_mma, "LSE, tcgen05 against mma.sync, config 4")
+    cu = cu_n.cpu()
+    for b in _shortest(w["lens"], 3):
+        k, v = _gather_pages(w, b)
+        sl = slice(int(cu[b]), int(cu[b + 1]))
+        o_ref, lse_ref = oracle.fmha_fwd(q_rot[sl].cpu()[None], k[None], v[None], mask_type=2, window=(-1, 0))
+        assert_o_close(o[sl], o_ref[0], f"sequence {b} against the oracle")
+        assert_lse_close(lse[:, sl], lse_ref[0], f"LSE of sequence {b} against the oracle")
