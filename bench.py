@@ -47,6 +47,24 @@ def load_peaks():
     return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
 
 
+def load_traffic(key: str, scale: float = 1.0):
+    """DRAM bytes per launch of a kernel from its committed ncu capture (`profiles/traffic.json`), or None when the
+    kernel's source has changed since the capture (the record carries the SHA-256 of the source files it was taken
+    from), so that a stale figure is never printed beside a fresh timing."""
+    import hashlib
+    path = os.path.join(ROOT, "profiles", "traffic.json")
+    try:
+        with open(path) as f:
+            rec = json.load(f)[key]
+        for rel, want in rec["source_sha256"].items():
+            with open(os.path.join(ROOT, rel), "rb") as f:
+                if hashlib.sha256(f.read()).hexdigest() != want:
+                    return None
+        return rec["dram_bytes_per_launch"] * scale
+    except (OSError, KeyError, ValueError):
+        return None
+
+
 # ----------------------------------------------------------------------------------------------------
 # clocks
 # ----------------------------------------------------------------------------------------------------
@@ -265,30 +283,31 @@ def cpu_decode_sample(w, nseq=48):
 
 # ----------------------------------------------------------------------------------------------------
 def run_reference(args, rank):
-    """Reference arm: the CPU statement of the path on the host cores (rank 0 only)."""
+    """Reference arm: the CPU statement of the path on the host cores (rank 0 only), on the same workload as the GPU
+    arm: every step is all 16 sequences of BASELINE config 2 (about 4 s on 16 cores)."""
     if rank != 0:
         return
     dev = torch.device("cpu")
     w = make_prefill(1234, dev)
-    from oracle import cpu as oracle
-    # bounded sample per step so that warmup + steps end within minutes
-    budget = 3.0e11
     samples = []
     for _ in range(args.warmup):
-        cpu_prefill_sample(w, budget_flops=budget / 4)
+        cpu_prefill_sample(w, budget_flops=float("inf"))
     t_all = 0.0
     for _ in range(args.steps):
-        s = cpu_prefill_sample(w, budget_flops=budget)
+        s = cpu_prefill_sample(w, budget_flops=float("inf"))
         samples.append(s)
         t_all += s["seconds"]
-    val = sum(s["value"] * s["seconds"] for s in samples) / t_all
+    val = w["flops"] * args.steps / t_all / 1e12
     line = {
         "impl": "reference", "metric": "prefill_fmha_tflops", "value": val, "unit": "TFLOP/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * t_all / args.steps, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": "varlen causal batch prefill (BASELINE config 2): batch 16, 32/8 heads, hdim 128, "
-                               "L~U[512,4096] seed 1234", "note": "CPU statement of the path (oracle port); the "
-                               "reference's own kernels need ROCm + ck_tile"},
+        "config": {"workload": "varlen causal batch prefill (BASELINE config 2): batch 16, 32 q / 8 kv heads, "
+                               "hdim 128, L~U[512,4096] from seed 1234",
+                   "tokens_per_gpu": w["total"], "flops_per_gpu_step": w["flops"],
+                   "flop_count": "causal-effective 4*d*hq*sum L(L+1)/2",
+                   "note": "CPU statement of the path (oracle port) on the whole workload, all host threads; the "
+                           "reference's own kernels need ROCm + ck_tile"},
         "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": HOST_THREADS, "kind": "port",
                          "sample": samples[-1]["sample"]},
         "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -306,8 +325,6 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-decode", action="store_true")
     ap.add_argument("--small", action="store_true", help="reduced sizes (for profiler captures)")
-    ap.add_argument("--profile-append-decode", type=int, default=0, metavar="BATCH",
-                    help="profiler aid: only run the config 4 decode step (after one append) on BATCH sequences, no JSON")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -348,21 +365,6 @@ def main():
 
     peaks = load_peaks()
     steps, warmup = args.steps, max(args.warmup, 3)
-
-    if args.profile_append_decode > 0:  # a small, bounded run for `ncu -k ... -c ...` captures of the config 4 kernels
-        wa = make_append_decode(777, device, batch=args.profile_append_decode)
-        cu_n, max_new = wa["cu_new"], max(wa["new"])
-        S4 = ops.default_num_splits(len(wa["lens"]), rows_per_kv_head=max_new * (HQ // HKV))
-        ws4 = ops.splitkv_workspace(wa["qn"], D, S4, cu_n)
-        ops.fmha_fwd_append_kv(wa["qn"], wa["k"], wa["v"], wa["kn"], wa["vn"], wa["ctx_len"], wa["cos"], wa["sin"],
-                               block_table=wa["table"], cu_seqlens_q=cu_n, cu_seqlens_knew=cu_n)
-        for _ in range(max(steps, 1) + warmup):
-            ops.fmha_fwd_splitkv(wa["qn"], wa["k"], wa["v"], seqlen_k=wa["seqlen"], block_table=wa["table"],
-                                 cu_seqlens_q=cu_n, max_seqlen_q=max_new, num_splits=S4, causal=True, workspace=ws4)
-        torch.cuda.synchronize()
-        print(json.dumps({"profile_append_decode": {"batch": args.profile_append_decode, "tokens": sum(wa["lens"]),
-                                                    "algorithmic_bytes": wa["bytes"], "num_splits": S4}}))
-        return
 
     # ------------------------------------------------------------------ prefill (headline)
     if args.small:
@@ -461,8 +463,8 @@ def main():
                    "l2": "inputs (q,k,v,o > 600 MB) larger than the 126 MB L2", "parallelism": f"dp{world}"},
         "roofline": {"bound": "tensor", "achieved": kernel_tflops, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
                      "frac": kernel_tflops / peaks["bf16_tflops"],
-                     # DRAM bytes per launch from the ncu capture summarised in profiles/fmha_fwd_sm100_prefill_bf16.md
-                     "traffic": None if args.small else 1.406e9,
+                     # DRAM bytes per launch from the committed ncu capture of this kernel on this workload
+                     "traffic": None if args.small else load_traffic("prefill_config2"),
                      "algorithmic_bytes": 2.0 * w["total"] * (2 * HQ * D + 2 * HKV * D) + 4.0 * w["total"] * HQ,
                      "peak_source": peaks["source"] + " (burst bf16 GEMM)"},
         "e2e": {"value": e2e_val, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
@@ -538,8 +540,7 @@ def main():
                        "num_splits": S, "l2": "K/V pool (GBs) larger than L2"},
             "roofline": {"bound": "hbm", "achieved": gbs_gpu, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                          "frac": gbs_gpu / peaks["hbm_gbs"],
-                         # DRAM bytes of the split-KV launch from the ncu capture in profiles/fmha_fwd_sm100_prefill_bf16.md
-                         "traffic": None if args.small else 4.247e9, "peak_source": peaks["source"],
+                         "traffic": None if args.small else load_traffic("decode_config3"), "peak_source": peaks["source"],
                          "note": "split-KV kernel + combine kernel timed together"},
             "e2e": {"value": tot_bytes * dsteps / (ms_de * 1e-3) / 1e9, "unit": "GB/s",
                     "h2d_bytes_per_step": hq2.numel() * 2 + hs.numel() * 4 + ht.numel() * 4,
@@ -577,9 +578,9 @@ def main():
                        "algorithmic_bytes_per_gpu_step": a_bytes, "num_splits": S4},
             "roofline": {"bound": "hbm", "achieved": a_bytes * asteps / (ms_a * 1e-3) / 1e9, "peak": peaks["hbm_gbs"],
                          "unit": "GB/s", "frac": a_bytes * asteps / (ms_a * 1e-3) / 1e9 / peaks["hbm_gbs"],
-                         # DRAM bytes of the split-KV launch: an ncu capture of 8 sequences (79 056 cached tokens: 330.4 MB
-                         # read + written, profiles/fmha_fwd_sm100_splitkv_append_decode_bf16.md) scaled by the token count
-                         "traffic": 330.4e6 / 79056 * sum(wa["lens"]),
+                         # DRAM bytes of the split-KV launch: the record is an ncu capture of 8 sequences, stored per cached
+                         # token (the kernel reads every K/V byte once, so its traffic grows with the token count)
+                         "traffic": load_traffic("append_decode_config4_per_token", scale=float(sum(wa["lens"]))),
                          "peak_source": peaks["source"], "note": "append-KV + split-KV + combine kernels timed together"},
             "gpu_launches": 3 * asteps,
         }

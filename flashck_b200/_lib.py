@@ -26,6 +26,9 @@ SIGNATURES = {
     "FmhaFwdBatchPrefill": ([_P] * 9 + [_I64] * 9 + [_F, _I64, _I64, _U32, _P, _P, _I], _I),
     "FmhaFwdPagedKVPrefill": ([_P] * 9 + [_I64] * 9 + [_F, _I64, _I64, _U32, _P, _P, _I], _I),
     "FmhaFwdSplitKV": ([_P] * 11 + [_I64] * 11 + [_F, _I64, _I64, _U32, _P, _I], _I),
+    "FmhaFwdBatchPrefillEx": ([_P] * 9 + [_I64] * 9 + [_F, _I64, _I64, _U32, _P, _P, _I, _I, _I], _I),
+    "FmhaFwdPagedKVPrefillEx": ([_P] * 9 + [_I64] * 9 + [_F, _I64, _I64, _U32, _P, _P, _I, _I, _I, _I64], _I),
+    "FmhaFwdSplitKVEx": ([_P] * 11 + [_I64] * 11 + [_F, _I64, _I64, _U32, _P, _I, _I, _I, _I64], _I),
     "FmhaFwdSplitKVCombine": ([_P] * 4 + [_I64] * 6 + [_P, _P, _I], _I),
     "FmhaSplitKVCombine": ([_P] * 4 + [_I64] * 6 + [_P, _P, _I], _I),
     "FmhaFwdSplitKVCombineStrided": ([_P] * 4 + [_I64] * 5 + [ctypes.POINTER(_I64), ctypes.POINTER(_I64), _I, _P], _I),
@@ -64,10 +67,13 @@ def check(rc: int, what: str) -> None:
 
 
 def device_status() -> int:
-    """Reads and clears the device status word (non-zero: a bounded device-side wait ran out)."""
+    """Reads and clears the device status word (0: nothing to report; low 29 bits: a bounded device-side wait ran out;
+    0x20000000: a work list overflowed; 0x40000000: append-KV skipped tokens that did not fit the cache)."""
     out = ctypes.c_int(0)
-    check(lib().FlashckDeviceStatus(ctypes.byref(out)), "FlashckDeviceStatus")
-    return out.value
+    rc = lib().FlashckDeviceStatus(ctypes.byref(out))
+    if rc not in (0, 2, 4):  # 2 / 4: the word itself says what happened (skipped work / timeout)
+        check(rc, "FlashckDeviceStatus")
+    return out.value & 0xffffffff
 
 
 def set_instance_param(family: int, key: str, value: int) -> None:

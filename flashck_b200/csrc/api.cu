@@ -109,6 +109,21 @@ int alibi_from_bias(const char* fn, const void* bias, const float** slopes, int*
     return FLASHCK_OK;
 }
 
+// The same with the kind of bias stated per call (the ...Ex entry points): nothing process-wide is read.
+int alibi_explicit(const char* fn, const void* bias, int bias_enum, int bias_rank_info, const float** slopes, int* rank) {
+    *slopes = nullptr;
+    *rank = 0;
+    FCK_REQUIRE(bias_enum == 0 || bias_enum == 2, FLASHCK_ERR_UNSUPPORTED,
+                "%s: bias_enum must be 0 (none) or 2 (alibi); an elementwise bias has no layout over pages", fn);
+    if (bias_enum == 0) return FLASHCK_OK;
+    FCK_REQUIRE(bias != nullptr, FLASHCK_ERR_INVALID_ARGUMENT, "%s: bias_enum 2 without a slope buffer", fn);
+    FCK_REQUIRE(bias_rank_info == 0 || bias_rank_info == 1, FLASHCK_ERR_INVALID_ARGUMENT,
+                "%s: bias_rank_info must be 0 ([1,hq]) or 1 ([batch,hq]) for ALiBi", fn);
+    *slopes = (const float*)bias;
+    *rank = bias_rank_info;
+    return FLASHCK_OK;
+}
+
 inline float resolve_scale(float scale, int64_t d) {
     return scale == 0.f ? 1.f / sqrtf((float)d) : scale;  // fmha_fwd_jinja.h:57-59
 }
@@ -139,6 +154,16 @@ int FlashckDeviceStatus(int* status_out) {
         FCK_CUDA(cudaMemcpy(ptr, &zero, sizeof(int), cudaMemcpyHostToDevice));
     }
     if (status_out) *status_out = v;
+    if (v & FLASHCK_STATUS_TIMEOUT_MASK) {
+        set_last_error("a bounded device-side wait ran out (status word 0x%x)", (unsigned)v);
+        return FLASHCK_ERR_DEVICE_TIMEOUT;
+    }
+    if (v != 0) {
+        set_last_error("a kernel skipped work: %s%s(status word 0x%x)",
+                       (v & FLASHCK_STATUS_WORKLIST_OVERFLOW) ? "on-chip work list overflow " : "",
+                       (v & FLASHCK_STATUS_APPEND_OVERFLOW) ? "append past the cache capacity " : "", (unsigned)v);
+        return FLASHCK_ERR_UNSUPPORTED;
+    }
     return FLASHCK_OK;
 }
 
@@ -185,16 +210,13 @@ int FmhaFwdBias(void* q, void* k, void* v, void* bias, void* o, int64_t* q_seq_s
     return run_fwd(p, (cudaStream_t)stream);
 }
 
-int FmhaFwdBatchPrefill(void* q, void* k, void* v, void* bias, void* o, int64_t* q_seq_start, void* kv_indptr,
-                        void* kv_page_indices, void* kv_last_page_len, int64_t batch, int64_t q_seq_len, int64_t hq,
-                        int64_t hkv, int64_t d, int64_t dv, int64_t q_max_seq_len, int64_t num_total_pages,
-                        int64_t paged_block_size, float scale, int64_t window_left, int64_t window_right,
-                        uint32_t mask_type, void* stream, void* lse, int dtype) {
+static int batch_prefill_impl(void* q, void* k, void* v, const float* slopes, int slope_rank, void* o, int64_t* q_seq_start,
+                              void* kv_indptr, void* kv_page_indices, void* kv_last_page_len, int64_t batch,
+                              int64_t q_seq_len, int64_t hq, int64_t hkv, int64_t d, int64_t dv, int64_t q_max_seq_len,
+                              int64_t num_total_pages, int64_t paged_block_size, float scale, int64_t window_left,
+                              int64_t window_right, uint32_t mask_type, void* stream, void* lse, int dtype) {
     int rc = check_common("FmhaFwdBatchPrefill", dtype, hq, hkv, d, dv, nullptr);
     if (rc) return rc;
-    const float* slopes = nullptr;
-    int slope_rank = 0;
-    if ((rc = alibi_from_bias("FmhaFwdBatchPrefill", bias, &slopes, &slope_rank))) return rc;
     FCK_REQUIRE(q && k && v && o && q_seq_start && kv_indptr && kv_page_indices && kv_last_page_len,
                 FLASHCK_ERR_INVALID_ARGUMENT, "FmhaFwdBatchPrefill: null pointer argument");
     FCK_REQUIRE(paged_block_size > 0 && num_total_pages >= 0 && batch >= 0 && q_max_seq_len >= 0,
@@ -215,16 +237,41 @@ int FmhaFwdBatchPrefill(void* q, void* k, void* v, void* bias, void* o, int64_t*
     return run_fwd(p, (cudaStream_t)stream);
 }
 
-int FmhaFwdPagedKVPrefill(void* q, void* k, void* v, void* bias, void* o, int64_t* q_seq_start, void* k_seq_len,
-                          void* block_table, int64_t* cache_batch_idx, int64_t batch, int64_t q_seq_len, int64_t hq,
-                          int64_t hkv, int64_t d, int64_t dv, int64_t q_max_seq_len, int64_t max_num_page_blocks,
-                          int64_t paged_block_size, float scale, int64_t window_left, int64_t window_right,
-                          uint32_t mask_type, void* stream, void* lse, int dtype) {
-    int rc = check_common("FmhaFwdPagedKVPrefill", dtype, hq, hkv, d, dv, nullptr);
-    if (rc) return rc;
+int FmhaFwdBatchPrefill(void* q, void* k, void* v, void* bias, void* o, int64_t* q_seq_start, void* kv_indptr,
+                        void* kv_page_indices, void* kv_last_page_len, int64_t batch, int64_t q_seq_len, int64_t hq,
+                        int64_t hkv, int64_t d, int64_t dv, int64_t q_max_seq_len, int64_t num_total_pages,
+                        int64_t paged_block_size, float scale, int64_t window_left, int64_t window_right,
+                        uint32_t mask_type, void* stream, void* lse, int dtype) {
     const float* slopes = nullptr;
     int slope_rank = 0;
-    if ((rc = alibi_from_bias("FmhaFwdPagedKVPrefill", bias, &slopes, &slope_rank))) return rc;
+    if (int rc = alibi_from_bias("FmhaFwdBatchPrefill", bias, &slopes, &slope_rank)) return rc;
+    return batch_prefill_impl(q, k, v, slopes, slope_rank, o, q_seq_start, kv_indptr, kv_page_indices, kv_last_page_len,
+                              batch, q_seq_len, hq, hkv, d, dv, q_max_seq_len, num_total_pages, paged_block_size, scale,
+                              window_left, window_right, mask_type, stream, lse, dtype);
+}
+
+int FmhaFwdBatchPrefillEx(void* q, void* k, void* v, void* bias, void* o, int64_t* q_seq_start, void* kv_indptr,
+                          void* kv_page_indices, void* kv_last_page_len, int64_t batch, int64_t q_seq_len, int64_t hq,
+                          int64_t hkv, int64_t d, int64_t dv, int64_t q_max_seq_len, int64_t num_total_pages,
+                          int64_t paged_block_size, float scale, int64_t window_left, int64_t window_right,
+                          uint32_t mask_type, void* stream, void* lse, int dtype, int bias_enum, int bias_rank_info) {
+    const float* slopes = nullptr;
+    int slope_rank = 0;
+    if (int rc = alibi_explicit("FmhaFwdBatchPrefillEx", bias, bias_enum, bias_rank_info, &slopes, &slope_rank)) return rc;
+    return batch_prefill_impl(q, k, v, slopes, slope_rank, o, q_seq_start, kv_indptr, kv_page_indices, kv_last_page_len,
+                              batch, q_seq_len, hq, hkv, d, dv, q_max_seq_len, num_total_pages, paged_block_size, scale,
+                              window_left, window_right, mask_type, stream, lse, dtype);
+}
+
+static int paged_prefill_impl(void* q, void* k, void* v, const float* slopes, int slope_rank, void* o, int64_t* q_seq_start,
+                              void* k_seq_len, void* block_table, int64_t* cache_batch_idx, int64_t batch,
+                              int64_t q_seq_len, int64_t hq, int64_t hkv, int64_t d, int64_t dv, int64_t q_max_seq_len,
+                              int64_t max_num_page_blocks, int64_t paged_block_size, float scale, int64_t window_left,
+                              int64_t window_right, uint32_t mask_type, void* stream, void* lse, int dtype,
+                              int64_t num_pool_pages) {
+    int rc = check_common("FmhaFwdPagedKVPrefill", dtype, hq, hkv, d, dv, nullptr);
+    if (rc) return rc;
+    FCK_REQUIRE(num_pool_pages > 0, FLASHCK_ERR_INVALID_ARGUMENT, "FmhaFwdPagedKVPrefill: the K/V pools hold no page");
     FCK_REQUIRE(q && k && v && o && k_seq_len && block_table, FLASHCK_ERR_INVALID_ARGUMENT,
                 "FmhaFwdPagedKVPrefill: null pointer argument");
     FCK_REQUIRE(batch > 0 && paged_block_size > 0 && max_num_page_blocks % batch == 0, FLASHCK_ERR_INVALID_ARGUMENT,
@@ -239,24 +286,50 @@ int FmhaFwdPagedKVPrefill(void* q, void* k, void* v, void* bias, void* o, int64_
     p.max_seqlen_q = q_seq_start ? (q_max_seq_len > 0 ? q_max_seq_len : q_seq_len) : q_seq_len;
     p.bt_stride = max_num_page_blocks / batch;  // fmha_fwd_split_kv_jinja.h:318
     p.page = paged_block_size;
-    p.num_pages = max_num_page_blocks;  // the pools hold max_num_page_blocks pages (fmha_fwd_split_kv_jinja.h:512-519)
+    p.num_pages = num_pool_pages;  // extent of the pools' tensor maps: a page id at or beyond it reads as zeros
     p.scale = resolve_scale(scale, d);
     p.mask_type = (int)mask_type; p.wl = window_left; p.wr = window_right; p.dtype = dtype;
     if (slopes) { p.bias = slopes; p.bias_type = 2; p.bias_rank = slope_rank; }
     return run_fwd(p, (cudaStream_t)stream);
 }
 
-int FmhaFwdSplitKV(void* q, void* k, void* v, void* bias, void* lse_acc, void* o_acc, int64_t* q_seq_start,
-                   int64_t* kv_seq_start, void* k_seq_len, void* block_table, int64_t* cache_batch_idx, int64_t batch,
-                   int64_t q_seq_len, int64_t kv_seq_len, int64_t hq, int64_t hkv, int64_t d, int64_t dv,
-                   int64_t q_max_seq_len, int64_t num_splits, int64_t max_num_page_blocks, int64_t paged_block_size,
-                   float scale, int64_t window_left, int64_t window_right, uint32_t mask_type, void* stream,
-                   int dtype) {
-    int rc = check_common("FmhaFwdSplitKV", dtype, hq, hkv, d, dv, nullptr);
-    if (rc) return rc;
+int FmhaFwdPagedKVPrefill(void* q, void* k, void* v, void* bias, void* o, int64_t* q_seq_start, void* k_seq_len,
+                          void* block_table, int64_t* cache_batch_idx, int64_t batch, int64_t q_seq_len, int64_t hq,
+                          int64_t hkv, int64_t d, int64_t dv, int64_t q_max_seq_len, int64_t max_num_page_blocks,
+                          int64_t paged_block_size, float scale, int64_t window_left, int64_t window_right,
+                          uint32_t mask_type, void* stream, void* lse, int dtype) {
     const float* slopes = nullptr;
     int slope_rank = 0;
-    if ((rc = alibi_from_bias("FmhaFwdSplitKV", bias, &slopes, &slope_rank))) return rc;
+    if (int rc = alibi_from_bias("FmhaFwdPagedKVPrefill", bias, &slopes, &slope_rank)) return rc;
+    // the reference's pools hold exactly max_num_page_blocks pages (fmha_fwd_split_kv_jinja.h:512-519)
+    return paged_prefill_impl(q, k, v, slopes, slope_rank, o, q_seq_start, k_seq_len, block_table, cache_batch_idx, batch,
+                              q_seq_len, hq, hkv, d, dv, q_max_seq_len, max_num_page_blocks, paged_block_size, scale,
+                              window_left, window_right, mask_type, stream, lse, dtype, max_num_page_blocks);
+}
+
+int FmhaFwdPagedKVPrefillEx(void* q, void* k, void* v, void* bias, void* o, int64_t* q_seq_start, void* k_seq_len,
+                            void* block_table, int64_t* cache_batch_idx, int64_t batch, int64_t q_seq_len, int64_t hq,
+                            int64_t hkv, int64_t d, int64_t dv, int64_t q_max_seq_len, int64_t max_num_page_blocks,
+                            int64_t paged_block_size, float scale, int64_t window_left, int64_t window_right,
+                            uint32_t mask_type, void* stream, void* lse, int dtype, int bias_enum, int bias_rank_info,
+                            int64_t num_pool_pages) {
+    const float* slopes = nullptr;
+    int slope_rank = 0;
+    if (int rc = alibi_explicit("FmhaFwdPagedKVPrefillEx", bias, bias_enum, bias_rank_info, &slopes, &slope_rank)) return rc;
+    return paged_prefill_impl(q, k, v, slopes, slope_rank, o, q_seq_start, k_seq_len, block_table, cache_batch_idx, batch,
+                              q_seq_len, hq, hkv, d, dv, q_max_seq_len, max_num_page_blocks, paged_block_size, scale,
+                              window_left, window_right, mask_type, stream, lse, dtype, num_pool_pages);
+}
+
+static int splitkv_impl(void* q, void* k, void* v, const float* slopes, int slope_rank, void* lse_acc, void* o_acc,
+                        int64_t* q_seq_start, int64_t* kv_seq_start, void* k_seq_len, void* block_table,
+                        int64_t* cache_batch_idx, int64_t batch, int64_t q_seq_len, int64_t kv_seq_len, int64_t hq,
+                        int64_t hkv, int64_t d, int64_t dv, int64_t q_max_seq_len, int64_t num_splits,
+                        int64_t max_num_page_blocks, int64_t paged_block_size, float scale, int64_t window_left,
+                        int64_t window_right, uint32_t mask_type, void* stream, int dtype, int64_t num_pool_pages) {
+    int rc = check_common("FmhaFwdSplitKV", dtype, hq, hkv, d, dv, nullptr);
+    if (rc) return rc;
+    FCK_REQUIRE(!block_table || num_pool_pages > 0, FLASHCK_ERR_INVALID_ARGUMENT, "FmhaFwdSplitKV: the K/V pools hold no page");
     FCK_REQUIRE(q && k && v && o_acc, FLASHCK_ERR_INVALID_ARGUMENT, "FmhaFwdSplitKV: q, k, v and o_acc must not be null");
     FCK_REQUIRE(num_splits >= 1 && num_splits <= 1024, FLASHCK_ERR_INVALID_ARGUMENT,
                 "FmhaFwdSplitKV: num_splits must be in [1,1024] (got %lld)", (long long)num_splits);
@@ -277,18 +350,51 @@ int FmhaFwdSplitKV(void* q, void* k, void* v, void* bias, void* lse_acc, void* o
     p.num_splits = num_splits;
     p.total_q = q_seq_len;
     if (block_table) {
-        // the reference sizes the pool to max_num_page_blocks pages (:512-519); a serving pool is usually larger,
-        // so the page axis of the tensor map is left unbounded and page ids are trusted like any pointer
-        p.num_pages = (int64_t)1 << 30;
+        // extent of the pools' tensor maps: a stale or corrupt page id at or beyond it reads as zeros, not as memory
+        // outside the pools
+        p.num_pages = num_pool_pages;
         p.bt_stride = max_num_page_blocks / batch;
         p.page = paged_block_size;
     } else {
-        p.num_pages = cache_batch_idx ? 0 : batch;
+        // contiguous cache [rows, kv_seq_len, hkv, d]: `batch` rows, or (with cache_batch_idx) the row count the caller
+        // states through num_pool_pages; 0 = unknown
+        p.num_pages = cache_batch_idx ? (num_pool_pages > 0 ? num_pool_pages : 0) : batch;
     }
     p.scale = resolve_scale(scale, d);
     p.mask_type = (int)mask_type; p.wl = window_left; p.wr = window_right; p.dtype = dtype;
     if (splitkv_sm100_supported(p)) return launch_splitkv_sm100(p, (cudaStream_t)stream);
     return launch_splitkv_decode(p, (cudaStream_t)stream);
+}
+
+int FmhaFwdSplitKV(void* q, void* k, void* v, void* bias, void* lse_acc, void* o_acc, int64_t* q_seq_start,
+                   int64_t* kv_seq_start, void* k_seq_len, void* block_table, int64_t* cache_batch_idx, int64_t batch,
+                   int64_t q_seq_len, int64_t kv_seq_len, int64_t hq, int64_t hkv, int64_t d, int64_t dv,
+                   int64_t q_max_seq_len, int64_t num_splits, int64_t max_num_page_blocks, int64_t paged_block_size,
+                   float scale, int64_t window_left, int64_t window_right, uint32_t mask_type, void* stream,
+                   int dtype) {
+    const float* slopes = nullptr;
+    int slope_rank = 0;
+    if (int rc = alibi_from_bias("FmhaFwdSplitKV", bias, &slopes, &slope_rank)) return rc;
+    // the reference's pools hold exactly max_num_page_blocks pages (fmha_fwd_split_kv_jinja.h:512-519)
+    return splitkv_impl(q, k, v, slopes, slope_rank, lse_acc, o_acc, q_seq_start, kv_seq_start, k_seq_len, block_table,
+                        cache_batch_idx, batch, q_seq_len, kv_seq_len, hq, hkv, d, dv, q_max_seq_len, num_splits,
+                        max_num_page_blocks, paged_block_size, scale, window_left, window_right, mask_type, stream, dtype,
+                        block_table ? max_num_page_blocks : 0);
+}
+
+int FmhaFwdSplitKVEx(void* q, void* k, void* v, void* bias, void* lse_acc, void* o_acc, int64_t* q_seq_start,
+                     int64_t* kv_seq_start, void* k_seq_len, void* block_table, int64_t* cache_batch_idx, int64_t batch,
+                     int64_t q_seq_len, int64_t kv_seq_len, int64_t hq, int64_t hkv, int64_t d, int64_t dv,
+                     int64_t q_max_seq_len, int64_t num_splits, int64_t max_num_page_blocks, int64_t paged_block_size,
+                     float scale, int64_t window_left, int64_t window_right, uint32_t mask_type, void* stream, int dtype,
+                     int bias_enum, int bias_rank_info, int64_t num_pool_pages) {
+    const float* slopes = nullptr;
+    int slope_rank = 0;
+    if (int rc = alibi_explicit("FmhaFwdSplitKVEx", bias, bias_enum, bias_rank_info, &slopes, &slope_rank)) return rc;
+    return splitkv_impl(q, k, v, slopes, slope_rank, lse_acc, o_acc, q_seq_start, kv_seq_start, k_seq_len, block_table,
+                        cache_batch_idx, batch, q_seq_len, kv_seq_len, hq, hkv, d, dv, q_max_seq_len, num_splits,
+                        max_num_page_blocks, paged_block_size, scale, window_left, window_right, mask_type, stream, dtype,
+                        num_pool_pages);
 }
 
 int FmhaFwdSplitKVCombine(void* lse_acc, void* o_acc, void* o, int64_t* q_seq_start, int64_t batch, int64_t q_seq_len,

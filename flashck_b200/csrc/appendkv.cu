@@ -30,6 +30,8 @@ struct AppendDev {
     int batch, seqlen_q, seqlen_knew, hq, hkv, d, dv, rotary_dim, rope_type, bt_stride, page;
     int64_t seqlen_k_cap;
     int64_t total_new, total_q;
+    int64_t capacity;  // tokens one sequence's cache can hold: pages_per_sequence * page, or the contiguous row length
+    int* status;       // device status word: FLASHCK_STATUS_APPEND_OVERFLOW is ORed in when a token is skipped
 };
 
 // largest b with seqstart[b] <= t
@@ -85,11 +87,24 @@ __global__ void __launch_bounds__(128) appendkv_kernel(const AppendDev a) {
         }
         const int64_t pos = (int64_t)a.seqlen_k[b] + j;
         const int64_t bphys = a.cache_batch_idx ? a.cache_batch_idx[b] : b;
+        // The lengths live on the device, so a full cache can only be seen here: a token that does not fit its
+        // sequence's cache (or whose block-table entry is the negative filler of an unassigned page) is not written --
+        // it would land in another sequence's page or past the buffer -- and the status word says so.
+        if (pos < 0 || pos >= a.capacity) {
+            if (threadIdx.x == 0) atomicOr(a.status, FLASHCK_STATUS_APPEND_OVERFLOW);
+            return;
+        }
         int64_t row;
-        if (a.block_table)
-            row = (int64_t)a.block_table[bphys * a.bt_stride + pos / a.page] * a.page + pos % a.page;
-        else
+        if (a.block_table) {
+            const int32_t pg = a.block_table[bphys * a.bt_stride + pos / a.page];
+            if (pg < 0) {
+                if (threadIdx.x == 0) atomicOr(a.status, FLASHCK_STATUS_APPEND_OVERFLOW);
+                return;
+            }
+            row = (int64_t)pg * a.page + pos % a.page;
+        } else {
             row = bphys * a.seqlen_k_cap + pos;
+        }
         const T* ksrc = (const T*)a.knew + t * a.hkv * a.d;
         T* kdst = (T*)a.k_cache + row * a.hkv * a.d;
         rope_heads<T>(ksrc, kdst, a.hkv, a.d, half, a.rope_type, (const T*)a.cosr + pos * half,
@@ -128,7 +143,11 @@ int launch_appendkv(const AppendKVParams& p, cudaStream_t stream) {
     FCK_REQUIRE(p.rope_type >= 0 && p.rope_type <= 2, FLASHCK_ERR_INVALID_ARGUMENT, "appendkv: rope_type must be 0..2");
     FCK_REQUIRE(p.rope_type == 0 || (p.rotary_dim > 0 && p.rotary_dim <= p.d && p.rotary_dim % 2 == 0),
                 FLASHCK_ERR_INVALID_ARGUMENT, "appendkv: rotary_dim must be even and in (0, hdim_q]");
+    int* status = device_status_ptr();
+    if (!status) return FLASHCK_ERR_CUDA;
     AppendDev a;
+    a.status = status;
+    a.capacity = p.block_table ? p.bt_stride * p.page : p.seqlen_k_cap;
     a.q = p.q; a.k_cache = p.k_cache; a.knew = p.knew; a.v_cache = p.v_cache; a.vnew = p.vnew;
     a.seqlen_k = p.seqlen_k; a.seqstart_q = p.seqstart_q; a.seqstart_knew = p.seqstart_knew;
     a.cosr = p.rotary_cos; a.sinr = p.rotary_sin; a.block_table = p.block_table;

@@ -534,7 +534,7 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                 }
             }
             if (overflow) {  // the host checks an upper bound of this; never silently drop work
-                atomicOr(p.status, 0x20000000);
+                atomicOr(p.status, FLASHCK_STATUS_WORKLIST_OVERFLOW);
                 cnt = 0;
             }
             ctrl->split_items = cnt;
@@ -561,7 +561,7 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     const int total_items = SPLIT ? 0 : ctrl->level_start[p.num_levels];
     int rounds = SPLIT ? ctrl->split_items : (total_items + (int)gridDim.x - 1) / (int)gridDim.x;
     if (!SPLIT && rounds > kMaxRounds) {  // the host checks an upper bound of this; never silently drop work
-        if (threadIdx.x == 0) atomicOr(p.status, 0x20000000);
+        if (threadIdx.x == 0) atomicOr(p.status, FLASHCK_STATUS_WORKLIST_OVERFLOW);
         rounds = 0;
     }
     for (int rnd = warp; !SPLIT && rnd < rounds; rnd += NTHREADS / 32) {  // this CTA's work list
@@ -1216,10 +1216,10 @@ template <typename T, int NPOLY8, bool WINDOW, int SPLIT>
 int launch_t(const FwdParams& p, const Sm100Dev& dev, cudaStream_t stream) {
     const int64_t rows_q = p.seqstart_q ? p.total_q : p.batch * p.seqlen_q;
     const bool paged = p.block_table || p.kv_indptr;
-    // contiguous: group mode carries the packed total in seqlen_k.  Paged: the reference sizes its pools to
-    // max_num_page_blocks pages, a serving pool is usually larger, so the token axis is left unbounded and page ids
-    // are trusted like any pointer.
-    const int64_t rows_k = paged ? 0x7fffff00ll : (p.seqstart_k ? p.seqlen_k : p.batch * p.seqlen_k);
+    // contiguous: group mode carries the packed total in seqlen_k.  Paged: the token axis of the pools' maps ends with
+    // the pool (num_pages pages), so a stale or corrupt page id reads as zeros instead of memory outside the pools.
+    const int64_t rows_k = paged ? std::max<int64_t>(p.num_pages, 1) * p.page
+                                 : (p.seqstart_k ? p.seqlen_k : p.batch * p.seqlen_k);
     const int box_k = paged ? (int)std::min<int64_t>(p.page, BN) : BN;
     CUtensorMap mq, mk, mv, mo;
     int rc;
@@ -1272,6 +1272,7 @@ bool fwd_sm100_supported(const FwdParams& p) {
         if ((items + sm_count() - 1) / sm_count() > kMaxRounds) return false;
     }
     if (p.total_q >= (1ll << 31) || (!paged && p.batch * p.seqlen_k >= (1ll << 31))) return false;
+    if (paged && p.num_pages * p.page >= (1ll << 31)) return false;  // token rows of the pools are 31-bit coordinates
     if (p.batch * std::max<int64_t>(p.seqlen_q, 1) >= (1ll << 31)) return false;
     return true;
 }
@@ -1343,10 +1344,11 @@ int launch_split_t(const SplitKVParams& p, const Sm100Dev& dev, cudaStream_t str
     CUtensorMap mq, mk, mv;
     int rc;
     if ((rc = make_map_q_packed(&mq, p.q, p.dtype, tokens, p.hkv, p.hq / p.hkv, SPLIT == 2 ? 64 : BM))) return rc;
-    // Paged pools: the page ids are trusted like pointers, and a copy never leaves its page.  Contiguous cache
-    // [batch, capacity, hkv, 128]: the last 128-token chunk of a row reaches past the row's end, and past the end of the
-    // buffer in the last row; the map carries the true row count so that those rows are not read (they come as zeros).
-    const int64_t cache_rows = p.block_table ? 0x7fffff00ll : p.batch * p.seqlen_k_cap;
+    // Paged pools: the map ends with the pool (num_pages pages: a page id beyond it reads as zeros), and a copy never
+    // leaves its page.  Contiguous cache [batch, capacity, hkv, 128]: the last 128-token chunk of a row reaches past the
+    // row's end, and past the end of the buffer in the last row; the map carries the true row count so that those rows
+    // are not read (they come as zeros).
+    const int64_t cache_rows = p.block_table ? std::max<int64_t>(p.num_pages, 1) * p.page : p.batch * p.seqlen_k_cap;
     if ((rc = make_map_3d(&mk, p.k, p.dtype, cache_rows, p.hkv, box_k))) return rc;
     if ((rc = make_map_3d(&mv, p.v, p.dtype, cache_rows, p.hkv, box_k))) return rc;
     auto kern = fmha_fwd_sm100_kernel<T, 0, false, SPLIT>;
@@ -1396,6 +1398,7 @@ bool splitkv_sm100_supported(const SplitKVParams& p) {
     if (std::min(streams, w_max / kItemCost + 2) > kSplitItems) return false;
     const int64_t tokens = p.seqstart_q ? p.total_q : p.batch * p.seqlen_q;
     if (tokens >= (1ll << 31) || (!p.block_table && p.batch * p.seqlen_k_cap >= (1ll << 31))) return false;
+    if (p.block_table && p.num_pages * p.page >= (1ll << 31)) return false;
     return true;
 }
 

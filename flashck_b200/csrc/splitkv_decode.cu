@@ -449,8 +449,19 @@ splitkv_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
                     }
                 }
                 // ---- O += P V ----
+                // A tile that reaches past the end of its sequence holds, behind the end, whatever the cache had there (the
+                // tail of the last page, or the unused part of a contiguous row).  Those keys have P = 0, but 0 times a NaN
+                // or Inf in V is NaN, so their V rows are cleared in the fragments: this thread's B registers hold keys
+                // 2*qlane, 2*qlane + 1 (registers 0 and 2) and the same + 8 (registers 1 and 3) of the 16-key tile.
+                const bool v_tail = tok0 + NT * kTok > len;  // (warp-uniform)
 #pragma unroll
                 for (int u = 0; u < NT; ++u) {
+                    uint32_t vm0 = 0xffffffffu, vm1 = 0xffffffffu;
+                    if (v_tail) {
+                        const int k0 = tok0 + u * kTok + qlane * 2;
+                        vm0 = (k0 < len ? 0x0000ffffu : 0u) | (k0 + 1 < len ? 0xffff0000u : 0u);
+                        vm1 = (k0 + 8 < len ? 0x0000ffffu : 0u) | (k0 + 9 < len ? 0xffff0000u : 0u);
+                    }
                     uint32_t pa[4];
                     pa[0] = Elem<T>::pack2(sacc[2 * u][0], sacc[2 * u][1]);
                     pa[1] = Elem<T>::pack2(sacc[2 * u][2], sacc[2 * u][3]);
@@ -465,6 +476,12 @@ splitkv_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
                         uint32_t bfr[4];
                         ldmatrix_x4_trans(bfr,
                                           vbase[u] + (dh * HK + hw) * HEAD_BYTES + key * 128 + ((c ^ (key & 7)) << 4));
+                        if (v_tail) {
+                            bfr[0] &= vm0;
+                            bfr[1] &= vm1;
+                            bfr[2] &= vm0;
+                            bfr[3] &= vm1;
+                        }
                         mma_16816<T>(o[2 * j], pa, bfr[0], bfr[1]);
                         mma_16816<T>(o[2 * j + 1], pa, bfr[2], bfr[3]);
                     }

@@ -63,11 +63,23 @@ extern "C" FLASHCK_API int FmhaFwdSplitKVStatic(void* q, void* k, void* v, void*
     FCK_REQUIRE(q && k && v && o, FLASHCK_ERR_INVALID_ARGUMENT, "FmhaFwdSplitKVStatic: q, k, v and o must not be null");
     FCK_REQUIRE(batch > 0 && q_seq_len >= 0 && hq > 0 && dv > 0 && num_splits >= 1 && num_splits <= 1024,
                 FLASHCK_ERR_INVALID_ARGUMENT, "FmhaFwdSplitKVStatic: bad batch / q_seq_len / heads / num_splits");
-    // workspace sizes in the layout of the regular entry points
+    // workspace sizes in the layout of the regular entry points.  The row count is formed in 128 bits from factors below
+    // 2^31 each, so that no absurd argument can wrap around and slip under the capacity check.
+    constexpr int64_t kFactorMax = 0x7fffffff;
+    FCK_REQUIRE(batch <= kFactorMax && q_seq_len <= kFactorMax && hq <= kFactorMax && dv <= kFactorMax,
+                FLASHCK_ERR_INVALID_ARGUMENT, "FmhaFwdSplitKVStatic: a size argument is 2^31 or larger");
     const int64_t bs = q_seq_start ? 1 : batch;
-    const size_t lse_bytes = (size_t)bs * hq * num_splits * q_seq_len * sizeof(float);
+    const unsigned __int128 rows128 = (unsigned __int128)bs * (unsigned __int128)hq * (unsigned __int128)num_splits *
+                                      (unsigned __int128)q_seq_len;
+    FCK_REQUIRE(rows128 * (unsigned __int128)(dv + 1) * sizeof(float) <= (unsigned __int128)kStaticScratchBytes,
+                FLASHCK_ERR_UNSUPPORTED,
+                "FmhaFwdSplitKVStatic: workspaces need more than the %zu bytes of the built-in scratch "
+                "(batch %lld x heads %lld x splits %lld x rows %lld x (hdim %lld + 1) floats); lower num_splits or use "
+                "FmhaFwdSplitKV with caller-owned workspaces",
+                kStaticScratchBytes, (long long)bs, (long long)hq, (long long)num_splits, (long long)q_seq_len, (long long)dv);
+    const size_t lse_bytes = (size_t)rows128 * sizeof(float);
     const size_t lse_padded = (lse_bytes + 255) & ~(size_t)255;
-    const size_t o_bytes = (size_t)bs * hq * num_splits * q_seq_len * dv * sizeof(float);
+    const size_t o_bytes = (size_t)rows128 * (size_t)dv * sizeof(float);
     FCK_REQUIRE(lse_padded + o_bytes <= kStaticScratchBytes, FLASHCK_ERR_UNSUPPORTED,
                 "FmhaFwdSplitKVStatic: workspaces need %zu bytes, the built-in scratch holds %zu; lower num_splits "
                 "or use FmhaFwdSplitKV with caller-owned workspaces",

@@ -13,9 +13,7 @@ functions take packed ``[total, h, d]`` tensors plus ``cu_seqlens`` (int64 ``[b+
 """
 from __future__ import annotations
 
-import contextlib
 import ctypes
-import threading
 from typing import Optional, Sequence, Tuple
 
 import torch
@@ -102,29 +100,16 @@ def _as_i32(name: str, t: torch.Tensor) -> torch.Tensor:
 # --------------------------------------------------------------------------------------------
 # dense / varlen forward
 # --------------------------------------------------------------------------------------------
-_ALIBI_LOCK = threading.Lock()
-
-
-@contextlib.contextmanager
-def _alibi_instance(alibi_slopes: Optional[torch.Tensor], batch: int, hq: int):
-    """The paged and split-KV symbols keep the reference's argument lists, in which the kind of bias is a property of
-    the compiled instance: while the call is made the instance parameters of the family say that the bias pointer holds
-    ALiBi slopes (fp32 ``[1|batch, hq]``).  Yields the pointer to pass as ``bias_buf_ptr``."""
+def _alibi_args(alibi_slopes: Optional[torch.Tensor], batch: int, hq: int):
+    """(pointer, bias_enum, bias_rank_info) for the ``...Ex`` symbols of the paged and split-KV families, which take the
+    kind of bias per call (ALiBi slopes fp32 ``[1|batch, hq]`` or nothing), so that no process-wide instance parameter
+    is touched on the launch path."""
     if alibi_slopes is None:
-        yield ctypes.c_void_p(0)
-        return
+        return ctypes.c_void_p(0), 0, 0
     _check_cuda("alibi_slopes", alibi_slopes, torch.float32)
     if alibi_slopes.dim() != 2 or alibi_slopes.shape[1] != hq or alibi_slopes.shape[0] not in (1, batch):
         raise ValueError(f"alibi_slopes must be fp32 [1|{batch}, {hq}], got {tuple(alibi_slopes.shape)}")
-    with _ALIBI_LOCK:
-        old = (_lib.get_instance_param(0, "bias_enum"), _lib.get_instance_param(0, "bias_rank_info"))
-        _lib.set_instance_param(0, "bias_enum", 2)
-        _lib.set_instance_param(0, "bias_rank_info", 0 if alibi_slopes.shape[0] == 1 else 1)
-        try:
-            yield _ptr(alibi_slopes)
-        finally:
-            _lib.set_instance_param(0, "bias_enum", old[0])
-            _lib.set_instance_param(0, "bias_rank_info", old[1])
+    return _ptr(alibi_slopes), 2, (0 if alibi_slopes.shape[0] == 1 else 1)
 
 
 def _bias_args(q: torch.Tensor, bias, alibi_slopes, batch: int, hq: int, sq: int, sk: int):
@@ -247,11 +232,12 @@ def batch_prefill(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, c
     mt, wl, wr = _mask(causal, window_size, mask_type)
     o = torch.empty((total_q, hq, dv), dtype=q.dtype, device=q.device)
     lse = torch.empty((hq, total_q), dtype=torch.float32, device=q.device) if return_lse else None
-    with torch.cuda.device(q.device), _alibi_instance(alibi_slopes, batch, hq) as bias_ptr:
-        rc = _lib.lib().FmhaFwdBatchPrefill(_ptr(q), _ptr(k_pool), _ptr(v_pool), bias_ptr, _ptr(o), _ptr(cu_q),
-                                            _ptr(indptr), _ptr(indices), _ptr(last), batch, total_q, hq, hkv, d, dv,
-                                            int(max_seqlen_q), pages, page, float(scale or 0.0), wl, wr, mt,
-                                            _stream(), _ptr(lse), _dtype_code(q))
+    bias_ptr, bias_enum, bias_rank = _alibi_args(alibi_slopes, batch, hq)
+    with torch.cuda.device(q.device):
+        rc = _lib.lib().FmhaFwdBatchPrefillEx(_ptr(q), _ptr(k_pool), _ptr(v_pool), bias_ptr, _ptr(o), _ptr(cu_q),
+                                              _ptr(indptr), _ptr(indices), _ptr(last), batch, total_q, hq, hkv, d, dv,
+                                              int(max_seqlen_q), pages, page, float(scale or 0.0), wl, wr, mt,
+                                              _stream(), _ptr(lse), _dtype_code(q), bias_enum, bias_rank)
     _lib.check(rc, "FmhaFwdBatchPrefill")
     return (o, lse) if return_lse else o
 
@@ -291,11 +277,12 @@ def fmha_fwd_paged_kv_prefill(q: torch.Tensor, k_pool: torch.Tensor, v_pool: tor
     mt, wl, wr = _mask(causal, window_size, mask_type)
     o = torch.empty(o_shape + (dv,), dtype=q.dtype, device=q.device)
     lse = torch.empty(lse_shape, dtype=torch.float32, device=q.device) if return_lse else None
-    with torch.cuda.device(q.device), _alibi_instance(alibi_slopes, batch, hq) as bias_ptr:
-        rc = _lib.lib().FmhaFwdPagedKVPrefill(_ptr(q), _ptr(k_pool), _ptr(v_pool), bias_ptr, _ptr(o), _ptr(cu_q), _ptr(sl),
-                                              _ptr(bt), _ptr(cbi), batch, shape_sq, hq, hkv, d, dv, max_sq,
-                                              batch * bt.shape[1], page, float(scale or 0.0), wl, wr, mt, _stream(),
-                                              _ptr(lse), _dtype_code(q))
+    bias_ptr, bias_enum, bias_rank = _alibi_args(alibi_slopes, batch, hq)
+    with torch.cuda.device(q.device):
+        rc = _lib.lib().FmhaFwdPagedKVPrefillEx(_ptr(q), _ptr(k_pool), _ptr(v_pool), bias_ptr, _ptr(o), _ptr(cu_q),
+                                                _ptr(sl), _ptr(bt), _ptr(cbi), batch, shape_sq, hq, hkv, d, dv, max_sq,
+                                                batch * bt.shape[1], page, float(scale or 0.0), wl, wr, mt, _stream(),
+                                                _ptr(lse), _dtype_code(q), bias_enum, bias_rank, pages)
     _lib.check(rc, "FmhaFwdPagedKVPrefill")
     return (o, lse) if return_lse else o
 
@@ -460,12 +447,14 @@ def fmha_fwd_splitkv(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
         lse_acc, o_acc = workspace
         S = o_acc.shape[2]
     mt, wl, wr = _mask(causal, window_size, mask_type)
-    with torch.cuda.device(q.device), _alibi_instance(alibi_slopes, batch, hq) as bias_ptr:
-        rc = _lib.lib().FmhaFwdSplitKV(_ptr(q), _ptr(k_cache), _ptr(v_cache), bias_ptr, _ptr(lse_acc), _ptr(o_acc),
-                                       _ptr(cu_q), _ptr(cu_k), _ptr(sl), _ptr(bt), _ptr(cbi), batch, shape_sq,
-                                       shape_sk, hq, hkv, d, dv, max_sq, S,
-                                       max_pages, page,
-                                       float(scale or 0.0), wl, wr, mt, _stream(), _dtype_code(q))
+    bias_ptr, bias_enum, bias_rank = _alibi_args(alibi_slopes, batch, hq)
+    # pages of a paged pool, or rows of a contiguous cache (packed K/V: unused): where the K/V tensor maps end
+    pool_extent = 0 if cu_k is not None else k_cache.shape[0]
+    with torch.cuda.device(q.device):
+        rc = _lib.lib().FmhaFwdSplitKVEx(_ptr(q), _ptr(k_cache), _ptr(v_cache), bias_ptr, _ptr(lse_acc), _ptr(o_acc),
+                                         _ptr(cu_q), _ptr(cu_k), _ptr(sl), _ptr(bt), _ptr(cbi), batch, shape_sq,
+                                         shape_sk, hq, hkv, d, dv, max_sq, S, max_pages, page, float(scale or 0.0), wl,
+                                         wr, mt, _stream(), _dtype_code(q), bias_enum, bias_rank, pool_extent)
     _lib.check(rc, "FmhaFwdSplitKV")
     if not combine:
         return lse_acc, o_acc

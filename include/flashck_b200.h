@@ -53,12 +53,19 @@ extern "C" {
 #define FLASHCK_ERR_CUDA 3               /* a CUDA runtime / driver call failed */
 #define FLASHCK_ERR_DEVICE_TIMEOUT 4     /* a bounded device-side wait ran out */
 
+/* Bits of the device status word (FlashckDeviceStatus).  The low 29 bits are set by bounded device-side waits that
+ * ran out (each kernel role has its own code); the two bits below report work that a kernel refused to do. */
+#define FLASHCK_STATUS_TIMEOUT_MASK 0x1fffffff
+#define FLASHCK_STATUS_WORKLIST_OVERFLOW 0x20000000 /* an on-chip work list was too small: the launch did nothing */
+#define FLASHCK_STATUS_APPEND_OVERFLOW 0x40000000   /* FmhaFwdAppendKV skipped tokens that did not fit the cache */
+
 /* Human-readable text of the last error raised on the calling thread. */
 FLASHCK_API const char* FlashckGetLastError(void);
 /* Library version string. */
 FLASHCK_API const char* FlashckVersion(void);
-/* Reads and clears the device-side status word of the current device (0 = no bounded wait ran out).
- * Synchronises the device. */
+/* Reads and clears the device-side status word of the current device into *status_out (0 = nothing to report).
+ * Synchronises the device.  Returns FLASHCK_ERR_DEVICE_TIMEOUT when a bounded wait ran out, FLASHCK_ERR_UNSUPPORTED
+ * when a kernel skipped work (one of the two bits above), FLASHCK_OK when the word was 0. */
 FLASHCK_API int FlashckDeviceStatus(int* status_out);
 
 /*
@@ -132,7 +139,9 @@ FLASHCK_API int FmhaFwdPagedKVPrefill(void* q_buf_ptr, void* k_buf_ptr, void* v_
  * (fmha_fwd_split_kv_jinja.h:543-547; group mode: b = 1, sq = total_q).  A split that received no keys gets
  * lse_acc = -inf.  lse_acc may be NULL only when num_splits == 1.
  * Paged: K/V pools [max_num_page_blocks, page, hkv, d|dv] (:512-519), block_table int32
- * [batch, max_num_page_blocks / batch] (:318,550), k_seq_len_ptr int32 [batch] (required when paged).
+ * [batch, max_num_page_blocks / batch] (:318,550), k_seq_len_ptr int32 [batch] (required when paged).  The pools'
+ * tensor maps end after max_num_page_blocks pages (a page id beyond that reads as zeros); pools of another size go
+ * through FmhaFwdSplitKVEx.
  * How the key range of a sequence is cut into splits is internal (balanced over the SMs); only
  * "at most num_splits splits per sequence" is guaranteed.
  */
@@ -143,6 +152,42 @@ FLASHCK_API int FmhaFwdSplitKV(void* q_buf_ptr, void* k_buf_ptr, void* v_buf_ptr
                    int64_t v_head_dim, int64_t q_max_seq_len, int64_t num_splits, int64_t max_num_page_blocks,
                    int64_t paged_block_size, float scale, int64_t window_left, int64_t window_right,
                    uint32_t mask_type, void* stream, int dtype);
+
+/*
+ * FmhaFwdBatchPrefillEx / FmhaFwdPagedKVPrefillEx / FmhaFwdSplitKVEx -- the three paged entry points with what the
+ * reference compiles into an instance, or implies, stated per call (the relation of FmhaFwdBias to FmhaFwd):
+ *   bias_enum, bias_rank_info   how bias_buf_ptr is read: 0 = ignored, 2 = fp32 ALiBi slopes ([1,hq] for rank 0,
+ *                               [batch,hq] for rank 1; core/profiling/attention/fmha_library.h:121-164).  No
+ *                               process-wide instance parameter is consulted, so concurrent callers cannot disturb each
+ *                               other.
+ *   num_pool_pages              pages the K/V pools really hold.  The reference sizes its pools to max_num_page_blocks
+ *                               (= batch * pages_per_sequence, fmha_fwd_split_kv_jinja.h:512-519), which the plain
+ *                               symbols assume; a serving pool is shared by more sequences than one call sees.  The
+ *                               pools' tensor maps end at this extent: a page id at or beyond it reads as zeros.
+ *                               FmhaFwdSplitKVEx on a contiguous cache with cache_batch_idx: rows of the cache (0 = unknown).
+ * All other arguments are those of the plain symbols.
+ */
+FLASHCK_API int FmhaFwdBatchPrefillEx(void* q_buf_ptr, void* k_buf_ptr, void* v_buf_ptr, void* bias_buf_ptr, void* o_buf_ptr,
+                          int64_t* q_seq_start_ptr, void* kv_indptr, void* kv_page_indices, void* kv_last_page_len,
+                          int64_t batch, int64_t q_seq_len, int64_t q_num_heads, int64_t kv_num_heads,
+                          int64_t qk_head_dim, int64_t v_head_dim, int64_t q_max_seq_len, int64_t num_total_pages,
+                          int64_t paged_block_size, float scale, int64_t window_left, int64_t window_right,
+                          uint32_t mask_type, void* stream, void* lse_ptr, int dtype, int bias_enum, int bias_rank_info);
+FLASHCK_API int FmhaFwdPagedKVPrefillEx(void* q_buf_ptr, void* k_buf_ptr, void* v_buf_ptr, void* bias_buf_ptr, void* o_buf_ptr,
+                            int64_t* q_seq_start_ptr, void* k_seq_len_ptr, void* block_table_buf_ptr,
+                            int64_t* cache_batch_idx_buf_ptr, int64_t batch, int64_t q_seq_len, int64_t q_num_heads,
+                            int64_t kv_num_heads, int64_t qk_head_dim, int64_t v_head_dim, int64_t q_max_seq_len,
+                            int64_t max_num_page_blocks, int64_t paged_block_size, float scale, int64_t window_left,
+                            int64_t window_right, uint32_t mask_type, void* stream, void* lse_ptr, int dtype,
+                            int bias_enum, int bias_rank_info, int64_t num_pool_pages);
+FLASHCK_API int FmhaFwdSplitKVEx(void* q_buf_ptr, void* k_buf_ptr, void* v_buf_ptr, void* bias_buf_ptr, void* lse_acc_buf_ptr,
+                     void* o_acc_buf_ptr, int64_t* q_seq_start_ptr, int64_t* kv_seq_start_ptr, void* k_seq_len_ptr,
+                     void* block_table_buf_ptr, int64_t* cache_batch_idx_buf_ptr, int64_t batch, int64_t q_seq_len,
+                     int64_t kv_seq_len, int64_t q_num_heads, int64_t kv_num_heads, int64_t qk_head_dim,
+                     int64_t v_head_dim, int64_t q_max_seq_len, int64_t num_splits, int64_t max_num_page_blocks,
+                     int64_t paged_block_size, float scale, int64_t window_left, int64_t window_right,
+                     uint32_t mask_type, void* stream, int dtype, int bias_enum, int bias_rank_info,
+                     int64_t num_pool_pages);
 
 /*
  * FmhaFwdSplitKVCombine -- LSE-weighted merge of the split partials into O (and LSE).
@@ -183,7 +228,9 @@ FLASHCK_API int FmhaFwdSplitKVCombineStrided(void* lse_acc_buf_ptr, void* o_acc_
  *   knew/vnew: [b,n,hkv,d|dv] or group mode [total_new,hkv,*] (knew_seq_start int64 [b+1]).
  *   k/v cache: paged pool [pages,page,hkv,*] + block_table int32 [b, max_num_page_blocks/b], or contiguous
  *      [b_cache, kv_seq_len, hkv, *] when block_table is NULL.  New token j lands at seqlen_k[b] + j.
- *   k_seq_len_ptr: int32 [b], cached length BEFORE the append (not updated by the call).
+ *   k_seq_len_ptr: int32 [b], cached length BEFORE the append (not updated by the call).  A new token that does not
+ *      fit its sequence's cache (position >= pages_per_sequence * page, or >= kv_seq_len of a contiguous cache, or a
+ *      negative block-table entry) is skipped and FLASHCK_STATUS_APPEND_OVERFLOW is set in the device status word.
  *   rotary_cos/sin: [positions, rotary_dim/2] in the element dtype, indexed by absolute position.
  * Cache contents are bit-exact against the CPU statement of the same arithmetic: fp32 products and sums,
  * each rounded separately (no FMA), round-to-nearest-even narrowing.

@@ -10,10 +10,12 @@ LSE_ATOL = 1e-3
 def assert_o_close(got, ref, what="O"):
     got, ref = got.float().cpu(), ref.float().cpu()
     assert got.shape == ref.shape, (what, got.shape, ref.shape)
+    if torch.isfinite(ref).all():
+        assert torch.isfinite(got).all(), f"{what}: {int((~torch.isfinite(got)).sum())} of {got.numel()} values are NaN or Inf"
     err = (got - ref).abs()
     bound = O_ATOL + O_RTOL * ref.abs()
-    bad = err > bound
-    assert not bad.any(), f"{what}: {int(bad.sum())} of {bad.numel()} outside 2e-2 abs/rel, max err {float(err.max()):.4g}"
+    bad = ~(err <= bound)  # written as a negation so that a NaN error counts as a failure
+    assert not bad.any(), f"{what}: {int(bad.sum())} of {bad.numel()} outside 2e-2 abs/rel, max err {float(err[~torch.isnan(err)].max()) if (~torch.isnan(err)).any() else float('nan'):.4g}"
 
 
 def assert_lse_close(got, ref, what="LSE"):
@@ -21,9 +23,10 @@ def assert_lse_close(got, ref, what="LSE"):
     assert got.shape == ref.shape, (what, got.shape, ref.shape)
     inf_g, inf_r = torch.isinf(got), torch.isinf(ref)
     assert torch.equal(inf_g, inf_r), f"{what}: -inf pattern differs"
+    assert not torch.isnan(got).any(), f"{what}: {int(torch.isnan(got).sum())} NaN values"
     if (~inf_r).any():
         err = (got[~inf_r] - ref[~inf_r]).abs().max()
-        assert err <= LSE_ATOL, f"{what}: max err {float(err):.4g} > 1e-3"
+        assert bool(err <= LSE_ATOL), f"{what}: max err {float(err):.4g} > 1e-3"
 
 
 def assert_bits_equal(got, ref, what="cache"):

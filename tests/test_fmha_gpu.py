@@ -690,6 +690,36 @@ def test_appendkv_contiguous_batch_mode():
     assert_bits_equal(qd, q_ref, "rotated q")
 
 
+def test_appendkv_full_cache_skips_the_tokens_and_reports_it():
+    """A token that does not fit its sequence's cache is not written and the status word says so.  Sequence 0 fills its
+    two pages (32 tokens) and is asked to take 3 more: the block-table entry such a token would index is the first entry
+    of sequence 1's row (a valid page of the pool, so that even a missing guard would stay inside the pool), and that
+    page must come out unchanged.  Sequence 1 has room and takes its token."""
+    dtype, hq, hkv, d, page = torch.bfloat16, 4, 2, 128, 16
+    lens, new = [32, 10], [3, 1]
+    cache = make_paged_cache(lens, hkv, d, d, page, dtype, seed=14, capacity=[32, 32])
+    assert cache.block_table.shape[1] == 2
+    cu_n = to_seqstarts(new)
+    total = int(cu_n[-1])
+    q = normal_tensor((total, hq, d), dtype, 111)
+    knew = normal_tensor((total, hkv, d), dtype, 112)
+    vnew = normal_tensor((total, hkv, d), dtype, 113)
+    cos, sin = rotary_cos_sin(64, d, dtype)
+    # expected: only sequence 1's token lands (oracle run on that sequence alone)
+    q1, k_ref, v_ref = q[3:].clone(), cache.k.clone(), cache.v.clone()
+    oracle.fmha_fwd_appendkv(q1, k_ref, knew[3:].contiguous(), v_ref, vnew[3:].contiguous(), cache.seqlen_k[1:], cos, sin,
+                             rope_type=1, block_table=cache.block_table[1:].contiguous(), seqstart_q=to_seqstarts([1]),
+                             seqstart_knew=to_seqstarts([1]))
+    assert _lib.device_status() == 0
+    kd, vd = _cu(cache.k), _cu(cache.v)
+    ops.fmha_fwd_append_kv(_cu(q), kd, vd, _cu(knew), _cu(vnew), _cu(cache.seqlen_k), _cu(cos), _cu(sin),
+                           block_table=_cu(cache.block_table), cu_seqlens_q=_cu(cu_n), cu_seqlens_knew=_cu(cu_n))
+    assert_bits_equal(kd, k_ref, "k cache")
+    assert_bits_equal(vd, v_ref, "v cache")
+    assert _lib.device_status() == 0x40000000  # FLASHCK_STATUS_APPEND_OVERFLOW; reading clears it
+    assert _lib.device_status() == 0
+
+
 def test_append_then_decode_config4_small():
     # BASELINE config 4 flow at reduced size: append 1..16 tokens with interleaved RoPE, then split-KV decode
     dtype = torch.bfloat16

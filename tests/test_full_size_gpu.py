@@ -1,6 +1,9 @@
 """GPU tests at the full sizes of the BASELINE configurations, through properties that do not need the oracle on
 the whole problem: two independent kernel instances agree, the number of splits does not change the merged
-result, and the oracle confirms the shortest sequences (which it finishes in a second or two)."""
+result, the oracle confirms the shortest sequences (which it finishes in a second or two) and, on the longest
+sequences -- where the lazy rescale of the running max, the 31-bit row arithmetic and the bounds of the work lists
+matter -- sampled query rows (prefill: one row costs L*d multiply-adds per head) or whole sequences (decode: a few
+rows each)."""
 import os
 import sys
 
@@ -25,6 +28,19 @@ def _bench():
 
 def _shortest(lens, n):
     return sorted(range(len(lens)), key=lambda i: lens[i])[:n]
+
+
+def _longest(lens, n):
+    return sorted(range(len(lens)), key=lambda i: -lens[i])[:n]
+
+
+def _sample_rows(L, n, seed):
+    """Row indices of a sequence of L rows: both ends, the rows either side of every 128-row tile edge near the ends
+    and the middle, and seeded random ones."""
+    g = torch.Generator().manual_seed(seed)
+    fixed = [0, 1, 126, 127, 128, 129, L // 2 // 128 * 128 - 1, L // 2 // 128 * 128, L - 130, L - 129, L - 128, L - 2, L - 1]
+    rnd = torch.randint(0, L, (n,), generator=g).tolist()
+    return sorted({r for r in fixed + rnd if 0 <= r < L})
 
 
 def _gather_pages(w, b):
@@ -61,6 +77,29 @@ def test_config2_full_size_instances_agree_and_shortest_sequences_match_the_orac
         assert_lse_close(lse[:, sl], lse_ref[0], f"LSE of sequence {b} against the oracle")
 
 
+def test_config2_full_size_sampled_rows_of_the_longest_sequences_match_the_oracle():
+    """Causal row i of a sequence sees keys 0..i, so its O and LSE for all heads are an unmasked attention of one query
+    row over the first i + 1 keys: the oracle computes exactly that, for about 40 rows of each of the three longest
+    sequences of BASELINE config 2 (lengths close to 4096)."""
+    bench = _bench()
+    dev = torch.device("cuda:0")
+    w = bench.make_prefill(1234, dev)
+    o, lse = ops.fmha_fwd_var_len(w["q"], w["k"], w["v"], w["cu"], w["cu"], w["max_len"], causal=True, return_lse=True)
+    assert _lib.device_status() == 0
+    cu = w["cu"].cpu()
+    o, lse = o.cpu(), lse.cpu()
+    checked = 0
+    for b in _longest(w["lens"], 3):
+        s0, L = int(cu[b]), w["lens"][b]
+        qb, kb, vb = (w[n][s0:s0 + L].cpu() for n in ("q", "k", "v"))
+        for i in _sample_rows(L, 28, seed=100 + b):
+            o_ref, lse_ref = oracle.fmha_fwd(qb[i:i + 1][None], kb[None, :i + 1].contiguous(), vb[None, :i + 1].contiguous())
+            assert_o_close(o[s0 + i], o_ref[0, 0], f"sequence {b} (L={L}) row {i} against the oracle")
+            assert_lse_close(lse[:, s0 + i], lse_ref[0, :, 0], f"LSE of sequence {b} row {i} against the oracle")
+            checked += 1
+    assert checked >= 100
+
+
 def test_config3_full_size_split_count_does_not_change_the_result_and_oracle_on_shortest():
     bench = _bench()
     dev = torch.device("cuda:0")
@@ -77,7 +116,7 @@ def test_config3_full_size_split_count_does_not_change_the_result_and_oracle_on_
     assert_lse_close(lse, lse1, "LSE, default splits against one split")
     assert_o_close(o9, o1, "nine splits against one split, config 3")
     assert_lse_close(lse9, lse1, "LSE, nine splits against one split")
-    for b in _shortest(w["lens"], 3):
+    for b in _shortest(w["lens"], 3) + _longest(w["lens"], 6):  # (a decode row is cheap: the longest ones in full)
         k, v = _gather_pages(w, b)
         o_ref, lse_ref = oracle.fmha_fwd(w["q"][b:b + 1].cpu(), k[None], v[None])
         assert_o_close(o[b:b + 1], o_ref, f"sequence {b} against the oracle")
@@ -111,7 +150,7 @@ def test_config4_full_size_append_then_decode_both_instances_and_oracle_on_short
     assert_o_close(o, o_mma, "tcgen05 split modes against the mma.sync decode kernel, config 4")
     assert_lse_close(lse, lse_mma, "LSE, tcgen05 against mma.sync, config 4")
     cu = cu_n.cpu()
-    for b in _shortest(w["lens"], 3):
+    for b in _shortest(w["lens"], 3) + _longest(w["lens"], 4):  # (at most 16 query rows each: the longest ones in full)
         k, v = _gather_pages(w, b)
         sl = slice(int(cu[b]), int(cu[b + 1]))
         o_ref, lse_ref = oracle.fmha_fwd(q_rot[sl].cpu()[None], k[None], v[None], mask_type=2, window=(-1, 0))

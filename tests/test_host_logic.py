@@ -64,3 +64,27 @@ def test_python_api_rejects_bad_tensors_before_launch():
         ops.fmha_fwd("q", q, q)
     with pytest.raises(ValueError, match="rotary"):
         ops.fmha_fwd_append_kv(q, q, q, q, q, torch.zeros(1, dtype=torch.int32))
+
+
+def test_comparison_helpers_reject_nan_and_inf():
+    """The parity helpers must fail on NaN / Inf output (a NaN error compares False against any bound)."""
+    from helpers import assert_lse_close, assert_o_close
+    ref = torch.ones(4, 8)
+    assert_o_close(ref.clone(), ref)
+    for bad in (float("nan"), float("inf"), -float("inf")):
+        got = ref.clone()
+        got[1, 3] = bad
+        with pytest.raises(AssertionError):
+            assert_o_close(got, ref)
+    with pytest.raises(AssertionError):
+        assert_o_close(torch.full_like(ref, float("nan")), ref)
+    with pytest.raises(AssertionError):
+        assert_o_close(ref + 0.5, ref)
+    lse = torch.tensor([0.5, -float("inf"), 2.0])
+    assert_lse_close(lse.clone(), lse)
+    with pytest.raises(AssertionError):
+        assert_lse_close(torch.tensor([0.5, -float("inf"), float("nan")]), lse)
+    with pytest.raises(AssertionError):
+        assert_lse_close(torch.tensor([0.5, 1.0, 2.0]), lse)
+    with pytest.raises(AssertionError):
+        assert_lse_close(torch.tensor([0.5, -float("inf"), 2.002]), lse)
