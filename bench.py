@@ -19,6 +19,7 @@ All inputs are synthetic (seeded N(0,1)), as the reference's own profiler genera
 from __future__ import annotations
 
 import argparse
+import ctypes
 import json
 import os
 import subprocess
@@ -212,6 +213,46 @@ def make_long_decode(seed: int, device, world: int, batch=4, ctx=524288, page=64
     return w
 
 
+def sharded_decode_parity(fdist, ops, device, rank, world):
+    """A small sequence-sharded decode (4 contexts of up to 8192 tokens, page 64, 64 q / 8 kv heads) through the code path
+    the long-context leg times -- ShardedDecoder on every rank of the job, eager and replayed from a CUDA graph -- with
+    rank 0's result checked against the CPU oracle on the unsharded cache."""
+    from flashck_b200.utils.inputs import make_paged_cache, normal_tensor
+    lens, hq, hkv, page = [8192, 4097, 64, 8000], 64, 8, 64
+    cache = make_paged_cache(lens, hkv, D, D, page, torch.bfloat16, seed=55)  # the same cache on every rank
+    q = normal_tensor((len(lens), 1, hq, D), torch.bfloat16, 56)
+    table, local_len = fdist.shard_pages(lens, cache.block_table, page, rank, world)
+    qd, kd, vd = q.to(device), cache.k.to(device), cache.v.to(device)
+    dec = fdist.ShardedDecoder(qd.shape, D, torch.bfloat16, device, hkv=hkv)
+    out = {}
+    try:
+        o, lse = dec(qd, kd, vd, table.to(device), local_len.to(device))
+        res = {"eager": (o.float().cpu(), lse.cpu())}
+        dec.capture(qd, kd, vd, table.to(device), local_len.to(device))
+        o, lse = dec.replay()
+        torch.cuda.synchronize()
+        res["graph"] = (o.float().cpu(), lse.cpu())
+        from flashck_b200 import _lib
+        status = _lib.device_status()
+        if rank == 0:
+            from oracle import cpu as oracle  # the checker, on rank 0 only
+            o_ref, lse_ref = oracle.fmha_fwd(q, cache.k, cache.v, seqlen_k=cache.seqlen_k, block_table=cache.block_table)
+            o_ref = o_ref.float()
+            ok = status == 0
+            for name, (o, lse) in res.items():
+                eo = float(((o - o_ref).abs() - 2e-2 * o_ref.abs()).max())
+                el = float((lse - lse_ref).abs().max())
+                out[f"max_o_err_beyond_rel_{name}"] = eo
+                out[f"max_lse_err_{name}"] = el
+                ok = ok and eo <= 2e-2 and el <= 1e-3 and bool(torch.isfinite(o).all())
+            out["parity_ok"] = bool(ok)
+            out["device_status"] = status
+            out["checked"] = f"rank 0 of {world}: O within 2e-2 abs/rel, LSE within 1e-3 of the oracle on the unsharded cache"
+    finally:
+        dec.close()
+    return out
+
+
 def time_steps(fn, steps, warmup, barrier=None):
     """Device time of `steps` calls of fn, in ms (CUDA events on the current stream)."""
     for _ in range(warmup):
@@ -334,7 +375,7 @@ def main():
         run_reference(args, rank)
         return
 
-    from flashck_b200 import ops
+    from flashck_b200 import _lib, ops
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback for the product path)")
@@ -589,33 +630,64 @@ def main():
     # ------------------------------------------------------------------ sequence-sharded long-context decode (config 5)
     if not args.no_decode and not args.small:
         from flashck_b200 import dist as fdist
+        parity = sharded_decode_parity(fdist, ops, device, rank, world)  # small problem, same code path, against the oracle
         wl = make_long_decode(999 + rank, device, world)
-        S5 = ops.default_num_splits(len(wl["lens"]))
-        ws5 = ops.splitkv_workspace(wl["q"], D, S5)
         if dist is not None:  # q is replicated
             dist.broadcast(wl["q"], src=0)
+        dec = fdist.ShardedDecoder(wl["q"].shape, D, torch.bfloat16, device, hkv=wl["hkv"])
+        S5 = dec.num_splits
+        lsteps = max(steps, 20)
 
         def long_decode_step():
+            return dec(wl["q"], wl["k"], wl["v"], wl["table"], wl["seqlen"])
+
+        ms_eager = max_over_ranks(time_steps(long_decode_step, lsteps, warmup, barrier))
+        dec.capture(wl["q"], wl["k"], wl["v"], wl["table"], wl["seqlen"])
+        ms_l = max_over_ranks(time_steps(dec.replay, lsteps, warmup, barrier))
+        # stages, each timed alone over the same number of calls on every rank (the exchange kernel waits for its peers,
+        # so its figure includes the skew between the ranks)
+        def split_only():
+            ops.fmha_fwd_splitkv(wl["q"], wl["k"], wl["v"], seqlen_k=wl["seqlen"], block_table=wl["table"],
+                                 num_splits=S5, workspace=(dec.lse_acc, dec.o_acc), combine=False)
+
+        def exchange_only():
+            one = dec._one
+            _lib.check(_lib.lib().FmhaFwdSplitKVShardedCombine(
+                one(dec.lse_acc), one(dec.o_acc), one(dec.o), one(dec.lse), dec._bufs, dec.rank, 1, dec.world,
+                *dec.shape, S5, 4, ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)), "FmhaFwdSplitKVShardedCombine")
+
+        ms_split = max_over_ranks(time_steps(split_only, lsteps, warmup, barrier))
+        ms_exch = max_over_ranks(time_steps(exchange_only, lsteps, warmup, barrier))
+        # the same step through torch.distributed: merge kernel, NCCL all-gather, merge kernel (the library-call baseline)
+        ws5 = (dec.lse_acc, dec.o_acc)
+
+        def nccl_step():
             return fdist.sequence_sharded_decode(wl["q"], wl["k"], wl["v"], wl["table"], wl["seqlen"], num_splits=S5,
                                                  workspace=ws5, return_lse=True)
 
-        lsteps = max(steps, 20)
-        ms_l = max_over_ranks(time_steps(long_decode_step, lsteps, warmup, barrier))
+        ms_nccl = max_over_ranks(time_steps(nccl_step, lsteps, warmup, barrier))
         gbs_l = wl["total_bytes"] * lsteps / (ms_l * 1e-3) / 1e9
         extra["long_decode"] = {
             "metric": "sequence_sharded_decode_hbm_gbs", "value": gbs_l, "unit": "GB/s", "ms_per_step": ms_l / lsteps,
             "steps": lsteps, "scaling": "strong",
             "config": {"workload": "long-context decode (BASELINE config 5): batch 4, seqlen_q 1, 64/8 heads, hdim 128, "
-                                   "ctx 524288 per sequence, page 64, KV pages sharded contiguously over the GPUs; "
-                                   "local split-KV + fp32 merge, one all-gather of the partials, final merge",
+                                   "ctx 524288 per sequence, page 64, KV pages sharded contiguously over the GPUs; per "
+                                   "step the split-KV kernel, then one kernel that merges the local splits, stores the "
+                                   "partial into every rank's buffer over NVLink and merges the ranks; the two launches "
+                                   "replayed from a CUDA graph (ShardedDecoder.capture / replay)",
                        "total_kv_bytes": wl["total_bytes"], "num_splits": S5,
-                       "gather_bytes_per_rank": 4 * fdist.partial_numel(4, 1, 64, D), "parallelism": f"sp{world}"},
+                       "exchange_bytes_per_rank_pair": 4 * 64 * (D + 2) * 8, "parallelism": f"sp{world}"},
+            "stages_ms": {"split_kv_kernel": ms_split / lsteps, "merge_exchange_merge_kernel": ms_exch / lsteps,
+                          "step_eager_launches": ms_eager / lsteps, "step_cuda_graph": ms_l / lsteps,
+                          "step_nccl_all_gather_path": ms_nccl / lsteps},
+            "parity": parity,
             "roofline": {"bound": "hbm", "achieved": gbs_l / world, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                          "frac": gbs_l / world / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"],
-                         "note": "per GPU; split-KV, two merges and the all-gather timed together"},
-            "gpu_launches": 3 * lsteps,
+                         "note": "per GPU; split-KV kernel and the merge + exchange + merge kernel timed together"},
+            "gpu_launches": 2 * lsteps,
         }
-        del wl, ws5
+        dec.close()
+        del wl, ws5, dec
 
     if rank == 0 and not args.no_cpu_baseline:
         cb = cpu_prefill_sample(w)

@@ -32,6 +32,12 @@ SIGNATURES = {
     "FmhaFwdSplitKVCombine": ([_P] * 4 + [_I64] * 6 + [_P, _P, _I], _I),
     "FmhaSplitKVCombine": ([_P] * 4 + [_I64] * 6 + [_P, _P, _I], _I),
     "FmhaFwdSplitKVCombineStrided": ([_P] * 4 + [_I64] * 5 + [ctypes.POINTER(_I64), ctypes.POINTER(_I64), _I, _P], _I),
+    "FlashckShardExchangeBytes": ([_I64] * 4 + [_I], _I64),
+    "FmhaFwdSplitKVShardedCombine": ([_P] * 5 + [_I, _I, _I] + [_I64] * 5 + [_I, _P], _I),
+    "FlashckPeerBufferCreate": ([_I64, ctypes.POINTER(_P), _P], _I),
+    "FlashckPeerBufferOpen": ([_P, ctypes.POINTER(_P)], _I),
+    "FlashckPeerBufferClose": ([_P], _I),
+    "FlashckPeerBufferFree": ([_P], _I),
     "FmhaFwdSplitKVStatic": ([_P] * 10 + [_I64] * 11 + [_F, _I64, _I64, _U32, _P, _I], _I),
     "FmhaFwdAppendKV": ([_P] * 12 + [_I64] * 9 + [_I, _I64, _I64, _P, _I], _I),
     "FlashckSetInstanceParam": ([_I, ctypes.c_char_p, _I64], _I),

@@ -479,7 +479,7 @@ int FlashckSetInstanceParam(int family, const char* key, int64_t value) {
         return FLASHCK_OK;
     }
     if (family == 0) rc = fwd_set_param(key, value);
-    else if (family == 2) rc = !strcmp(key, "use_sm100_splitkv") ? fwd_set_param(key, value) : splitkv_set_param(key, value);
+    else if (family == 2) rc = (!strcmp(key, "use_sm100_splitkv") || !strcmp(key, "exp_mode_splitkv")) ? fwd_set_param(key, value) : splitkv_set_param(key, value);
     if (rc) set_last_error("FlashckSetInstanceParam: unknown family/key %d/%s", family, key);
     return rc;
 }
@@ -489,7 +489,7 @@ int FlashckGetInstanceParam(int family, const char* key, int64_t* value_out) {
     if (family == 0 && !strcmp(key, "bias_enum")) { *value_out = g_bias_enum; return FLASHCK_OK; }
     if (family == 0 && !strcmp(key, "bias_rank_info")) { *value_out = g_bias_rank_info; return FLASHCK_OK; }
     if (family == 0) rc = fwd_get_param(key, value_out);
-    else if (family == 2) rc = !strcmp(key, "use_sm100_splitkv") ? fwd_get_param(key, value_out) : splitkv_get_param(key, value_out);
+    else if (family == 2) rc = (!strcmp(key, "use_sm100_splitkv") || !strcmp(key, "exp_mode_splitkv")) ? fwd_get_param(key, value_out) : splitkv_get_param(key, value_out);
     if (rc) set_last_error("FlashckGetInstanceParam: unknown family/key %d/%s", family, key);
     return rc;
 }

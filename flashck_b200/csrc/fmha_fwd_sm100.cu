@@ -50,10 +50,20 @@ constexpr int KV_SLOTS = 2;
 constexpr int TILE_BYTES = BM * HD * 2;   // 32 KB: one Q, K or V tile
 constexpr int HALF_BYTES = TILE_BYTES / 2;  // one 64-column block (128 rows x 128 B)
 constexpr int NTHREADS = 384;
-constexpr float kRescaleThreshold = 8.f;  // log2 units
+constexpr float kRescaleThreshold = 8.f;  // log2 units; fp32 exponentials: P stays below 2^8
+// With the packed f16x2 exp2 the threshold also bounds the rounding of the arguments (f16 spacing grows with the
+// magnitude): 2 keeps an argument above the running max within 2^-11, at the price of a few more O rescales in the
+// first tiles of a row.  Instance parameter "rescale_log2_x100".
+std::atomic<int64_t> g_rescale_half_x100{200};
 
 std::atomic<int64_t> g_use_sm100{1};
-std::atomic<int64_t> g_poly8{0};  // 3: three of every 8 column pairs take the exp2 polynomial on the FMA pipe; 0: none
+// exponentials of the softmax (template parameter EXPM of the kernel): 0 fp32 on the exp2 unit, 1 packed f16x2 on the
+// exp2 unit, 11 / 12 / 13 fp32 with 1 / 2 / 3 of every 8 column pairs on an FMA-pipe polynomial
+// (measured on B200, BASELINE config 2, bf16: 0 -> 962 TFLOP/s; 1 -> 915 at a rescale threshold of 4 and up, 866 at 2,
+// with the LSE of a row that one late key dominates off by up to 9.7e-4; 11 / 12 / 13 -> 934 / 916 / 883: the unpacking
+// of the packed results and the polynomial both cost the softmax warps more issue slots than the exp2 unit gives back)
+std::atomic<int64_t> g_exp_mode{0};
+std::atomic<int64_t> g_exp_mode_splitkv{0};
 std::atomic<int64_t> g_use_sm100_splitkv{1};  // multi-token split-KV on the tcgen05 instance
 
 struct Sm100Dev {
@@ -83,6 +93,7 @@ struct Sm100Dev {
     int num_levels;   // row blocks of the longest sequence (128 rows when heads are paired, else 256)
     int pair_heads;   // the two Q tiles of a work item are two q heads of one kv group
     float scale_log2;
+    float rescale_thr;  // the running max is raised (and O rescaled) when the row max exceeds it by more than this (log2 units)
 };
 
 // ---- PTX wrappers ---------------------------------------------------------------------------------------------
@@ -196,6 +207,34 @@ __device__ __forceinline__ float2 exp2_poly2(float2 x) {
     r.x = __int_as_float(__float_as_int(pl.x) + (__float_as_int(t.x) << 23));
     r.y = __int_as_float(__float_as_int(pl.y) + (__float_as_int(t.y) << 23));
     return r;
+}
+
+// 2^x for two values with one instruction of the exp2 unit: the arguments are packed to f16x2 and the unit's packed
+// half-precision form returns both results, so a 128-column row costs 64 issues of that unit instead of 128 -- at
+// hdim 128 the exp2 unit is otherwise busy as long as the tensor pipe.  The arguments are <= the rescale threshold (the
+// running max lags the true max by at most that much; 2 with this form), far inside the f16 range; f16 carries 11 significant bits, so an argument
+// in [-2, 2] is off by at most 2^-11 (a factor of 1 +- 3.4e-4 in P) and the result is rounded to 11 bits -- P is rounded
+// to the 8 (bf16) or 11 (fp16) bits of the element type anyway, and the row sum averages the rounding over the keys.
+__device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
+    uint32_t r;
+    asm("cvt.rn.f16x2.f32 %0, %1, %2;\n" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+__device__ __forceinline__ uint32_t ex2_f16x2(uint32_t x) {
+    uint32_t y;
+    asm("ex2.approx.f16x2 %0, %1;\n" : "=r"(y) : "r"(x));
+    return y;
+}
+__device__ __forceinline__ float2 unpack_f16x2(uint32_t v) {
+    float2 r;
+    asm("{\n.reg .f16 l, h;\nmov.b32 {l, h}, %2;\ncvt.f32.f16 %0, l;\ncvt.f32.f16 %1, h;\n}\n" : "=f"(r.x), "=f"(r.y) : "r"(v));
+    return r;
+}
+// acc.x += low half, acc.y += high half, each as one mixed-precision add (f16 operand, fp32 sum)
+__device__ __forceinline__ void add_f16x2_to(float2& acc, uint32_t v) {
+    asm("{\n.reg .f16 l, h;\nmov.b32 {l, h}, %2;\nadd.f32.f16 %0, l, %0;\nadd.f32.f16 %1, h, %1;\n}\n"
+        : "+f"(acc.x), "+f"(acc.y)
+        : "r"(v));
 }
 
 constexpr int kMaxBatch = 256;    // sequences the on-chip schedule can hold (larger batches use the general instance)
@@ -385,13 +424,18 @@ __device__ __forceinline__ void get_item(const Ctrl* ctrl, const Sm100Dev& p, in
 //          0-63 takes keys 0-63 of every 128-key tile, the copy in rows 64-127 takes keys 64-127, each as a split of its
 //          own (2 * piece, 2 * piece + 1).  Every softmax thread then handles 64 columns instead of 128 with half of the
 //          threads idle, which halves the softmax part of the per-tile chain.
-template <typename T, int NPOLY8, bool WINDOW, int SPLIT>
+// EXPM: how the softmax takes its exponentials.  0: one fp32 exp2 per element on the exp2 unit; 1: two per issue
+//       through the unit's packed f16x2 form (see pack_f16x2); 11, 12, 13: fp32, with 1, 2 or 3 of every 8 column pairs
+//       on a polynomial on the FMA pipe instead.
+template <typename T, int EXPM, bool WINDOW, int SPLIT>
 __global__ void __launch_bounds__(NTHREADS, 1)
 fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                       const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_o,
                       const Sm100Dev p) {
     extern __shared__ uint8_t smem_raw[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    constexpr int NPOLY8 = EXPM >= 11 ? EXPM - 10 : 0;
+    constexpr bool HEXP = EXPM == 1;
 
     // ---- shared memory carve-up ----
     const uint32_t raw = smem_u32(smem_raw);
@@ -1000,8 +1044,8 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                     mx = fmaxf(max3(a0, a1, a2), a3);
                 }
                 mx *= p.scale_log2;  // scale > 0: max commutes with scaling
-                // raise the running max only on a jump of more than 2^8; rescale O in TMEM when that happens
-                const bool grow = mx > m_used + kRescaleThreshold;
+                // raise the running max only on a jump of more than 2^8 (2^2 with the packed exp2); rescale O in TMEM then
+                const bool grow = mx > m_used + p.rescale_thr;
                 if (n > 0 && __any_sync(0xffffffffu, grow)) {
                     if (SPLIT) {
                         // O must be at rest: the PV of step n-1 may still be running, S of this step was computed ahead
@@ -1039,6 +1083,18 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                     for (int j = 0; j < 32; ++j) {
                         const int e = c * 64 + 2 * j;
                         const float2 x = __ffma2_rn(make_float2(__uint_as_float(sreg[e]), __uint_as_float(sreg[e + 1])), sc2, nm2);
+                        if constexpr (HEXP) {
+                            const uint32_t ph = ex2_f16x2(pack_f16x2(x.x, x.y));
+                            if constexpr (std::is_same<T, __half>::value) {  // P is the unit's result as it stands
+                                if (j & 1) add_f16x2_to(psb, ph); else add_f16x2_to(psa, ph);
+                                pk[j] = ph;
+                            } else {
+                                const float2 pr = unpack_f16x2(ph);
+                                if (j & 1) psb = __fadd2_rn(psb, pr); else psa = __fadd2_rn(psa, pr);
+                                pk[j] = Elem<T>::pack2(pr.x, pr.y);
+                            }
+                            continue;
+                        }
                         float2 pr;
                         if (NP > 0 && ((j * NP) & 7) < NP) pr = exp2_poly2(x);
                         else { pr.x = ex2_fast(x.x); pr.y = ex2_fast(x.y); }
@@ -1212,7 +1268,7 @@ int make_map_o(CUtensorMap* map, const void* base, int dtype, int64_t rows, int6
     return FLASHCK_OK;
 }
 
-template <typename T, int NPOLY8, bool WINDOW, int SPLIT>
+template <typename T, int EXPM, bool WINDOW, int SPLIT>
 int launch_t(const FwdParams& p, const Sm100Dev& dev, cudaStream_t stream) {
     const int64_t rows_q = p.seqstart_q ? p.total_q : p.batch * p.seqlen_q;
     const bool paged = p.block_table || p.kv_indptr;
@@ -1227,7 +1283,7 @@ int launch_t(const FwdParams& p, const Sm100Dev& dev, cudaStream_t stream) {
     if ((rc = make_map_3d(&mk, p.k, p.dtype, rows_k, p.hkv, box_k))) return rc;
     if ((rc = make_map_3d(&mv, p.v, p.dtype, rows_k, p.hkv, box_k))) return rc;
     if ((rc = make_map_o(&mo, p.o, p.dtype, rows_q, p.hq))) return rc;
-    auto kern = fmha_fwd_sm100_kernel<T, NPOLY8, WINDOW, SPLIT>;
+    auto kern = fmha_fwd_sm100_kernel<T, EXPM, WINDOW, SPLIT>;
     const size_t smem = 1024 + (size_t)(2 + 2 * KV_SLOTS) * TILE_BYTES + 8 * STAGE_BYTES + sizeof(Ctrl);
     static thread_local int configured_device = -1;
     int devid = 0;
@@ -1298,13 +1354,22 @@ int launch_fwd_sm100(const FwdParams& p, cudaStream_t stream) {
     dev.scale_log2 = p.scale * 1.4426950408889634f;
     const bool bf16 = p.dtype == FLASHCK_DTYPE_BFLOAT16;
     const bool window = p.mask_type != 0 && !(p.wl < 0 && p.wr == 0);
-    const bool poly = g_poly8.load() != 0;
-    if (window) {
-        if (poly) return bf16 ? launch_t<__nv_bfloat16, 3, true, 0>(p, dev, stream) : launch_t<__half, 3, true, 0>(p, dev, stream);
-        return bf16 ? launch_t<__nv_bfloat16, 0, true, 0>(p, dev, stream) : launch_t<__half, 0, true, 0>(p, dev, stream);
+    const int expm = (int)g_exp_mode.load();
+    dev.rescale_thr = expm == 1 ? 0.01f * (float)g_rescale_half_x100.load() : kRescaleThreshold;
+#define FCK_SM100_LAUNCH(E, W) \
+    return bf16 ? launch_t<__nv_bfloat16, E, W, 0>(p, dev, stream) : launch_t<__half, E, W, 0>(p, dev, stream)
+    if (window) {  // (the window instances come with the two exp2-unit forms only)
+        if (expm == 1) { FCK_SM100_LAUNCH(1, true); }
+        FCK_SM100_LAUNCH(0, true);
     }
-    if (poly) return bf16 ? launch_t<__nv_bfloat16, 3, false, 0>(p, dev, stream) : launch_t<__half, 3, false, 0>(p, dev, stream);
-    return bf16 ? launch_t<__nv_bfloat16, 0, false, 0>(p, dev, stream) : launch_t<__half, 0, false, 0>(p, dev, stream);
+    switch (expm) {
+        case 1: FCK_SM100_LAUNCH(1, false);
+        case 11: FCK_SM100_LAUNCH(11, false);
+        case 12: FCK_SM100_LAUNCH(12, false);
+        case 13: FCK_SM100_LAUNCH(13, false);
+        default: FCK_SM100_LAUNCH(0, false);
+    }
+#undef FCK_SM100_LAUNCH
 }
 
 // ---- split-KV with several query rows per kv head (append + decode, speculative decoding, chunked prefill) ----
@@ -1337,7 +1402,7 @@ bool split_duplicates_rows(const SplitKVParams& p) {
     return p.max_seqlen_q * (p.hq / p.hkv) <= 64 && p.num_splits >= 2;
 }
 
-template <typename T, int SPLIT>
+template <typename T, int SPLIT, int EXPM>
 int launch_split_t(const SplitKVParams& p, const Sm100Dev& dev, cudaStream_t stream) {
     const int64_t tokens = p.seqstart_q ? p.total_q : p.batch * p.seqlen_q;
     const int box_k = p.block_table ? (int)std::min<int64_t>(p.page, BN) : BN;
@@ -1351,7 +1416,7 @@ int launch_split_t(const SplitKVParams& p, const Sm100Dev& dev, cudaStream_t str
     const int64_t cache_rows = p.block_table ? std::max<int64_t>(p.num_pages, 1) * p.page : p.batch * p.seqlen_k_cap;
     if ((rc = make_map_3d(&mk, p.k, p.dtype, cache_rows, p.hkv, box_k))) return rc;
     if ((rc = make_map_3d(&mv, p.v, p.dtype, cache_rows, p.hkv, box_k))) return rc;
-    auto kern = fmha_fwd_sm100_kernel<T, 0, false, SPLIT>;
+    auto kern = fmha_fwd_sm100_kernel<T, EXPM, false, SPLIT>;
     const size_t smem = 1024 + (size_t)(2 + 2 * KV_SLOTS) * TILE_BYTES + 8 * STAGE_BYTES + sizeof(Ctrl);
     static thread_local int configured_device = -1;
     int devid = 0;
@@ -1424,17 +1489,39 @@ int launch_splitkv_sm100(const SplitKVParams& p, cudaStream_t stream) {
     dev.pair_heads = 0; dev.num_levels = 1;
     dev.scale_log2 = p.scale * 1.4426950408889634f;
     const bool bf16 = p.dtype == FLASHCK_DTYPE_BFLOAT16;
-    if (split_duplicates_rows(p))
-        return bf16 ? launch_split_t<__nv_bfloat16, 2>(p, dev, stream) : launch_split_t<__half, 2>(p, dev, stream);
-    return bf16 ? launch_split_t<__nv_bfloat16, 1>(p, dev, stream) : launch_split_t<__half, 1>(p, dev, stream);
+    const bool hexp = g_exp_mode_splitkv.load() == 1;
+    dev.rescale_thr = hexp ? 0.01f * (float)g_rescale_half_x100.load() : kRescaleThreshold;
+    if (split_duplicates_rows(p)) {
+        if (hexp) return bf16 ? launch_split_t<__nv_bfloat16, 2, 1>(p, dev, stream) : launch_split_t<__half, 2, 1>(p, dev, stream);
+        return bf16 ? launch_split_t<__nv_bfloat16, 2, 0>(p, dev, stream) : launch_split_t<__half, 2, 0>(p, dev, stream);
+    }
+    if (hexp) return bf16 ? launch_split_t<__nv_bfloat16, 1, 1>(p, dev, stream) : launch_split_t<__half, 1, 1>(p, dev, stream);
+    return bf16 ? launch_split_t<__nv_bfloat16, 1, 0>(p, dev, stream) : launch_split_t<__half, 1, 0>(p, dev, stream);
 }
+
+static bool valid_exp_mode(int64_t v) { return v == 0 || v == 1 || (v >= 11 && v <= 13); }
 
 int fwd_set_param(const char* key, int64_t value) {
     if (!strcmp(key, "use_sm100")) { g_use_sm100 = value; return FLASHCK_OK; }
     if (!strcmp(key, "use_sm100_splitkv")) { g_use_sm100_splitkv = value; return FLASHCK_OK; }
-    if (!strcmp(key, "poly8")) {
-        if (value != 0 && value != 3) return FLASHCK_ERR_INVALID_ARGUMENT;  // 3 of every 8 column pairs, or none
-        g_poly8 = value;
+    if (!strcmp(key, "exp_mode")) {
+        if (!valid_exp_mode(value)) return FLASHCK_ERR_INVALID_ARGUMENT;
+        g_exp_mode = value;
+        return FLASHCK_OK;
+    }
+    if (!strcmp(key, "exp_mode_splitkv")) {
+        if (value != 0 && value != 1) return FLASHCK_ERR_INVALID_ARGUMENT;
+        g_exp_mode_splitkv = value;
+        return FLASHCK_OK;
+    }
+    if (!strcmp(key, "rescale_log2_x100")) {
+        if (value < 0 || value > 1400) return FLASHCK_ERR_INVALID_ARGUMENT;  // f16 holds 2^15; P < 2^14 leaves headroom
+        g_rescale_half_x100 = value;
+        return FLASHCK_OK;
+    }
+    if (!strcmp(key, "poly8")) {  // older spelling: the polynomial share alone (0 = exp2 unit in fp32)
+        if (value < 0 || value > 3) return FLASHCK_ERR_INVALID_ARGUMENT;
+        g_exp_mode = value ? 10 + value : 0;
         return FLASHCK_OK;
     }
     return FLASHCK_ERR_INVALID_ARGUMENT;
@@ -1442,7 +1529,10 @@ int fwd_set_param(const char* key, int64_t value) {
 int fwd_get_param(const char* key, int64_t* value) {
     if (!strcmp(key, "use_sm100")) { *value = g_use_sm100; return FLASHCK_OK; }
     if (!strcmp(key, "use_sm100_splitkv")) { *value = g_use_sm100_splitkv; return FLASHCK_OK; }
-    if (!strcmp(key, "poly8")) { *value = g_poly8; return FLASHCK_OK; }
+    if (!strcmp(key, "exp_mode")) { *value = g_exp_mode; return FLASHCK_OK; }
+    if (!strcmp(key, "exp_mode_splitkv")) { *value = g_exp_mode_splitkv; return FLASHCK_OK; }
+    if (!strcmp(key, "rescale_log2_x100")) { *value = g_rescale_half_x100; return FLASHCK_OK; }
+    if (!strcmp(key, "poly8")) { const int64_t m = g_exp_mode; *value = m >= 11 ? m - 10 : 0; return FLASHCK_OK; }
     return FLASHCK_ERR_INVALID_ARGUMENT;
 }
 

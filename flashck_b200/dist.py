@@ -11,11 +11,16 @@ design on top of the same operators:
   LSE-weighted merge with ``num_splits = world size`` yields O on every rank
   (:func:`sequence_sharded_decode`).  A rank whose shard is empty contributes ``LSE = -inf``.
 
-The all-gather goes through ``torch.distributed`` (NCCL over NVLink on GPUs, gloo in the CPU tests); nothing here
-issues TMA multicast or peer loads.
+Two exchanges exist.  :func:`sequence_sharded_decode` uses ``torch.distributed`` (NCCL over NVLink on GPUs, gloo in
+the CPU tests): local merge kernel, ``all_gather_into_tensor``, final merge kernel.  :class:`ShardedDecoder` -- the fast
+path -- replaces those three steps by one kernel of this library (``FmhaFwdSplitKVShardedCombine``) that merges the
+local splits, stores the partial into every rank's exchange buffer through CUDA-IPC mapped peer pointers (plain
+stores, a flag in every 8 bytes) and merges the ranks; its buffers are preallocated, nothing is allocated per step,
+and the two launches of a step can be captured in a CUDA graph.  Nothing here issues TMA multicast.
 """
 from __future__ import annotations
 
+import ctypes
 from typing import Callable, List, Optional, Sequence, Tuple
 
 import torch
@@ -29,6 +34,7 @@ __all__ = [
     "gathered_strides",
     "gathered_to_workspaces",
     "sequence_sharded_decode",
+    "ShardedDecoder",
 ]
 
 
@@ -147,3 +153,129 @@ def sequence_sharded_decode(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch
     return F.fmha_fwd_splitkv_combine_strided(gathered, b, sq, hq, dv, world, lse_offset=b * sq * hq * dv,
                                               lse_strides=lse_strides, o_strides=o_strides, dtype=q.dtype,
                                               return_lse=return_lse)
+
+
+# ------------------------------------------------------------------------------------------------
+# the fused exchange: one kernel for local merge + peer stores + final merge
+# ------------------------------------------------------------------------------------------------
+class ShardedDecoder:
+    """Decode over a KV cache sharded by pages across the ranks of ``group``, two kernel launches per step: the
+    split-KV kernel on this rank's pages, then ``FmhaFwdSplitKVShardedCombine``.
+
+    Construction is collective (every rank of the group must do it, with the same shapes): it allocates this rank's
+    exchange buffer with ``FlashckPeerBufferCreate``, all-gathers the 64-byte CUDA-IPC handles through
+    ``torch.distributed`` and maps the peers' buffers.  With one rank (or no process group) the buffer is local and no
+    handle is exchanged.  ``__call__`` allocates nothing: the split workspaces and the outputs are created once here.
+
+        dec = ShardedDecoder(q.shape, dv, q.dtype, q.device, group=group)
+        o, lse = dec(q, k_pool, v_pool, local_block_table, local_seqlen_k)     # o, lse are the decoder's own buffers
+        dec.capture(q, k_pool, v_pool, local_block_table, local_seqlen_k)       # optional: the step as a CUDA graph
+        o, lse = dec.replay()                                                   # after updating the inputs in place
+
+    Every rank must make the same sequence of calls (a step waits, with a bound of about a second, for the partials of
+    all ranks).  Call :meth:`close` on every rank when done."""
+
+    def __init__(self, q_shape: Sequence[int], dv: int, dtype: torch.dtype, device, *, group=None, num_splits: int = 0,
+                 hkv: int = 0):
+        import torch.distributed as dist
+        from . import _lib
+        from .ops import fmha as F
+        self._lib, self._F = _lib, F
+        self.device = torch.device(device)
+        b, sq, hq, _ = [int(x) for x in q_shape]
+        self.shape = (b, sq, hq, int(dv))
+        self.dtype = dtype
+        self.group = group
+        self.distributed = dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1
+        self.world = dist.get_world_size(group) if self.distributed else 1
+        self.rank = dist.get_rank(group) if self.distributed else 0
+        if self.world > 8:
+            raise ValueError("ShardedDecoder serves the GPUs of one node (at most 8 ranks)")
+        self.num_splits = int(num_splits) if num_splits and num_splits > 0 else \
+            F.default_num_splits(b, rows_per_kv_head=sq * (hq // hkv) if hkv else 1)
+        self.lse_acc = torch.empty((b, hq, self.num_splits, sq), dtype=torch.float32, device=self.device)
+        self.o_acc = torch.empty((b, hq, self.num_splits, sq, dv), dtype=torch.float32, device=self.device)
+        self.o = torch.empty((b, sq, hq, dv), dtype=dtype, device=self.device)
+        self.lse = torch.empty((b, hq, sq), dtype=torch.float32, device=self.device)
+        self._out_code = {torch.float16: 3, torch.bfloat16: 4, torch.float32: 7}[dtype]
+        self._graph = None
+        self._own = None
+        self._opened: List[int] = []
+        lib = _lib.lib()
+        nbytes = lib.FlashckShardExchangeBytes(b, sq, hq, dv, self.world)
+        with torch.cuda.device(self.device):
+            if self.world == 1:
+                self._local = torch.zeros(nbytes, dtype=torch.uint8, device=self.device)
+                ptrs = [self._local.data_ptr()]
+            else:
+                own = ctypes.c_void_p(0)
+                handle = ctypes.create_string_buffer(64)
+                _lib.check(lib.FlashckPeerBufferCreate(nbytes, ctypes.byref(own), handle), "FlashckPeerBufferCreate")
+                self._own = own.value
+                handles: List[Optional[bytes]] = [None] * self.world
+                dist.all_gather_object(handles, handle.raw, group=group)
+                ptrs = []
+                for r, h in enumerate(handles):
+                    if r == self.rank:
+                        ptrs.append(self._own)
+                        continue
+                    p = ctypes.c_void_p(0)
+                    _lib.check(lib.FlashckPeerBufferOpen(ctypes.create_string_buffer(h, 64), ctypes.byref(p)),
+                               f"FlashckPeerBufferOpen(rank {r})")
+                    self._opened.append(p.value)
+                    ptrs.append(p.value)
+                dist.barrier(group=group)  # every rank has mapped every buffer before the first step
+        self._bufs = (ctypes.c_void_p * self.world)(*ptrs)
+        self._one = lambda t: (ctypes.c_void_p * 1)(t.data_ptr())
+
+    # -- one step: split-KV on the local pages, then merge + exchange + merge
+    def __call__(self, q, k_pool, v_pool, local_block_table, local_seqlen_k, *, scale: Optional[float] = None):
+        b, sq, hq, dv = self.shape
+        if tuple(q.shape[:3]) != (b, sq, hq):
+            raise ValueError(f"q must be [{b}, {sq}, {hq}, d], got {tuple(q.shape)}")
+        self._F.fmha_fwd_splitkv(q, k_pool, v_pool, seqlen_k=local_seqlen_k, block_table=local_block_table,
+                                 num_splits=self.num_splits, scale=scale, workspace=(self.lse_acc, self.o_acc),
+                                 combine=False)
+        with torch.cuda.device(self.device):
+            rc = self._lib.lib().FmhaFwdSplitKVShardedCombine(
+                self._one(self.lse_acc), self._one(self.o_acc), self._one(self.o), self._one(self.lse), self._bufs,
+                self.rank, 1, self.world, b, sq, hq, dv, self.num_splits, self._out_code,
+                ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+        self._lib.check(rc, "FmhaFwdSplitKVShardedCombine")
+        return self.o, self.lse
+
+    def capture(self, q, k_pool, v_pool, local_block_table, local_seqlen_k, *, scale: Optional[float] = None):
+        """Captures the step on these tensors as a CUDA graph (after one ordinary step, so that one-time set-up of the
+        kernels is done outside the capture).  Update the tensors in place, then :meth:`replay`."""
+        self(q, k_pool, v_pool, local_block_table, local_seqlen_k, scale=scale)
+        torch.cuda.synchronize(self.device)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            self(q, k_pool, v_pool, local_block_table, local_seqlen_k, scale=scale)
+        self._graph = graph
+        return self
+
+    def replay(self):
+        if self._graph is None:
+            raise RuntimeError("capture() first")
+        self._graph.replay()
+        return self.o, self.lse
+
+    def close(self) -> None:
+        """Unmaps the peers' buffers and frees this rank's (collective: a buffer is freed after every rank unmapped it)."""
+        if self._bufs is None:
+            return
+        torch.cuda.synchronize(self.device)
+        self._graph = None
+        lib = self._lib.lib()
+        with torch.cuda.device(self.device):
+            for p in self._opened:
+                lib.FlashckPeerBufferClose(ctypes.c_void_p(p))
+            self._opened = []
+            if self.distributed:
+                import torch.distributed as dist
+                dist.barrier(group=self.group)
+            if self._own is not None:
+                lib.FlashckPeerBufferFree(ctypes.c_void_p(self._own))
+                self._own = None
+        self._bufs = None

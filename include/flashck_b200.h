@@ -218,6 +218,36 @@ FLASHCK_API int FmhaFwdSplitKVCombineStrided(void* lse_acc_buf_ptr, void* o_acc_
                                              const int64_t* o_acc_strides, int out_dtype, void* stream);
 
 /*
+ * FmhaFwdSplitKVShardedCombine -- for a KV sequence sharded over the GPUs of one node: the merge of this rank's splits,
+ * the exchange of the per-rank fp32 partials (O_r, LSE_r) over NVLink and the merge over the ranks, in one kernel.
+ * The reference is single-GPU and has no counterpart; the arithmetic is its combine's
+ * (fmha_fwd_split_kv_combine_jinja.h:125-140) applied twice.  Every rank of the group calls it once per decode step,
+ * after its FmhaFwdSplitKV, with
+ *   lse_acc / o_acc      this rank's split workspaces in the reference layout ([b,hq,S,rows], [b,hq,S,rows,dv] fp32),
+ *   o / lse              the results ([b,rows,hq,dv] in out_dtype, fp32 [b,hq,rows] or NULL), identical on every rank,
+ *   exchange_bufs        `world` device pointers: the exchange buffer of every rank as mapped into this process (its
+ *                        own from FlashckPeerBufferCreate, the others from FlashckPeerBufferOpen), each of
+ *                        FlashckShardExchangeBytes(...) bytes, zeroed once before the first call and used for this
+ *                        purpose only (same sizes on every call).
+ * The pointer arguments are host arrays indexed by LOCAL rank: a process that owns one GPU passes local_ranks = 1 and
+ * first_rank = its rank.  local_ranks > 1 plays several ranks of the group in one (cooperative) launch on one GPU, all
+ * buffers local -- the form the single-GPU tests use.  Partials travel as plain stores to peer memory with a flag in
+ * every 8 bytes; the waits for them are bounded (about a second), after which the row is left unwritten and
+ * FlashckDeviceStatus reports FLASHCK_ERR_DEVICE_TIMEOUT.  Every rank must make the same sequence of calls.
+ */
+FLASHCK_API int64_t FlashckShardExchangeBytes(int64_t batch, int64_t rows, int64_t q_num_heads, int64_t v_head_dim, int world);
+FLASHCK_API int FmhaFwdSplitKVShardedCombine(void* const* lse_acc_ptrs, void* const* o_acc_ptrs, void* const* o_ptrs,
+                                 void* const* lse_ptrs, void* const* exchange_bufs, int first_rank, int local_ranks,
+                                 int world, int64_t batch, int64_t rows, int64_t q_num_heads, int64_t v_head_dim,
+                                 int64_t num_splits, int out_dtype, void* stream);
+/* Exchange buffers.  Create: cudaMalloc + zero fill + a 64-byte handle another process of the node can open (CUDA IPC).
+ * These four are set-up calls (they allocate, map and synchronise); nothing on the per-step path does. */
+FLASHCK_API int FlashckPeerBufferCreate(int64_t bytes, void** ptr_out, void* handle_out64);
+FLASHCK_API int FlashckPeerBufferOpen(const void* handle64, void** ptr_out);
+FLASHCK_API int FlashckPeerBufferClose(void* ptr);
+FLASHCK_API int FlashckPeerBufferFree(void* ptr);
+
+/*
  * FmhaFwdAppendKV -- rotary embedding of Q and the new keys, and the K/V cache write.
  * The reference names the kind (core/profiling/attention/fmha_library.h:19,41), the rotary modes
  * (fmha_library.h:195-219: 0 none, 1 interleaved, 2 half-rotated) and the table generator

@@ -115,6 +115,65 @@ def test_fmha_fwd_instances_agree():
     assert_lse_close(outs[0][1], outs[1][1])
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("exp_mode", [0, 1, 11, 12, 13])
+def test_fmha_fwd_exp_modes_match_the_oracle(dtype, exp_mode):
+    """Every way the tcgen05 softmax takes its exponentials (instance parameter exp_mode: fp32 on the exp2 unit, packed
+    f16x2 on the exp2 unit, fp32 with a share on the FMA-pipe polynomial) against the oracle, causal and unmasked."""
+    lens = [900, 130, 1, 385]
+    cu = to_seqstarts(lens)
+    q = normal_tensor((sum(lens), 8, 128), dtype, 15)
+    k = normal_tensor((sum(lens), 2, 128), dtype, 16)
+    v = normal_tensor((sum(lens), 2, 128), dtype, 17)
+    old = _lib.get_instance_param(0, "exp_mode")
+    _lib.set_instance_param(0, "exp_mode", exp_mode)
+    try:
+        for mt, window in ((1, (-1, 0)), (0, (-1, -1)), (2, (200, 0))):
+            o_ref, lse_ref = oracle.fmha_fwd(q, k, v, seqstart_q=cu, seqstart_k=cu, mask_type=mt, window=window)
+            o, lse = ops.fmha_fwd_var_len(_cu(q), _cu(k), _cu(v), _cu(cu), _cu(cu), max(lens), mask_type=mt,
+                                          window_size=window, return_lse=True)
+            assert_o_close(o, o_ref, f"O, exp_mode {exp_mode}, mask {mt}")
+            assert_lse_close(lse, lse_ref, f"LSE, exp_mode {exp_mode}, mask {mt}")
+    finally:
+        _lib.set_instance_param(0, "exp_mode", old)
+    assert _lib.get_instance_param(0, "exp_mode") == old
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_fmha_fwd_packed_exp2_lse_with_one_dominant_late_key(dtype):
+    """The hard case for the packed f16x2 exponentials: a row whose sum is one key, and that key arrives in a later key
+    tile with a score a little above the running max, so that its exponential is taken at a positive argument (where f16
+    is coarser) and nothing averages its rounding.  Queries and keys lie along one direction u: the ordinary keys score
+    far below two others, key 5 (the running max after the first tile) and key 401, which beats it by 0.14 to 1.9 in log2
+    units depending on the row -- so l = 1 + 2^delta, the share of the late key is up to 0.79, and its rounding shows in
+    the LSE undiluted."""
+    d, L, first, star = 128, 640, 5, 401  # the dominant key sits in the fourth 128-key tile
+    g = torch.Generator().manual_seed(7)
+    u = torch.zeros(d)
+    u[:16] = 0.25  # |u| = 1
+    a = torch.linspace(0.5, 6.5, L)                        # row r: q = a_r * sqrt(d) * u, so that q.k * scale = a_r * (k.u)
+    q = (a[:, None] * d ** 0.5 * u[None, :]).to(dtype)
+    ku = torch.full((L,), -40.0)                            # ordinary keys: weight e^(-33 a) against the two below
+    ku[first] = -7.0                                        # the running max after the first tile
+    ku[star] = -6.8                                         # 0.2 a_r above it: 0.14 .. 1.9 in log2 units over the rows
+    k = (ku[:, None] * u[None, :]).to(dtype)
+    v = torch.randn(L, d, generator=g).to(dtype)
+    q, k, v = q[None, :, None, :].contiguous(), k[None, :, None, :].contiguous(), v[None, :, None, :].contiguous()
+    o_ref, lse_ref = oracle.fmha_fwd(q, k, v)
+    worst = {}
+    for exp_mode in (0, 1):
+        old = _lib.get_instance_param(0, "exp_mode")
+        _lib.set_instance_param(0, "exp_mode", exp_mode)
+        try:
+            o, lse = ops.fmha_fwd(_cu(q), _cu(k), _cu(v), return_lse=True)
+        finally:
+            _lib.set_instance_param(0, "exp_mode", old)
+        assert_o_close(o, o_ref, f"O, exp_mode {exp_mode}")
+        assert_lse_close(lse, lse_ref, f"LSE, exp_mode {exp_mode}")
+        worst[exp_mode] = float((lse.cpu() - lse_ref).abs().max())
+    print("max LSE error: fp32 exp2 %.3g, packed f16x2 exp2 %.3g" % (worst[0], worst[1]))
+
+
 def test_fmha_fwd_var_len_gqa():
     dtype = torch.bfloat16
     lens = [1, 64, 65, 200, 0, 333]
@@ -637,6 +696,81 @@ def test_sequence_sharded_decode_ranks_emulated_on_one_gpu(world):
     o, lse = fdist.sequence_sharded_decode(qd, kd, vd, _cu(table), _cu(local), gather=replay, return_lse=True)
     assert_o_close(o, o_ref)
     assert_lse_close(lse, lse_ref)
+
+
+@pytest.mark.parametrize("world", [1, 2, 4, 8])
+def test_sharded_combine_kernel_ranks_played_in_one_cooperative_launch(world):
+    """FmhaFwdSplitKVShardedCombine (merge of the local splits + exchange of the partials + merge over the ranks in one
+    kernel) with all ranks of the group played on this GPU in one cooperative launch, every exchange buffer local.
+    Each rank's split partials come from the split-KV kernel on that rank's page shard; every rank's result must be the
+    oracle's attention over the whole cache.  Three calls in a row on the same buffers: the second uses the other half
+    of the buffers, the third finds the first call's flags in its half."""
+    import ctypes
+    from flashck_b200 import dist as fdist
+    dtype = torch.bfloat16
+    hq, hkv, d, page, S = 16, 2, 128, 64, 5
+    lens = [8192 + 17, 130, 0, 64 * 9]
+    b = len(lens)
+    cache = make_paged_cache(lens, hkv, d, d, page, dtype, seed=61)
+    k, v = _cu(cache.k), _cu(cache.v)
+    shards = [fdist.shard_pages(lens, cache.block_table, page, r, world) for r in range(world)]
+    lib = _lib.lib()
+    nbytes = lib.FlashckShardExchangeBytes(b, 1, hq, d, world)
+    bufs = [torch.zeros(nbytes, dtype=torch.uint8, device=DEV) for _ in range(world)]
+    outs = [torch.empty(b, 1, hq, d, dtype=dtype, device=DEV) for _ in range(world)]
+    lses = [torch.empty(b, hq, 1, dtype=torch.float32, device=DEV) for _ in range(world)]
+    arr = lambda ts: (ctypes.c_void_p * len(ts))(*[t.data_ptr() for t in ts])
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    for call in range(3):
+        q = normal_tensor((b, 1, hq, d), dtype, 62 + call)
+        o_ref, lse_ref = oracle.fmha_fwd(q, cache.k, cache.v, seqlen_k=cache.seqlen_k, block_table=cache.block_table)
+        qd = _cu(q)
+        parts = [ops.fmha_fwd_splitkv(qd, k, v, seqlen_k=_cu(sl), block_table=_cu(bt), num_splits=S, combine=False)
+                 for bt, sl in shards]
+        for o_, l_ in zip(outs, lses):
+            o_.fill_(float("nan"))
+            l_.fill_(float("nan"))
+        _lib.check(lib.FmhaFwdSplitKVShardedCombine(arr([p[0] for p in parts]), arr([p[1] for p in parts]), arr(outs),
+                                                    arr(lses), arr(bufs), 0, world, world, b, 1, hq, d, S, _lib.BFLOAT16,
+                                                    stream), "FmhaFwdSplitKVShardedCombine")
+        assert _lib.device_status() == 0
+        for r in range(world):
+            assert_o_close(outs[r], o_ref, f"call {call}, rank {r} of {world}")
+            assert_lse_close(lses[r], lse_ref, f"LSE, call {call}, rank {r} of {world}")
+        header = bufs[0][:8].view(torch.int32).tolist()
+        assert header == [call + 1, 0]  # calls completed, CTAs still running
+
+
+def test_sharded_decoder_single_rank_matches_the_oracle_with_and_without_a_graph():
+    """ShardedDecoder with one rank (no process group): two launches per step, nothing allocated per step, and the same
+    step replayed from a CUDA graph after the inputs were updated in place."""
+    from flashck_b200 import dist as fdist
+    dtype = torch.bfloat16
+    hq, hkv, d, page = 64, 8, 128, 64
+    lens = [4096 + 5, 640]
+    b = len(lens)
+    cache = make_paged_cache(lens, hkv, d, d, page, dtype, seed=71)
+    k, v, bt, sl = _cu(cache.k), _cu(cache.v), _cu(cache.block_table), _cu(cache.seqlen_k)
+    q = normal_tensor((b, 1, hq, d), dtype, 72)
+    qd = _cu(q)
+    dec = fdist.ShardedDecoder(qd.shape, d, dtype, DEV)
+    try:
+        o_ref, lse_ref = oracle.fmha_fwd(q, cache.k, cache.v, seqlen_k=cache.seqlen_k, block_table=cache.block_table)
+        o, lse = dec(qd, k, v, bt, sl)
+        assert_o_close(o, o_ref)
+        assert_lse_close(lse, lse_ref)
+        dec.capture(qd, k, v, bt, sl)
+        q2 = normal_tensor((b, 1, hq, d), dtype, 73)
+        qd.copy_(_cu(q2))
+        o_ref, lse_ref = oracle.fmha_fwd(q2, cache.k, cache.v, seqlen_k=cache.seqlen_k, block_table=cache.block_table)
+        for _ in range(3):
+            o, lse = dec.replay()
+        torch.cuda.synchronize()
+        assert_o_close(o, o_ref, "graph replay")
+        assert_lse_close(lse, lse_ref, "graph replay")
+        assert _lib.device_status() == 0
+    finally:
+        dec.close()
 
 
 # ------------------------------------------------------------------------------------------------
