@@ -82,6 +82,12 @@ PFN_encodeTiled get_encode_tiled() {
 
 namespace {
 
+// instance parameters of the split-KV family that belong to the tcgen05 kernel's file
+bool split_key_of_sm100(const char* key) {
+    return !strcmp(key, "use_sm100_splitkv") || !strcmp(key, "exp_mode_splitkv") || !strcmp(key, "split_item_cost") ||
+           !strcmp(key, "split_min_piece_tiles");
+}
+
 // how FmhaFwd reads a non-null bias pointer (the reference fixes both per compiled instance)
 std::atomic<int64_t> g_bias_enum{1}, g_bias_rank_info{0};
 
@@ -479,7 +485,7 @@ int FlashckSetInstanceParam(int family, const char* key, int64_t value) {
         return FLASHCK_OK;
     }
     if (family == 0) rc = fwd_set_param(key, value);
-    else if (family == 2) rc = (!strcmp(key, "use_sm100_splitkv") || !strcmp(key, "exp_mode_splitkv")) ? fwd_set_param(key, value) : splitkv_set_param(key, value);
+    else if (family == 2) rc = split_key_of_sm100(key) ? fwd_set_param(key, value) : splitkv_set_param(key, value);
     if (rc) set_last_error("FlashckSetInstanceParam: unknown family/key %d/%s", family, key);
     return rc;
 }
@@ -489,7 +495,7 @@ int FlashckGetInstanceParam(int family, const char* key, int64_t* value_out) {
     if (family == 0 && !strcmp(key, "bias_enum")) { *value_out = g_bias_enum; return FLASHCK_OK; }
     if (family == 0 && !strcmp(key, "bias_rank_info")) { *value_out = g_bias_rank_info; return FLASHCK_OK; }
     if (family == 0) rc = fwd_get_param(key, value_out);
-    else if (family == 2) rc = (!strcmp(key, "use_sm100_splitkv") || !strcmp(key, "exp_mode_splitkv")) ? fwd_get_param(key, value_out) : splitkv_get_param(key, value_out);
+    else if (family == 2) rc = split_key_of_sm100(key) ? fwd_get_param(key, value_out) : splitkv_get_param(key, value_out);
     if (rc) set_last_error("FlashckGetInstanceParam: unknown family/key %d/%s", family, key);
     return rc;
 }

@@ -88,6 +88,7 @@ struct Sm100Dev {
     float* o_acc;
     float* lse_acc;
     int num_splits, piece_tiles, group, sq_cap;
+    int item_cost;    // units of the work line that stand for an item's fixed cost (see kItemCostDefault)
     int causal;       // mask type: 0 none, 1 top-left, 2 bottom-right, 3 window with top-left alignment
     int wl, wr;       // window of a masked problem: keys [i + shift - wl, i + shift + wr] of row i; -1 = unbounded
     int num_levels;   // row blocks of the longest sequence (128 rows when heads are paired, else 256)
@@ -290,12 +291,14 @@ static_assert(1024 + (2 + 2 * KV_SLOTS) * TILE_BYTES + 8 * STAGE_BYTES + sizeof(
               "tiles, staging buffers and the control block must fit the 227 KB a CTA can have");
 
 // Split modes.  A stream is the key tiles one (sequence, 128-row block of the packed rows, kv head) needs; all streams,
-// in that order, each preceded by kItemCost units that stand for an item's fixed cost (Q load, pipeline fill, epilogue),
+// in that order, each preceded by item_cost units (kItemCostDefault) that stand for an item's fixed cost (Q load, pipeline fill, epilogue),
 // form one line that is cut into equal pieces of split_w units, one per CTA, so that the SMs finish together whatever
 // the lengths are.  The part of a stream inside one CTA's piece is a work item and one split of the result; a stream
 // cut k times uses splits 0..k.  split_w is raised where needed so that no stream needs more splits than the
 // workspace has; with a single split per stream the whole stream goes to the CTA its start falls to.
-constexpr int kItemCost = 6;
+constexpr int kItemCostDefault = 6;   // instance parameter "split_item_cost" (1 .. 64)
+std::atomic<int64_t> g_split_item_cost{kItemCostDefault};
+std::atomic<int64_t> g_split_min_piece_tiles{8};  // instance parameter "split_min_piece_tiles": at least 1024 keys per work item
 
 // key tiles the rows of row block `rb` of a sequence see
 __device__ __forceinline__ int split_stream_tiles(const Sm100Dev& p, int sq, int sk, int rb) {
@@ -310,9 +313,9 @@ __device__ __forceinline__ int split_stream_tiles(const Sm100Dev& p, int sq, int
 }
 
 // splits a stream of n tiles starting at unit g0 of the line uses (pieces; the mode with duplicated rows writes two per piece)
-__device__ __forceinline__ int split_stream_pieces(int g0, int n, int w, int max_pieces) {
+__device__ __forceinline__ int split_stream_pieces(int g0, int n, int w, int max_pieces, int item_cost) {
     if (n == 0 || max_pieces == 1) return 1;
-    return (g0 + kItemCost + n - 1) / w - (g0 + kItemCost) / w + 1;
+    return (g0 + item_cost + n - 1) / w - (g0 + item_cost) / w + 1;
 }
 
 __device__ __forceinline__ void expand_item_split(const Ctrl* ctrl, const Sm100Dev& p, uint32_t packed, int rnd, Item& it) {
@@ -416,7 +419,7 @@ __device__ __forceinline__ void get_item(const Ctrl* ctrl, const Sm100Dev& p, in
 
 // WINDOW: the mask has a left window or a right window other than 0 (everything but no mask / causal); a separate
 // instance, so that the common masks do not carry the second bound of the visible range through the softmax loop.
-// SPLIT 1: the split-KV form described at Sm100Dev (one Q tile per item; work cut as described at kItemCost).  The S
+// SPLIT 1: the split-KV form described at Sm100Dev (one Q tile per item; work cut as described at kItemCostDefault).  The S
 //          columns of tile 1 are a second S buffer, its Q room a third K slot; K, V and Q have a producer warp each
 //          (9, 10, 11); warp 8 issues the QK^T, the first thread of warp 4 the PV products, warps 5-7 write LSE = -inf
 //          to the splits no work item fills.
@@ -512,7 +515,7 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
             int cost = 0, nmax = 0;
             for (int rb = 0; rb < rbc; ++rb) {
                 const int n = split_stream_tiles(p, sq, sk, rb);
-                cost += n + kItemCost;
+                cost += n + p.item_cost;
                 nmax = max(nmax, n);
             }
             ctrl->nblk[b] = cost * p.hkv;
@@ -532,7 +535,7 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                 nmax = max(nmax, (int)ctrl->items[b]);
             }
             ctrl->level_start[p.batch] = run;
-            int w = max((run + (int)gridDim.x - 1) / (int)gridDim.x, p.piece_tiles + kItemCost);
+            int w = max((run + (int)gridDim.x - 1) / (int)gridDim.x, p.piece_tiles + p.item_cost);
             if (max_pieces >= 2) w = max(w, (nmax + max_pieces - 2) / (max_pieces - 1));  // ceil(n / w) + 1 <= max_pieces
             ctrl->split_w = w;
         }
@@ -554,7 +557,7 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                     const int rbc = (sq * p.group + BM - 1) / BM;
                     int seg0 = ctrl->level_start[b];
                     for (int rb = 0; rb < rbc && seg0 < hi; ++rb) {
-                        const int n = split_stream_tiles(p, sq, sk, rb), c = n + kItemCost;
+                        const int n = split_stream_tiles(p, sq, sk, rb), c = n + p.item_cost;
                         const int kh_lo = max(0, (lo - seg0) / c), kh_hi = min(p.hkv - 1, (hi - 1 - seg0) / c);
                         for (int kh = kh_lo; kh <= kh_hi; ++kh) {
                             const int g0 = seg0 + kh * c;
@@ -562,10 +565,10 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                             if (n == 0 || max_pieces == 1) {
                                 if (g0 < lo) continue;  // the whole stream belongs to the CTA its start falls to
                             } else {
-                                t_lo = max(0, lo - g0 - kItemCost);
-                                t_hi = min(n, hi - g0 - kItemCost);
+                                t_lo = max(0, lo - g0 - p.item_cost);
+                                t_hi = min(n, hi - g0 - p.item_cost);
                                 if (t_hi <= t_lo) continue;
-                                piece = (int)blockIdx.x - (g0 + kItemCost) / w;
+                                piece = (int)blockIdx.x - (g0 + p.item_cost) / w;
                             }
                             if (cnt >= kSplitItems) { overflow = true; break; }
                             ctrl->items[cnt] = 0x80000000u | ((uint32_t)b << 22) | ((uint32_t)kh << 12) | ((uint32_t)piece << 4) | (uint32_t)rb;
@@ -961,10 +964,10 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                     const int rbc = (sq * p.group + BM - 1) / BM;
                     int seg0 = ctrl->level_start[b];
                     for (int rb = 0; rb < rbc; ++rb) {
-                        const int n = split_stream_tiles(p, sq, sk, rb), c = n + kItemCost;
+                        const int n = split_stream_tiles(p, sq, sk, rb), c = n + p.item_cost;
                         const int rows = min(BM, sq * p.group - rb * BM);
                         for (int kh = 0; kh < p.hkv; ++kh) {
-                            const int used = split_stream_pieces(seg0 + kh * c, n, w, max_pieces) * kDup;
+                            const int used = split_stream_pieces(seg0 + kh * c, n, w, max_pieces, p.item_cost) * kDup;
                             const int cnt = (p.num_splits - used) * rows;
                             for (int e = (int)threadIdx.x - 160; e < cnt; e += 96) {
                                 const int sp = used + e / rows, pr = rb * BM + e % rows;
@@ -1375,7 +1378,6 @@ int launch_fwd_sm100(const FwdParams& p, cudaStream_t stream) {
 // ---- split-KV with several query rows per kv head (append + decode, speculative decoding, chunked prefill) ----
 namespace {
 
-constexpr int kMinPieceTiles = 8;  // at least 1024 keys per work item
 
 // Q [tokens, hkv, group, 128] as boxes of (64 columns, group heads, 1 kv head, 128/group tokens).
 int make_map_q_packed(CUtensorMap* map, const void* base, int dtype, int64_t tokens, int64_t hkv, int64_t group, int rows) {
@@ -1450,17 +1452,18 @@ bool splitkv_sm100_supported(const SplitKVParams& p) {
     }
     if (p.num_splits > 1 && !p.lse_acc) return false;
     if (p.num_splits > 255) return false;  // the split index of a work item has 8 bits
-    // The work line (see kItemCost) is indexed with 31 bits, and a CTA's work list holds kSplitItems items: a CTA's
-    // piece of w units reaches into at most w / kItemCost + 2 streams, and w is at most the larger of the line's
+    // The work line (see kItemCostDefault) is indexed with 31 bits, and a CTA's work list holds kSplitItems items: a CTA's
+    // piece of w units reaches into at most w / item_cost + 2 streams, and w is at most the larger of the line's
     // 148th, the shortest piece, and what keeps the longest possible stream within the workspace's splits.
     const int64_t cap_tiles = split_cap_tiles(p);
     const int64_t streams = p.batch * p.hkv * ((p.max_seqlen_q * group + BM - 1) / BM);
-    const int64_t line = streams * (cap_tiles + kItemCost);
+    const int64_t item_cost = g_split_item_cost.load(), min_piece = g_split_min_piece_tiles.load();
+    const int64_t line = streams * (cap_tiles + item_cost);
     if (line >= (1ll << 31)) return false;
     const int64_t max_pieces = std::max<int64_t>(1, split_duplicates_rows(p) ? p.num_splits / 2 : p.num_splits);
-    int64_t w_max = std::max<int64_t>(line / sm_count() + 1, kMinPieceTiles + kItemCost);
+    int64_t w_max = std::max<int64_t>(line / sm_count() + 1, min_piece + item_cost);
     if (max_pieces >= 2) w_max = std::max(w_max, cap_tiles / (max_pieces - 1) + 1);
-    if (std::min(streams, w_max / kItemCost + 2) > kSplitItems) return false;
+    if (std::min(streams, w_max / item_cost + 2) > kSplitItems) return false;
     const int64_t tokens = p.seqstart_q ? p.total_q : p.batch * p.seqlen_q;
     if (tokens >= (1ll << 31) || (!p.block_table && p.batch * p.seqlen_k_cap >= (1ll << 31))) return false;
     if (p.block_table && p.num_pages * p.page >= (1ll << 31)) return false;
@@ -1482,7 +1485,8 @@ int launch_splitkv_sm100(const SplitKVParams& p, cudaStream_t stream) {
     dev.page = p.block_table ? (int)p.page : BN;
     dev.bt_stride = (int)p.bt_stride;
     dev.o_acc = p.o_acc; dev.lse_acc = p.lse_acc; dev.num_splits = (int)p.num_splits;
-    dev.piece_tiles = kMinPieceTiles;
+    dev.piece_tiles = (int)g_split_min_piece_tiles.load();
+    dev.item_cost = (int)g_split_item_cost.load();
     dev.group = (int)(p.hq / p.hkv);
     dev.sq_cap = (int)p.seqlen_q;
     dev.causal = p.mask_type; dev.wl = -1; dev.wr = p.mask_type ? 0 : -1;
@@ -1514,6 +1518,16 @@ int fwd_set_param(const char* key, int64_t value) {
         g_exp_mode_splitkv = value;
         return FLASHCK_OK;
     }
+    if (!strcmp(key, "split_item_cost")) {
+        if (value < 1 || value > 64) return FLASHCK_ERR_INVALID_ARGUMENT;
+        g_split_item_cost = value;
+        return FLASHCK_OK;
+    }
+    if (!strcmp(key, "split_min_piece_tiles")) {
+        if (value < 1 || value > 4096) return FLASHCK_ERR_INVALID_ARGUMENT;
+        g_split_min_piece_tiles = value;
+        return FLASHCK_OK;
+    }
     if (!strcmp(key, "rescale_log2_x100")) {
         if (value < 0 || value > 1400) return FLASHCK_ERR_INVALID_ARGUMENT;  // f16 holds 2^15; P < 2^14 leaves headroom
         g_rescale_half_x100 = value;
@@ -1532,6 +1546,8 @@ int fwd_get_param(const char* key, int64_t* value) {
     if (!strcmp(key, "exp_mode")) { *value = g_exp_mode; return FLASHCK_OK; }
     if (!strcmp(key, "exp_mode_splitkv")) { *value = g_exp_mode_splitkv; return FLASHCK_OK; }
     if (!strcmp(key, "rescale_log2_x100")) { *value = g_rescale_half_x100; return FLASHCK_OK; }
+    if (!strcmp(key, "split_item_cost")) { *value = g_split_item_cost; return FLASHCK_OK; }
+    if (!strcmp(key, "split_min_piece_tiles")) { *value = g_split_min_piece_tiles; return FLASHCK_OK; }
     if (!strcmp(key, "poly8")) { const int64_t m = g_exp_mode; *value = m >= 11 ? m - 10 : 0; return FLASHCK_OK; }
     return FLASHCK_ERR_INVALID_ARGUMENT;
 }

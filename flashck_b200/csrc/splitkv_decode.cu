@@ -22,6 +22,7 @@
 // Every mbarrier wait is bounded; on expiry the CTA sets the device status word and drains.
 #include "kernels.h"
 
+#include <algorithm>
 #include <atomic>
 #include <string.h>
 #include <type_traits>
@@ -34,6 +35,8 @@ constexpr int kTok = 16;  // tokens per tile
 
 std::atomic<int64_t> g_stages{0};          // 0 = as many as fit
 std::atomic<int64_t> g_ctas_per_sm_x100{100};  // grid.x = SMs * this / 100
+std::atomic<int64_t> g_heads_per_cta{0};   // kv heads per CTA (8, 4, 2, 1); 0 = the most that divides nhead_k and fits 8 warps
+std::atomic<int64_t> g_row_tiles{0};       // 16-row tiles of (token, group head) rows per pass (1, 2, 4); 0 = by the problem
 
 struct DecodeDev {
     const void* q;
@@ -601,14 +604,18 @@ template <typename T, int D, int MT>
 int launch_hk(const SplitKVParams& p, const DecodeDev& dev, cudaStream_t stream) {
     const int64_t hkv = p.hkv;
     constexpr int kMaxHK = 8 / MT;
+    // the instance parameter caps the heads per CTA; a value the problem cannot take (not a divisor of nhead_k, more
+    // than 8 warps with this many row tiles) falls through to the next smaller one
+    const int64_t want = g_heads_per_cta.load();
+    const int cap = want > 0 ? (int)want : 8;
     if constexpr (kMaxHK >= 8) {
-        if (hkv % 8 == 0) return launch_inst<T, D, 8, MT>(p, dev, stream);
+        if (cap >= 8 && hkv % 8 == 0) return launch_inst<T, D, 8, MT>(p, dev, stream);
     }
     if constexpr (kMaxHK >= 4) {
-        if (hkv % 4 == 0) return launch_inst<T, D, 4, MT>(p, dev, stream);
+        if (cap >= 4 && hkv % 4 == 0) return launch_inst<T, D, 4, MT>(p, dev, stream);
     }
     if constexpr (kMaxHK >= 2) {
-        if (hkv % 2 == 0) return launch_inst<T, D, 2, MT>(p, dev, stream);
+        if (cap >= 2 && hkv % 2 == 0) return launch_inst<T, D, 2, MT>(p, dev, stream);
     }
     return launch_inst<T, D, 1, MT>(p, dev, stream);
 }
@@ -616,8 +623,10 @@ int launch_hk(const SplitKVParams& p, const DecodeDev& dev, cudaStream_t stream)
 template <typename T, int D>
 int launch_mt(const SplitKVParams& p, const DecodeDev& dev, cudaStream_t stream) {
     const int64_t row_tiles = (p.max_seqlen_q * (p.hq / p.hkv) + 15) / 16;
-    if (row_tiles <= 1) return launch_hk<T, D, 1>(p, dev, stream);
-    if (row_tiles <= 2) return launch_hk<T, D, 2>(p, dev, stream);
+    const int64_t want = g_row_tiles.load();  // more row tiles per pass than the problem has rows only idle warps
+    const int64_t mt = want > 0 ? std::min<int64_t>(want, row_tiles <= 1 ? 1 : (row_tiles <= 2 ? 2 : 4)) : row_tiles;
+    if (mt <= 1) return launch_hk<T, D, 1>(p, dev, stream);
+    if (mt <= 2) return launch_hk<T, D, 2>(p, dev, stream);
     return launch_hk<T, D, 4>(p, dev, stream);
 }
 
@@ -626,11 +635,23 @@ int launch_mt(const SplitKVParams& p, const DecodeDev& dev, cudaStream_t stream)
 int splitkv_set_param(const char* key, int64_t value) {
     if (!strcmp(key, "stages")) { g_stages = value; return FLASHCK_OK; }
     if (!strcmp(key, "ctas_per_sm_x100")) { g_ctas_per_sm_x100 = value; return FLASHCK_OK; }
+    if (!strcmp(key, "heads_per_cta")) {
+        if (value != 0 && value != 1 && value != 2 && value != 4 && value != 8) return FLASHCK_ERR_INVALID_ARGUMENT;
+        g_heads_per_cta = value;
+        return FLASHCK_OK;
+    }
+    if (!strcmp(key, "row_tiles")) {
+        if (value != 0 && value != 1 && value != 2 && value != 4) return FLASHCK_ERR_INVALID_ARGUMENT;
+        g_row_tiles = value;
+        return FLASHCK_OK;
+    }
     return FLASHCK_ERR_INVALID_ARGUMENT;
 }
 int splitkv_get_param(const char* key, int64_t* value) {
     if (!strcmp(key, "stages")) { *value = g_stages; return FLASHCK_OK; }
     if (!strcmp(key, "ctas_per_sm_x100")) { *value = g_ctas_per_sm_x100; return FLASHCK_OK; }
+    if (!strcmp(key, "heads_per_cta")) { *value = g_heads_per_cta; return FLASHCK_OK; }
+    if (!strcmp(key, "row_tiles")) { *value = g_row_tiles; return FLASHCK_OK; }
     return FLASHCK_ERR_INVALID_ARGUMENT;
 }
 

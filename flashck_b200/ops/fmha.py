@@ -112,6 +112,31 @@ def _alibi_args(alibi_slopes: Optional[torch.Tensor], batch: int, hq: int):
     return _ptr(alibi_slopes), 2, (0 if alibi_slopes.shape[0] == 1 else 1)
 
 
+def _dtype_name(t: torch.Tensor) -> str:
+    return "fp16" if t.dtype == torch.float16 else "bf16"
+
+
+def _mask_name(mt: int, wl: int, wr: int) -> str:
+    if mt == 0:
+        return "none"
+    return "causal" if (wl < 0 and wr == 0) else "window"
+
+
+def _launch_tuned(family: str, problem_args: dict, call):
+    """Runs ``call`` (one C-ABI launch that returns a status).  With ``FC_TUNING_MODE`` 1 or 2 the instance parameters
+    of the family are first set to the tuning cache's winner for this problem; on a cache miss the candidates are timed
+    on this very call's tensors and the winner is cached (the reference tunes at graph-compile time and serves later
+    runs from ``flash_ck.db``, core/profiling/graph_codegen.cc:54-126)."""
+    from .. import tuner
+    if not tuner.tuning_enabled():
+        return call()
+    from ..instances import FmhaProblem
+    def run():  # a candidate that refuses the problem must not look fast: its status is an error
+        _lib.check(call(), family)
+    tuner.select_instance(family, FmhaProblem(family=family, **problem_args), run)
+    return call()
+
+
 def _bias_args(q: torch.Tensor, bias, alibi_slopes, batch: int, hq: int, sq: int, sk: int):
     """(buffer, bias_enum, bias_rank_info) for the C call; the enum and rank values are those of the reference's
     BiasEnum / BiasEnumInfo (core/profiling/attention/fmha_library.h:121-164)."""
@@ -157,9 +182,13 @@ def fmha_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, scale: Option
     lse = torch.empty((b, hq, sq), dtype=torch.float32, device=q.device) if return_lse else None
     bias_buf, bias_enum, bias_rank = _bias_args(q, bias, alibi_slopes, b, hq, sq, sk)
     with torch.cuda.device(q.device):
-        rc = _lib.lib().FmhaFwdBias(_ptr(q), _ptr(k), _ptr(v), _ptr(bias_buf), _ptr(o), None, None, None, b, sq, sk, hq,
-                                    hkv, d, dv, sq, float(scale or 0.0), wl, wr, mt, _stream(), _ptr(lse),
-                                    _dtype_code(q), bias_enum, bias_rank, float(logits_soft_cap))
+        rc = _launch_tuned(
+            "fmha_fwd", dict(dtype=_dtype_name(q), mode="batch", batch=b, hq=hq, hkv=hkv, d=d, dv=dv, max_seqlen_q=sq,
+                             max_seqlen_k=sk, mask=_mask_name(mt, wl, wr), bias=("none", "elementwise", "alibi")[bias_enum],
+                             soft_cap=logits_soft_cap > 0),
+            lambda: _lib.lib().FmhaFwdBias(_ptr(q), _ptr(k), _ptr(v), _ptr(bias_buf), _ptr(o), None, None, None, b, sq, sk,
+                                           hq, hkv, d, dv, sq, float(scale or 0.0), wl, wr, mt, _stream(), _ptr(lse),
+                                           _dtype_code(q), bias_enum, bias_rank, float(logits_soft_cap)))
     _lib.check(rc, "FmhaFwd")
     return (o, lse) if return_lse else o
 
@@ -195,10 +224,15 @@ def fmha_fwd_var_len(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqle
     bias_buf, bias_enum, bias_rank = _bias_args(q, bias, alibi_slopes, 1 if bias is not None else batch, hq, total_q,
                                                 total_k)
     with torch.cuda.device(q.device):
-        rc = _lib.lib().FmhaFwdBias(_ptr(q), _ptr(k), _ptr(v), _ptr(bias_buf), _ptr(o), _ptr(cu_q), _ptr(cu_k), None,
-                                    batch, total_q, total_k, hq, hkv, d, dv, int(max_seqlen_q), float(scale or 0.0), wl,
-                                    wr, mt, _stream(), _ptr(lse), _dtype_code(q), bias_enum, bias_rank,
-                                    float(logits_soft_cap))
+        rc = _launch_tuned(
+            "fmha_fwd", dict(dtype=_dtype_name(q), mode="group", batch=batch, hq=hq, hkv=hkv, d=d, dv=dv,
+                             max_seqlen_q=int(max_seqlen_q), max_seqlen_k=int(max_seqlen_k) or int(max_seqlen_q),
+                             mask=_mask_name(mt, wl, wr), bias=("none", "elementwise", "alibi")[bias_enum],
+                             soft_cap=logits_soft_cap > 0),
+            lambda: _lib.lib().FmhaFwdBias(_ptr(q), _ptr(k), _ptr(v), _ptr(bias_buf), _ptr(o), _ptr(cu_q), _ptr(cu_k), None,
+                                           batch, total_q, total_k, hq, hkv, d, dv, int(max_seqlen_q), float(scale or 0.0),
+                                           wl, wr, mt, _stream(), _ptr(lse), _dtype_code(q), bias_enum, bias_rank,
+                                           float(logits_soft_cap)))
     _lib.check(rc, "FmhaFwd")
     return (o, lse) if return_lse else o
 
@@ -450,11 +484,16 @@ def fmha_fwd_splitkv(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
     bias_ptr, bias_enum, bias_rank = _alibi_args(alibi_slopes, batch, hq)
     # pages of a paged pool, or rows of a contiguous cache (packed K/V: unused): where the K/V tensor maps end
     pool_extent = 0 if cu_k is not None else k_cache.shape[0]
+    cap_k = bt.shape[1] * page if bt is not None else shape_sk
     with torch.cuda.device(q.device):
-        rc = _lib.lib().FmhaFwdSplitKVEx(_ptr(q), _ptr(k_cache), _ptr(v_cache), bias_ptr, _ptr(lse_acc), _ptr(o_acc),
-                                         _ptr(cu_q), _ptr(cu_k), _ptr(sl), _ptr(bt), _ptr(cbi), batch, shape_sq,
-                                         shape_sk, hq, hkv, d, dv, max_sq, S, max_pages, page, float(scale or 0.0), wl,
-                                         wr, mt, _stream(), _dtype_code(q), bias_enum, bias_rank, pool_extent)
+        rc = _launch_tuned(
+            "fmha_fwd_split_kv", dict(dtype=_dtype_name(q), mode="group" if group else "batch", batch=batch, hq=hq, hkv=hkv,
+                                      d=d, dv=dv, max_seqlen_q=max_sq, max_seqlen_k=int(cap_k), mask=_mask_name(mt, wl, wr),
+                                      bias="alibi" if bias_enum else "none", paged=bt is not None, page=int(page)),
+            lambda: _lib.lib().FmhaFwdSplitKVEx(_ptr(q), _ptr(k_cache), _ptr(v_cache), bias_ptr, _ptr(lse_acc), _ptr(o_acc),
+                                                _ptr(cu_q), _ptr(cu_k), _ptr(sl), _ptr(bt), _ptr(cbi), batch, shape_sq,
+                                                shape_sk, hq, hkv, d, dv, max_sq, S, max_pages, page, float(scale or 0.0),
+                                                wl, wr, mt, _stream(), _dtype_code(q), bias_enum, bias_rank, pool_extent))
     _lib.check(rc, "FmhaFwdSplitKV")
     if not combine:
         return lse_acc, o_acc

@@ -23,11 +23,11 @@ import itertools
 import json
 import os
 import sqlite3
-from dataclasses import dataclass, field
+from dataclasses import asdict, dataclass, field
 from typing import Callable, Dict, Iterable, List, Optional
 
-__all__ = ["TuningFlags", "load_search_space", "expand_param", "cartesian_product", "ProfilingDB", "Tuner",
-           "FAMILY_IDS"]
+__all__ = ["TuningFlags", "load_search_space", "load_candidates", "expand_param", "cartesian_product", "ProfilingDB",
+           "Tuner", "FAMILY_IDS", "select_instance", "tuning_enabled", "ncu_tensor_pipe_pct"]
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 FAMILY_IDS = {"fmha_fwd": 0, "fmha_fwd_split_kv": 2}  # FmhaKind values (fmha_library.h:17-25)
@@ -80,8 +80,21 @@ def cartesian_product(space: Dict[str, List[int]]) -> List[Dict[str, int]]:
     return [dict(zip(keys, combo)) for combo in itertools.product(*(space[k] for k in keys))]
 
 
-def instance_name(family: str, cfg: Dict[str, int]) -> str:
-    return family + "_" + "_".join(f"{k}{v}" for k, v in sorted(cfg.items()))
+def load_candidates(family: str, config_root: Optional[str] = None) -> List:
+    """Every instance of the family's search space (sections ``instance``, ``launch`` and ``strategy`` of its JSON file
+    multiplied out, core/profiling/attention/fmha_fwd/fmha_fwd_emitter.cc:132-323), in canonical form, without
+    duplicates, in a stable order."""
+    from . import instances as I
+    space: Dict[str, List[int]] = {}
+    for section in ("instance", "launch", "strategy"):
+        space.update(load_search_space(family, config_root, section))
+    seen, out = set(), []
+    for cfg in cartesian_product(space):
+        inst = I.from_config(family, cfg).canonical()
+        if inst not in seen:
+            seen.add(inst)
+            out.append(inst)
+    return out
 
 
 class ProfilingDB:
@@ -95,7 +108,10 @@ class ProfilingDB:
             "CREATE TABLE IF NOT EXISTS fmha ("
             "id INTEGER PRIMARY KEY AUTOINCREMENT, cuda_version TEXT NOT NULL, device_name TEXT NOT NULL,"
             "setting TEXT NOT NULL, problem TEXT NOT NULL, instance_name TEXT NOT NULL, instance TEXT NOT NULL,"
-            "split_k INTEGER NOT NULL DEFAULT -1, latency REAL, tflops REAL, bandwidth REAL)")
+            "split_k INTEGER NOT NULL DEFAULT -1, latency REAL, tflops REAL, bandwidth REAL, tensor_pipe_pct REAL)")
+        cols = [r[1] for r in self.conn.execute("PRAGMA table_info(fmha)")]
+        if "tensor_pipe_pct" not in cols:  # a database written before the column existed
+            self.conn.execute("ALTER TABLE fmha ADD COLUMN tensor_pipe_pct REAL")
         self.conn.commit()
 
     @staticmethod
@@ -104,21 +120,22 @@ class ProfilingDB:
 
     def query(self, env: dict, setting: dict, problem: dict) -> Optional[dict]:
         row = self.conn.execute(
-            "SELECT instance_name, instance, latency, tflops, bandwidth FROM fmha WHERE cuda_version=? AND device_name=? "
+            "SELECT instance_name, instance, latency, tflops, bandwidth, tensor_pipe_pct, split_k FROM fmha WHERE cuda_version=? AND device_name=? "
             "AND setting=? AND problem=? ORDER BY id DESC LIMIT 1",
             (env["cuda_version"], env["device_name"], self._key(setting), self._key(problem))).fetchone()
         if row is None:
             return None
         return {"instance_name": row[0], "instance": json.loads(row[1]), "latency": row[2], "tflops": row[3],
-                "bandwidth": row[4]}
+                "bandwidth": row[4], "tensor_pipe_pct": row[5], "split_k": row[6]}
 
     def insert(self, env: dict, setting: dict, problem: dict, name: str, instance: dict, latency: float,
-               tflops: Optional[float], bandwidth: Optional[float]) -> None:
+               tflops: Optional[float], bandwidth: Optional[float], tensor_pipe_pct: Optional[float] = None,
+               split_k: int = -1) -> None:
         self.conn.execute(
-            "INSERT INTO fmha (cuda_version, device_name, setting, problem, instance_name, instance, latency, tflops, "
-            "bandwidth) VALUES (?,?,?,?,?,?,?,?,?)",
+            "INSERT INTO fmha (cuda_version, device_name, setting, problem, instance_name, instance, split_k, latency, "
+            "tflops, bandwidth, tensor_pipe_pct) VALUES (?,?,?,?,?,?,?,?,?,?,?)",
             (env["cuda_version"], env["device_name"], self._key(setting), self._key(problem), name,
-             json.dumps(instance, sort_keys=True), latency, tflops, bandwidth))
+             json.dumps(instance, sort_keys=True), split_k, latency, tflops, bandwidth, tensor_pipe_pct))
         self.conn.commit()
 
     def flush(self) -> None:
@@ -129,16 +146,21 @@ class ProfilingDB:
 
 @dataclass
 class Tuner:
-    """Times the candidates of one family on a caller-supplied workload and applies the winner.
+    """Times the valid instances of one family on a caller-supplied workload and applies the winner.
 
     ``timer(run, cold, repeats, flush)`` returns milliseconds per call; the default uses CUDA events.  ``apply`` sets
-    one instance parameter (default: ``FlashckSetInstanceParam``).  Both are injectable so that the selection logic
-    is testable without a GPU."""
+    one instance parameter (default: ``FlashckSetInstanceParam``).  ``utilisation(instance)`` (optional) returns the
+    tensor-pipe busy percentage of a candidate, e.g. from an ncu capture of a small case
+    (:func:`ncu_tensor_pipe_pct`); it is stored beside the timing, and with ``FC_TUNING_METRIC`` 1 it breaks ties
+    between candidates whose TFLOP/s differ by less than 1 %.  All three are injectable so that the selection logic is
+    testable without a GPU."""
     flags: TuningFlags = field(default_factory=TuningFlags)
     db: Optional[ProfilingDB] = None
     timer: Optional[Callable] = None
     apply: Optional[Callable[[int, str, int], None]] = None
     env: Optional[dict] = None
+    utilisation: Optional[Callable] = None
+    log: List[dict] = field(default_factory=list)  # every candidate timed by the last sweep
 
     def __post_init__(self):
         if self.db is None:
@@ -157,44 +179,129 @@ class Tuner:
         return {"metric": f.FC_TUNING_METRIC, "cold": f.FC_TUNING_NUM_COLD_ITERATION, "repeats": f.FC_TUNING_NUM_REPEATS,
                 "flush_cache": bool(f.FC_TUNING_FLUSH_CACHE)}
 
-    def candidates(self, family: str) -> List[Dict[str, int]]:
-        cands = cartesian_product(load_search_space(family, self.flags.FC_CONFIG_JSON_PATH))
-        return cands[:1] if self.flags.FC_TUNING_MODE == 0 else cands
+    def candidates(self, family: str, problem) -> List:
+        """Valid instances for the problem, narrowed as FC_TUNING_MODE says: 0 (heuristic) the first survivor of the
+        rules of thumb, 2 (hybrid) all survivors, 1 (autotuning) every valid instance
+        (fmha_fwd_emitter.cc:325-466 applies the same three modes)."""
+        from . import instances as I
+        valid = [t for t in load_candidates(family, self.flags.FC_CONFIG_JSON_PATH) if I.is_valid(t, problem)]
+        if not valid:
+            raise RuntimeError(f"no instance of {family} can run {problem.name()}")
+        mode = self.flags.FC_TUNING_MODE
+        if mode == 1:
+            return valid
+        kept = I.heuristic_filter(valid, problem)
+        return kept[:1] if mode == 0 else kept
 
-    def _score(self, ms: float, flops: Optional[float], nbytes: Optional[float]) -> float:
+    def _score(self, rec: dict) -> float:
         m = self.flags.FC_TUNING_METRIC
-        if m == 1 and flops:
-            return flops / ms
-        if m == 2 and nbytes:
-            return nbytes / ms
-        return -ms
+        if m == 1 and rec["tflops"]:
+            return rec["tflops"]
+        if m == 2 and rec["bandwidth"]:
+            return rec["bandwidth"]
+        return -rec["latency"]
 
-    def tune(self, family: str, problem: dict, run: Callable[[], object], flops: Optional[float] = None,
+    def _better(self, a: dict, b: Optional[dict]) -> bool:
+        if b is None:
+            return True
+        sa, sb = self._score(a), self._score(b)
+        if self.flags.FC_TUNING_METRIC == 1 and a.get("tensor_pipe_pct") and b.get("tensor_pipe_pct") \
+                and abs(sa - sb) <= 0.01 * max(abs(sa), abs(sb)):
+            return a["tensor_pipe_pct"] > b["tensor_pipe_pct"]
+        return sa > sb
+
+    def _apply(self, fam: int, params: Dict[str, int]) -> None:
+        for k, v in params.items():
+            self.apply(fam, k, v)
+
+    def tune(self, family: str, problem, run: Callable[[], object], flops: Optional[float] = None,
              nbytes: Optional[float] = None) -> dict:
-        """Returns the winning record and leaves its parameters applied."""
+        """Returns the winning record (served from the cache when there is one) and leaves its parameters applied.
+        ``problem`` is an :class:`flashck_b200.instances.FmhaProblem`."""
+        from . import instances as I
         fam = FAMILY_IDS[family]
-        cached = None if self.flags.FC_FORCE_PROFILING else self.db.query(self.env, self.setting(), problem)
+        key = problem.key()
+        cached = None if self.flags.FC_FORCE_PROFILING else self.db.query(self.env, self.setting(), key)
         if cached is not None:
-            for k, v in cached["instance"].items():
-                self.apply(fam, k, v)
+            self._apply(fam, I.from_config(family, cached["instance"]).params())
+            cached["from_cache"] = True
             return cached
-        best = None
-        for cfg in self.candidates(family):
-            for k, v in cfg.items():
-                self.apply(fam, k, v)
-            ms = float(self.timer(run, self.flags.FC_TUNING_NUM_COLD_ITERATION, self.flags.FC_TUNING_NUM_REPEATS,
-                                  self.flags.FC_TUNING_FLUSH_CACHE))
-            rec = {"instance_name": instance_name(family, cfg), "instance": cfg, "latency": ms,
-                   "tflops": flops / ms / 1e9 if flops else None, "bandwidth": nbytes / ms / 1e6 if nbytes else None}
-            if best is None or self._score(ms, flops, nbytes) > self._score(best["latency"], flops, nbytes):
+        best, self.log = None, []
+        for inst in self.candidates(family, problem):
+            self._apply(fam, inst.params())
+            try:
+                ms = float(self.timer(run, self.flags.FC_TUNING_NUM_COLD_ITERATION, self.flags.FC_TUNING_NUM_REPEATS,
+                                      self.flags.FC_TUNING_FLUSH_CACHE))
+            except RuntimeError as e:  # the library refused the problem on this instance: not a candidate
+                self.log.append({"instance_name": inst.name(problem), "instance": asdict(inst), "error": str(e)})
+                continue
+            rec = {"instance_name": inst.name(problem), "instance": asdict(inst), "latency": ms,
+                   "tflops": flops / ms / 1e9 if flops else None, "bandwidth": nbytes / ms / 1e6 if nbytes else None,
+                   "tensor_pipe_pct": float(self.utilisation(inst)) if self.utilisation else None,
+                   "split_k": int(getattr(inst, "num_splits", -1) or -1), "from_cache": False}
+            self.log.append(rec)
+            if self._better(rec, best):
                 best = rec
         if best is None:
-            raise RuntimeError(f"no candidate instance for family {family}")
-        for k, v in best["instance"].items():
-            self.apply(fam, k, v)
-        self.db.insert(self.env, self.setting(), problem, best["instance_name"], best["instance"], best["latency"],
-                       best["tflops"], best["bandwidth"])
+            raise RuntimeError(f"every candidate of {family} failed on {problem.name()}: {self.log}")
+        self._apply(fam, I.from_config(family, best["instance"]).params())
+        self.db.insert(self.env, self.setting(), key, best["instance_name"], best["instance"], best["latency"],
+                       best["tflops"], best["bandwidth"], best["tensor_pipe_pct"], best["split_k"])
         return best
+
+
+# The tuner the functional API consults when FC_TUNING_MODE is not 0 (one per process, created on first use).
+_DEFAULT_TUNER: Optional[Tuner] = None
+
+
+def tuning_enabled() -> bool:
+    """The functional API tunes in-call when the mode is not 0 (heuristic) and a cache directory is set
+    (``FC_TUNING_DB_DIR``, empty by default as in the reference): without a place to keep the winners every process
+    would repeat the sweep, so the prebuilt default instances run instead."""
+    return int(_flag("FC_TUNING_MODE")) != 0 and bool(_flag("FC_TUNING_DB_DIR"))
+
+
+def select_instance(family: str, problem, run: Callable[[], object], flops: Optional[float] = None,
+                    nbytes: Optional[float] = None) -> dict:
+    """What ``flashck_b200.ops`` calls before a launch when tuning is on: applies the cached winner for the problem,
+    or -- on a miss -- times the candidates on the caller's own tensors (``run`` launches the call) and caches the
+    winner.  The instance parameters are process-wide, like the reference's single ProfilingEngine
+    (core/profiling/profiling_engine.cc:70-74)."""
+    global _DEFAULT_TUNER
+    if _DEFAULT_TUNER is None or _DEFAULT_TUNER.flags.FC_TUNING_MODE != int(_flag("FC_TUNING_MODE")) \
+            or _DEFAULT_TUNER.flags.FC_TUNING_DB_DIR != _flag("FC_TUNING_DB_DIR"):
+        _DEFAULT_TUNER = Tuner()
+    return _DEFAULT_TUNER.tune(family, problem, run, flops, nbytes)
+
+
+def ncu_tensor_pipe_pct(family: str, params: Dict[str, int], workload: str = "small") -> Optional[float]:
+    """sm__pipe_tensor_cycles_active (% of peak) of one candidate, from a one-metric ncu capture of a single launch of
+    the small probe workload (``python -m flashck_b200.tuner --probe``) in a child process; None when ncu is missing or
+    refuses to profile (then the CUDA-event TFLOP/s alone decides)."""
+    import csv
+    import io
+    import shutil
+    import subprocess
+    import sys
+    ncu = shutil.which("ncu")
+    if ncu is None:
+        return None
+    kernel = "regex:fmha_fwd_sm100|fmha_fwd_generic" if family == "fmha_fwd" else "regex:splitkv_decode|fmha_fwd_sm100"
+    cmd = [ncu, "--metrics", "sm__pipe_tensor_cycles_active.avg.pct_of_peak_sustained_active", "--clock-control", "none",
+           "-k", kernel, "-s", "2", "-c", "1", "--csv", sys.executable, "-m", "flashck_b200.tuner", "--probe", family,
+           "--workload", workload, "--params", json.dumps(params)]
+    try:
+        r = subprocess.run(cmd, capture_output=True, text=True, timeout=300)
+    except (OSError, subprocess.TimeoutExpired):
+        return None
+    rows = [l for l in r.stdout.splitlines() if l.startswith('"')]
+    for row in csv.DictReader(io.StringIO("\n".join(rows))):
+        if row.get("Metric Name", "").startswith("sm__pipe_tensor_cycles_active"):
+            try:
+                return float(row["Metric Value"].replace(",", ""))
+            except ValueError:
+                return None
+    return None
 
 
 def _environment() -> dict:
@@ -229,3 +336,94 @@ def _cuda_event_timer(run: Callable[[], object], cold: int, repeats: int, flush:
         torch.cuda.synchronize()
         total += beg.elapsed_time(end)
     return total / repeats
+
+
+# --------------------------------------------------------------------------------------------------------------
+# command line: tune the shipped workloads on this GPU, or run one candidate a few times for a profiler
+# --------------------------------------------------------------------------------------------------------------
+def _workload(name: str):
+    """(family, problem, run, flops, bytes) of a seeded synthetic workload: ``small`` / ``config2`` (varlen causal
+    prefill, 32/8 heads, hdim 128), ``decode_small`` / ``config3`` (paged decode, page 16), ``config4`` (1-16 query
+    tokens per sequence over a paged cache, causal)."""
+    import torch
+    from . import ops
+    from .instances import FmhaProblem
+    from .utils.inputs import make_paged_cache, normal_tensor, to_seqstarts, uniform_seqlens
+    dev, dt, hq, hkv, d = "cuda", torch.bfloat16, 32, 8, 128
+    if name in ("small", "config2"):
+        lens = uniform_seqlens(4, 512, 2048, 1234) if name == "small" else uniform_seqlens(16, 512, 4096, 1234)
+        cu = to_seqstarts(lens).to(dev)
+        total = sum(lens)
+        q, k, v = (normal_tensor((total, h, d), dt, 1 + i).to(dev) for i, h in enumerate((hq, hkv, hkv)))
+        flops = 4.0 * d * hq * sum(L * (L + 1) / 2 for L in lens)
+        prob = FmhaProblem("fmha_fwd", "bf16", "group", len(lens), hq, hkv, d, d, max(lens), max(lens), "causal")
+        run = lambda: ops.fmha_fwd_var_len(q, k, v, cu, cu, max(lens), causal=True, return_lse=True)
+        return "fmha_fwd", prob, run, flops, None
+    if name in ("decode_small", "config3"):
+        lens = uniform_seqlens(16, 1024, 16384, 4321) if name == "decode_small" else uniform_seqlens(64, 1024, 32768, 4321)
+        cache = make_paged_cache(lens, hkv, d, d, 16, dt, seed=5)
+        k, v, bt, sl = cache.k.to(dev), cache.v.to(dev), cache.block_table.to(dev), cache.seqlen_k.to(dev)
+        q = normal_tensor((len(lens), 1, hq, d), dt, 6).to(dev)
+        S = ops.default_num_splits(len(lens))
+        ws = ops.splitkv_workspace(q, d, S)
+        prob = FmhaProblem("fmha_fwd_split_kv", "bf16", "batch", len(lens), hq, hkv, d, d, 1, bt.shape[1] * 16, "none",
+                           paged=True, page=16)
+        run = lambda: ops.fmha_fwd_splitkv(q, k, v, seqlen_k=sl, block_table=bt, num_splits=S, workspace=ws)
+        return "fmha_fwd_split_kv", prob, run, None, float(sum(lens) * hkv * 2 * d * 2)
+    if name == "config4":
+        lens = uniform_seqlens(32, 2048 + 16, 16384 + 16, 777)
+        new = uniform_seqlens(32, 1, 16, 778)
+        cache = make_paged_cache(lens, hkv, d, d, 16, dt, seed=7)
+        k, v, bt, sl = cache.k.to(dev), cache.v.to(dev), cache.block_table.to(dev), cache.seqlen_k.to(dev)
+        cu = to_seqstarts(new).to(dev)
+        q = normal_tensor((sum(new), hq, d), dt, 8).to(dev)
+        S = ops.default_num_splits(len(lens), rows_per_kv_head=max(new) * (hq // hkv))
+        ws = ops.splitkv_workspace(q, d, S, cu)
+        prob = FmhaProblem("fmha_fwd_split_kv", "bf16", "group", len(lens), hq, hkv, d, d, max(new), bt.shape[1] * 16,
+                           "causal", paged=True, page=16)
+        run = lambda: ops.fmha_fwd_splitkv(q, k, v, seqlen_k=sl, block_table=bt, cu_seqlens_q=cu, max_seqlen_q=max(new),
+                                           num_splits=S, causal=True, workspace=ws)
+        return "fmha_fwd_split_kv", prob, run, None, float(sum(lens) * hkv * 2 * d * 2)
+    raise SystemExit(f"unknown workload {name}")
+
+
+def main(argv=None) -> None:
+    import argparse
+    ap = argparse.ArgumentParser(prog="python -m flashck_b200.tuner", description=__doc__.splitlines()[0])
+    ap.add_argument("--tune", nargs="+", metavar="WORKLOAD", help="small, config2, decode_small, config3, config4")
+    ap.add_argument("--mode", type=int, default=1, help="FC_TUNING_MODE for --tune (1 every valid instance, 2 hybrid)")
+    ap.add_argument("--with-ncu", action="store_true", help="tensor-pipe %% of every prefill candidate from ncu (small case)")
+    ap.add_argument("--db-dir", default=None)
+    ap.add_argument("--probe", metavar="FAMILY", help="run one candidate a few times (for a profiler) and exit")
+    ap.add_argument("--workload", default="small")
+    ap.add_argument("--params", default="{}")
+    args = ap.parse_args(argv)
+    import torch
+    from . import _lib
+    if args.probe:
+        fam = FAMILY_IDS[args.probe]
+        for k, v in json.loads(args.params).items():
+            _lib.set_instance_param(fam, k, int(v))
+        _, _, run, _, _ = _workload(args.workload if args.probe == "fmha_fwd" or args.workload != "small" else "decode_small")
+        for _ in range(4):
+            run()
+        torch.cuda.synchronize()
+        return
+    flags = TuningFlags(FC_TUNING_MODE=args.mode, FC_FORCE_PROFILING=True)
+    if args.db_dir:
+        flags.FC_TUNING_DB_DIR = args.db_dir
+    for name in args.tune or []:
+        family, prob, run, flops, nbytes = _workload(name)
+        flags.FC_TUNING_METRIC = 1 if flops else 2
+        util = None
+        if args.with_ncu and family == "fmha_fwd":
+            util = lambda inst: ncu_tensor_pipe_pct("fmha_fwd", inst.params(), "small")
+        tn = Tuner(flags=flags, utilisation=util)
+        best = tn.tune(family, prob, run, flops, nbytes)
+        print(json.dumps({"workload": name, "problem": prob.name(), "winner": best, "candidates": tn.log}), flush=True)
+        del run
+        torch.cuda.empty_cache()
+
+
+if __name__ == "__main__":
+    main()
