@@ -69,5 +69,41 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return LIB
 
 
+def build_pybind(force: bool = False) -> str:
+    """Compiles ``csrc/pybind/flash_ck.cpp`` -- the pybind11 / PyTorch binding over the C++ operator API -- into
+    ``flashck_b200/flash_ck<ext suffix>`` with g++, linked against ``libflashck_b200.so`` (found at run time next to the
+    module) and the torch libraries of this interpreter."""
+    import sysconfig
+
+    import torch
+    from torch.utils import cpp_extension as ce
+    src = os.path.join(CSRC, "pybind", "flash_ck.cpp")
+    out = os.path.join(HERE, "flash_ck" + sysconfig.get_config_var("EXT_SUFFIX"))
+    lib = build()
+    deps = [src, lib, os.path.join(HERE, "..", "include", "flashck", "fmha", "fmha_fwd.h"),
+            os.path.join(HERE, "..", "include", "flashck_b200.h")]
+    if not force and os.path.exists(out) and os.path.getmtime(out) >= _newest(deps):
+        return out
+    gxx = os.environ.get("CXX") or shutil.which("g++")
+    if not gxx:
+        raise RuntimeError("g++ not found; set CXX")
+    cuda_home = os.environ.get("CUDA_HOME") or os.path.dirname(os.path.dirname(_nvcc()))
+    torch_lib = os.path.join(os.path.dirname(torch.__file__), "lib")
+    cmd = [gxx, "-O2", "-std=c++17", "-shared", "-fPIC", "-fvisibility=hidden", "-Wno-attributes",
+           f"-D_GLIBCXX_USE_CXX11_ABI={int(torch._C._GLIBCXX_USE_CXX11_ABI)}", "-DTORCH_EXTENSION_NAME=flash_ck",
+           "-DTORCH_API_INCLUDE_EXTENSION_H"]
+    for inc in ce.include_paths() + [sysconfig.get_paths()["include"], os.path.join(cuda_home, "include"),
+                                     os.path.join(HERE, "..", "include")]:
+        cmd += ["-isystem" if "torch" in inc or "cuda" in inc else "-I", inc]
+    cmd += [src, "-o", out, "-L", torch_lib, "-ltorch", "-ltorch_cpu", "-lc10", "-lc10_cuda", "-ltorch_python",
+            "-L", HERE, "-l:libflashck_b200.so", f"-Wl,-rpath,{torch_lib}", "-Wl,-rpath,$ORIGIN"]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"g++ failed for {src}:\n{r.stdout}\n{r.stderr[-6000:]}")
+    return out
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    if "--no-pybind" not in sys.argv:
+        print(build_pybind(force="--force" in sys.argv))

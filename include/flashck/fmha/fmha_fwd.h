@@ -76,6 +76,62 @@ T* fmha_fwd_bias(T* q, T* k, T* v, const void* bias, BiasEnum bias_enum, int bia
     return o;
 }
 
+// Varlen (group mode) forward attention on packed tokens: q [total_q, hq, d], k / v [total_k, hkv, d|dv], seqstart_*
+// int64 [batch + 1].  The name the reference's test suite gives the operation (tests/pytorch/fmha/
+// test_fmha_fwd_var_len.py); same C symbol as fmha_fwd.  Returns `o`.
+template <typename T>
+T* fmha_fwd_varlen(T* q, T* k, T* v, T* o, float* lse, int64_t* seqstart_q, int64_t* seqstart_k, int64_t batch,
+                   int64_t total_q, int64_t total_k, int64_t q_num_heads, int64_t kv_num_heads, int64_t qk_head_dim,
+                   int64_t v_head_dim, int64_t max_seqlen_q, float scale = 0.f, std::array<int64_t, 2> window_size = {-1, -1},
+                   GenericAttentionMaskEnum mask = GenericAttentionMaskEnum::NO_MASK, void* stream = nullptr,
+                   int dtype = detail::dtype_code<T>()) {
+    if (seqstart_q == nullptr || seqstart_k == nullptr) throw std::runtime_error("fmha_fwd_varlen: seqstart arrays are required");
+    return fmha_fwd<T>(q, k, v, o, lse, seqstart_q, seqstart_k, nullptr, batch, total_q, total_k, q_num_heads, kv_num_heads,
+                       qk_head_dim, v_head_dim, max_seqlen_q, scale, window_size, mask, stream, dtype);
+}
+
+// Varlen prefill over an SGLang-style page table (fmha_fwd_batch_prefill): K/V pools [num_total_pages, page, hkv, d|dv],
+// kv_indptr int32 [batch + 1], kv_page_indices int32, kv_last_page_len int32 [batch]; `alibi_slopes` (fp32, rank 0 =
+// [1,hq], 1 = [batch,hq]) or nullptr.  Returns `o`.
+template <typename T>
+T* fmha_batch_prefill(T* q, T* k_pool, T* v_pool, T* o, float* lse, int64_t* seqstart_q, int32_t* kv_indptr,
+                      int32_t* kv_page_indices, int32_t* kv_last_page_len, int64_t batch, int64_t total_q,
+                      int64_t q_num_heads, int64_t kv_num_heads, int64_t qk_head_dim, int64_t v_head_dim,
+                      int64_t max_seqlen_q, int64_t num_total_pages, int64_t page_block_size, float scale = 0.f,
+                      std::array<int64_t, 2> window_size = {-1, 0},
+                      GenericAttentionMaskEnum mask = GenericAttentionMaskEnum::MASK_FROM_BOTTOM_RIGHT,
+                      const float* alibi_slopes = nullptr, int alibi_rank = 0, void* stream = nullptr,
+                      int dtype = detail::dtype_code<T>()) {
+    detail::check(FmhaFwdBatchPrefillEx(q, k_pool, v_pool, const_cast<float*>(alibi_slopes), o, seqstart_q, kv_indptr,
+                                        kv_page_indices, kv_last_page_len, batch, total_q, q_num_heads, kv_num_heads,
+                                        qk_head_dim, v_head_dim, max_seqlen_q, num_total_pages, page_block_size, scale,
+                                        window_size[0], window_size[1], static_cast<uint32_t>(mask), stream, lse, dtype,
+                                        alibi_slopes ? 2 : 0, alibi_rank),
+                  "fmha_batch_prefill");
+    return o;
+}
+
+// Prefill reading K/V through a block table (fmha_fwd_paged_kv_prefill): pools [num_pool_pages, page, hkv, d|dv],
+// block_table int32 [batch, pages_per_seq], seqlen_k int32 [batch]; q in batch mode or packed with seqstart_q.
+// Returns `o`.
+template <typename T>
+T* fmha_fwd_paged_kv_prefill(T* q, T* k_pool, T* v_pool, T* o, float* lse, int64_t* seqstart_q, int32_t* seqlen_k,
+                             int32_t* block_table, int64_t* cache_batch_idx, int64_t batch, int64_t seqlen_q,
+                             int64_t q_num_heads, int64_t kv_num_heads, int64_t qk_head_dim, int64_t v_head_dim,
+                             int64_t max_seqlen_q, int64_t pages_per_seq, int64_t num_pool_pages, int64_t page_block_size,
+                             float scale = 0.f, std::array<int64_t, 2> window_size = {-1, 0},
+                             GenericAttentionMaskEnum mask = GenericAttentionMaskEnum::MASK_FROM_BOTTOM_RIGHT,
+                             const float* alibi_slopes = nullptr, int alibi_rank = 0, void* stream = nullptr,
+                             int dtype = detail::dtype_code<T>()) {
+    detail::check(FmhaFwdPagedKVPrefillEx(q, k_pool, v_pool, const_cast<float*>(alibi_slopes), o, seqstart_q, seqlen_k,
+                                          block_table, cache_batch_idx, batch, seqlen_q, q_num_heads, kv_num_heads,
+                                          qk_head_dim, v_head_dim, max_seqlen_q, batch * pages_per_seq, page_block_size,
+                                          scale, window_size[0], window_size[1], static_cast<uint32_t>(mask), stream, lse,
+                                          dtype, alibi_slopes ? 2 : 0, alibi_rank, num_pool_pages),
+                  "fmha_fwd_paged_kv_prefill");
+    return o;
+}
+
 // Split-KV attention over a contiguous or paged cache followed by the combine.  Workspaces are caller-owned:
 // lse_acc [b,hq,num_splits,sq], o_acc [b,hq,num_splits,sq,dv] fp32.  Returns `o`.
 template <typename T>
@@ -86,11 +142,13 @@ T* fmha_fwd_splitkv(T* q, T* k_cache, T* v_cache, T* o, float* lse, float* lse_a
                     int64_t max_num_page_blocks, int64_t page_block_size, float scale = 0.f,
                     std::array<int64_t, 2> window_size = {-1, -1},
                     GenericAttentionMaskEnum mask = GenericAttentionMaskEnum::NO_MASK, void* stream = nullptr,
-                    int dtype = detail::dtype_code<T>()) {
-    detail::check(FmhaFwdSplitKV(q, k_cache, v_cache, nullptr, lse_acc, o_acc, seqstart_q, seqstart_k, seqlen_k,
-                                 block_table, cache_batch_idx, batch, seqlen_q, seqlen_k_max, q_num_heads, kv_num_heads,
-                                 qk_head_dim, v_head_dim, max_seqlen_q, num_splits, max_num_page_blocks, page_block_size,
-                                 scale, window_size[0], window_size[1], static_cast<uint32_t>(mask), stream, dtype),
+                    int dtype = detail::dtype_code<T>(), int64_t num_pool_pages = 0) {
+    // num_pool_pages: pages the pools really hold (0 = max_num_page_blocks, the reference's pool size)
+    detail::check(FmhaFwdSplitKVEx(q, k_cache, v_cache, nullptr, lse_acc, o_acc, seqstart_q, seqstart_k, seqlen_k,
+                                   block_table, cache_batch_idx, batch, seqlen_q, seqlen_k_max, q_num_heads, kv_num_heads,
+                                   qk_head_dim, v_head_dim, max_seqlen_q, num_splits, max_num_page_blocks, page_block_size,
+                                   scale, window_size[0], window_size[1], static_cast<uint32_t>(mask), stream, dtype, 0, 0,
+                                   num_pool_pages > 0 ? num_pool_pages : max_num_page_blocks),
                   "fmha_fwd_splitkv");
     detail::check(FmhaFwdSplitKVCombine(lse_acc, o_acc, o, seqstart_q, batch, seqlen_q, q_num_heads, v_head_dim,
                                         max_seqlen_q, num_splits, stream, lse, dtype),
@@ -128,21 +186,25 @@ public:
         : mode_(mode), q_num_heads_(q_num_heads), kv_num_heads_(kv_num_heads), qk_head_dim_(qk_head_dim),
           v_head_dim_(v_head_dim), scale_(scale), bias_enum_(bias_enum), window_size_(window_size),
           mask_enum_(mask_enum) {
-        if (bias_enum != BiasEnum::NO_BIAS) throw std::runtime_error("AttentionLayer: only BiasEnum::NO_BIAS is supported");
         if (mode != FmhaOperationMode::Batch && mode != FmhaOperationMode::Group)
             throw std::runtime_error("fmha only supports Batch && group mode");
     }
 
     // q [batch, q_seq_len, q_num_heads, qk_head_dim] (group mode: packed [total_q, ...] with q_seq_len = total_q);
-    // seqstart_q / seqstart_k [batch+1] and seqlen_k [batch] only in group mode.  `out` receives O; returns it.
+    // seqstart_q / seqstart_k [batch+1] and seqlen_k [batch] only in group mode.  `bias` is read as the layer's
+    // bias_enum says: ELEMENTWISE_BIAS -> values of type T, bias_rank_info 0 = [1,1,sq,sk], 1 = [1,hq,sq,sk],
+    // 2 = [b,hq,sq,sk]; ALIBI -> fp32 slopes, 0 = [1,hq], 1 = [b,hq].  `out` receives O; returns it.
     T* operator()(T* q, T* k, T* v, T* out, int64_t batch, int64_t q_seq_len, int64_t kv_seq_len, int64_t max_seqlen_q,
-                  T* bias = nullptr, int64_t* seqstart_q = nullptr, int64_t* seqstart_k = nullptr,
-                  int64_t* seqlen_k = nullptr, float* lse = nullptr, void* stream = nullptr) const {
-        if (bias != nullptr) throw std::runtime_error("AttentionLayer: bias is not supported");
+                  const void* bias = nullptr, int64_t* seqstart_q = nullptr, int64_t* seqstart_k = nullptr,
+                  int64_t* seqlen_k = nullptr, float* lse = nullptr, void* stream = nullptr, int bias_rank_info = 0,
+                  float logits_soft_cap = 0.f, int dtype = detail::dtype_code<T>()) const {
+        if ((bias != nullptr) != (bias_enum_ != BiasEnum::NO_BIAS))
+            throw std::runtime_error("AttentionLayer: a bias buffer goes with a bias_enum other than NO_BIAS, and only with one");
         const bool group = mode_ == FmhaOperationMode::Group;
-        return naive::fmha_fwd<T>(q, k, v, out, lse, group ? seqstart_q : nullptr, group ? seqstart_k : nullptr,
-                                  group ? seqlen_k : nullptr, batch, q_seq_len, kv_seq_len, q_num_heads_, kv_num_heads_,
-                                  qk_head_dim_, v_head_dim_, max_seqlen_q, scale_, window_size_, mask_enum_, stream);
+        return naive::fmha_fwd_bias<T>(q, k, v, bias, bias_enum_, bias_rank_info, logits_soft_cap, out, lse,
+                                       group ? seqstart_q : nullptr, group ? seqstart_k : nullptr, group ? seqlen_k : nullptr,
+                                       batch, q_seq_len, kv_seq_len, q_num_heads_, kv_num_heads_, qk_head_dim_, v_head_dim_,
+                                       max_seqlen_q, scale_, window_size_, mask_enum_, stream, dtype);
     }
 
     FmhaOperationMode mode_;

@@ -18,10 +18,20 @@ int main() {
     } catch (const std::runtime_error& e) {
         if (!std::strstr(e.what(), "multiple")) { std::printf("unexpected message: %s\n", e.what()); ++failures; }
     }
-    try {
+    try {  // a layer built for ALiBi wants its slopes
         AttentionLayer<_Float16> layer(FmhaOperationMode::Batch, 2, 2, 64, 64, 1.f, BiasEnum::ALIBI);
+        _Float16 dummy[8] = {0};
+        layer(dummy, dummy, dummy, dummy, 1, 1, 1, 1);
         ++failures;
     } catch (const std::runtime_error&) {}
+    try {  // the paged wrappers reach the library too (refused: 3 q heads over 2 kv heads)
+        bf16 dummy[8] = {0};
+        naive::fmha_batch_prefill<bf16>(dummy, dummy, dummy, dummy, nullptr, nullptr, nullptr, nullptr, nullptr, 1, 1, 3, 2,
+                                        128, 128, 1, 1, 16);
+        ++failures;
+    } catch (const std::runtime_error& e) {
+        if (!std::strstr(e.what(), "multiple")) { std::printf("unexpected message: %s\n", e.what()); ++failures; }
+    }
     try {  // a bias kind without a bias buffer is refused before any CUDA work
         bf16 dummy[8] = {0};
         naive::fmha_fwd_bias<bf16>(dummy, dummy, dummy, nullptr, BiasEnum::ELEMENTWISE_BIAS, 0, 0.f, dummy, nullptr, nullptr,
