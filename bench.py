@@ -535,6 +535,32 @@ def main():
         }
         del wp
 
+    # ------------------------------------------------------------------ the headline prefill on 8-bit operands (next row)
+    if not args.no_decode:
+        (q8, dq), (k8, dk), (v8, dv8) = (ops.quantize_fp8(w[n], torch.float8_e4m3fn) for n in ("q", "k", "v"))
+        sc_s, sc_p = dq * dk / D ** 0.5, 256.0
+
+        def fp8_step():
+            return ops.fmha_fwd_fp8(q8, k8, v8, scale_s=sc_s, scale_p=sc_p, scale_o=dv8 / sc_p, cu_seqlens_q=w["cu"],
+                                    cu_seqlens_k=w["cu"], max_seqlen_q=w["max_len"], causal=True, out_dtype=torch.bfloat16,
+                                    return_lse=True)
+
+        ms_8 = max_over_ranks(time_steps(fp8_step, max(3, steps // 4), 3, barrier))
+        n8 = max(3, steps // 4)
+        t8 = w["flops"] * n8 / (ms_8 * 1e-3) / 1e12
+        extra["prefill_fp8"] = {
+            "metric": "prefill_fmha_fp8_tflops", "value": total_flops * n8 / (ms_8 * 1e-3) / 1e12, "unit": "TFLOP/s",
+            "ms_per_step": ms_8 / n8, "steps": n8, "dtype": "f8e4m3",
+            "config": {"workload": "the headline prefill with Q, K, V quantised to E4M3 (static per-tensor scales), P rounded "
+                                   "to E4M3, O in bf16 (FmhaFwdFp8); runs on the general mma.sync instance, which widens "
+                                   "the 8-bit operands to halves in shared memory"},
+            "roofline": {"bound": "tensor", "achieved": t8, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                         "frac": t8 / peaks["bf16_tflops"], "traffic": None,
+                         "peak_source": peaks["source"] + " (burst bf16 GEMM; no 8-bit peak was measured on this pool)"},
+            "gpu_launches": n8,
+        }
+        del q8, k8, v8
+
     # ------------------------------------------------------------------ decode (config 3)
     if not args.no_decode:
         if args.small:

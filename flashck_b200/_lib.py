@@ -12,7 +12,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libflashck_b200.so")
 _LIB: Optional[ctypes.CDLL] = None
 
-FLOAT16, BFLOAT16 = 3, 4  # flashck::DataType values (core/utils/dtype.h:16-28)
+FLOAT8, BFLOAT8, FLOAT16, BFLOAT16 = 1, 2, 3, 4  # flashck::DataType values (core/utils/dtype.h:16-28)
 
 _P, _I64, _F, _U32, _I = ctypes.c_void_p, ctypes.c_int64, ctypes.c_float, ctypes.c_uint32, ctypes.c_int
 
@@ -23,6 +23,7 @@ SIGNATURES = {
     "FlashckDeviceStatus": ([ctypes.POINTER(ctypes.c_int)], _I),
     "FmhaFwd": ([_P] * 8 + [_I64] * 8 + [_F, _I64, _I64, _U32, _P, _P, _I], _I),
     "FmhaFwdBias": ([_P] * 8 + [_I64] * 8 + [_F, _I64, _I64, _U32, _P, _P, _I, _I, _I, _F], _I),
+    "FmhaFwdFp8": ([_P] * 6 + [_I64] * 8 + [_F, _F, _F, _I64, _I64, _U32, _P, _P, _I, _I], _I),
     "FmhaFwdBatchPrefill": ([_P] * 9 + [_I64] * 9 + [_F, _I64, _I64, _U32, _P, _P, _I], _I),
     "FmhaFwdPagedKVPrefill": ([_P] * 9 + [_I64] * 9 + [_F, _I64, _I64, _U32, _P, _P, _I], _I),
     "FmhaFwdSplitKV": ([_P] * 11 + [_I64] * 11 + [_F, _I64, _I64, _U32, _P, _I], _I),

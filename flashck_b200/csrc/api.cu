@@ -184,11 +184,45 @@ int FmhaFwd(void* q, void* k, void* v, void* bias, void* o, int64_t* q_seq_start
                        bias ? (int)g_bias_enum.load() : 0, (int)g_bias_rank_info.load(), 0.f);
 }
 
+int FmhaFwdFp8(void* q, void* k, void* v, void* o, int64_t* q_seq_start, int64_t* k_seq_start, int64_t batch,
+               int64_t q_seq_len, int64_t kv_seq_len, int64_t hq, int64_t hkv, int64_t d, int64_t dv, int64_t q_max_seq_len,
+               float scale_s, float scale_p, float scale_o, int64_t window_left, int64_t window_right, uint32_t mask_type,
+               void* stream, void* lse, int dtype, int o_dtype) {
+    FCK_REQUIRE(dtype == FLASHCK_DTYPE_FLOAT8 || dtype == FLASHCK_DTYPE_BFLOAT8, FLASHCK_ERR_UNSUPPORTED,
+                "FmhaFwdFp8: dtype must be 1 (float8 e4m3) or 2 (bfloat8 e5m2), got %d", dtype);
+    FCK_REQUIRE(o_dtype >= FLASHCK_DTYPE_FLOAT8 && o_dtype <= FLASHCK_DTYPE_BFLOAT16, FLASHCK_ERR_UNSUPPORTED,
+                "FmhaFwdFp8: o_dtype must be 1, 2, 3 or 4, got %d", o_dtype);
+    FCK_REQUIRE(hq > 0 && hkv > 0 && hq % hkv == 0, FLASHCK_ERR_INVALID_ARGUMENT,
+                "FmhaFwdFp8: nhead_q (%lld) must be a positive multiple of nhead_k (%lld)", (long long)hq, (long long)hkv);
+    FCK_REQUIRE(q && k && v && o, FLASHCK_ERR_INVALID_ARGUMENT, "FmhaFwdFp8: q, k, v and o must not be null");
+    FCK_REQUIRE(batch >= 0 && q_seq_len >= 0 && kv_seq_len >= 0 && d > 0 && dv > 0, FLASHCK_ERR_INVALID_ARGUMENT, "FmhaFwdFp8: bad size");
+    FCK_REQUIRE(mask_type <= 3, FLASHCK_ERR_INVALID_ARGUMENT, "FmhaFwdFp8: mask_type must be 0..3");
+    FCK_REQUIRE((q_seq_start == nullptr) == (k_seq_start == nullptr), FLASHCK_ERR_INVALID_ARGUMENT,
+                "FmhaFwdFp8: group mode needs both seqstart arrays");
+    FCK_REQUIRE(scale_p > 0.f && scale_o > 0.f && scale_s >= 0.f, FLASHCK_ERR_INVALID_ARGUMENT, "FmhaFwdFp8: scales must be positive");
+    FwdParams p{};
+    p.q = q; p.k = k; p.v = v; p.o = o; p.lse = (float*)lse;
+    p.seqstart_q = q_seq_start; p.seqstart_k = k_seq_start;
+    p.batch = batch; p.seqlen_q = q_seq_len; p.seqlen_k = kv_seq_len; p.hq = hq; p.hkv = hkv; p.d = d; p.dv = dv;
+    p.total_q = q_seq_len;
+    p.max_seqlen_q = q_seq_start ? (q_max_seq_len > 0 ? q_max_seq_len : q_seq_len) : q_seq_len;
+    p.scale = resolve_scale(scale_s, d);
+    p.mask_type = (int)mask_type; p.wl = window_left; p.wr = window_right; p.dtype = dtype;
+    p.scale_p = scale_p; p.scale_o = scale_o; p.out_dtype = o_dtype;
+    return launch_fwd_generic(p, (cudaStream_t)stream);  // (the tcgen05 instance is built for 16-bit operands)
+}
+
 int FmhaFwdBias(void* q, void* k, void* v, void* bias, void* o, int64_t* q_seq_start, int64_t* k_seq_start,
                 int64_t* k_seq_len, int64_t batch, int64_t q_seq_len, int64_t kv_seq_len, int64_t hq, int64_t hkv,
                 int64_t d, int64_t dv, int64_t q_max_seq_len, float scale, int64_t window_left, int64_t window_right,
                 uint32_t mask_type, void* stream, void* lse, int dtype, int bias_enum, int bias_rank_info,
                 float logits_soft_cap) {
+    if (dtype == FLASHCK_DTYPE_FLOAT8 || dtype == FLASHCK_DTYPE_BFLOAT8) {
+        FCK_REQUIRE(bias_enum == 0 && logits_soft_cap == 0.f && k_seq_len == nullptr, FLASHCK_ERR_UNSUPPORTED,
+                    "FmhaFwd: the 8-bit element types take no bias, soft cap or k_seq_len array");
+        return FmhaFwdFp8(q, k, v, o, q_seq_start, k_seq_start, batch, q_seq_len, kv_seq_len, hq, hkv, d, dv, q_max_seq_len,
+                          scale, 1.f, 1.f, window_left, window_right, mask_type, stream, lse, dtype, dtype);
+    }
     int rc = check_common("FmhaFwd", dtype, hq, hkv, d, dv, nullptr);
     if (rc) return rc;
     FCK_REQUIRE(bias_enum >= 0 && bias_enum <= 2, FLASHCK_ERR_INVALID_ARGUMENT,

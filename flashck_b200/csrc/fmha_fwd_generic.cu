@@ -11,6 +11,10 @@
 // mma.sync m16n8k16; fp32 online softmax in base 2 with quad-shuffle row reductions; P is rounded to the
 // element dtype before PV and O is accumulated in fp32, as the reference's FmhaFwdTypeConfig prescribes
 // (attention_kernels/fmha_common_jinja.h:120-155).  K/V tiles that the mask hides completely are skipped.
+#include <cuda_fp8.h>
+
+#include <type_traits>
+
 #include "kernels.h"
 
 namespace fck {
@@ -44,7 +48,32 @@ struct FwdDev {
     int64_t bias_sq;       // rows of one head's bias plane
     float soft_cap;        // 0 = off
     float scale;
+    // 8-bit instances (template parameter F8): P is stretched by scale_p before it is rounded to 8 bits, the accumulator
+    // is taken to the range of O by scale_o (attention_kernels/fmha_fwd/fmha_fwd_jinja.h:326-328); O leaves as out_dtype
+    float scale_p, scale_o;
+    int out_dtype;
 };
+
+// 8 consecutive 8-bit floats (one uint2) as 8 halves (one uint4): exact, every E4M3 / E5M2 value is a half.
+template <int F8>
+__device__ __forceinline__ uint4 f8x8_to_half8(uint2 v) {
+    constexpr __nv_fp8_interpretation_t kind = F8 == 1 ? __NV_E4M3 : __NV_E5M2;
+    uint4 r;
+    __half2_raw h;
+    h = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(v.x & 0xffffu), kind); r.x = (uint32_t)h.x | ((uint32_t)h.y << 16);
+    h = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(v.x >> 16), kind);     r.y = (uint32_t)h.x | ((uint32_t)h.y << 16);
+    h = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(v.y & 0xffffu), kind); r.z = (uint32_t)h.x | ((uint32_t)h.y << 16);
+    h = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(v.y >> 16), kind);     r.w = (uint32_t)h.x | ((uint32_t)h.y << 16);
+    return r;
+}
+// Two probabilities rounded to the 8-bit type (nearest even, saturating) and handed to the MMA as the halves they equal.
+template <int F8>
+__device__ __forceinline__ uint32_t quantize_p2(float a, float b) {
+    constexpr __nv_fp8_interpretation_t kind = F8 == 1 ? __NV_E4M3 : __NV_E5M2;
+    const __nv_fp8x2_storage_t q = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, kind);
+    const __half2_raw h = __nv_cvt_fp8x2_to_halfraw2(q, kind);
+    return (uint32_t)h.x | ((uint32_t)h.y << 16);
+}
 
 // Row-major [rows][D] 16-bit tile; 16-byte chunk index XORed with (row & 7).
 template <int D>
@@ -55,9 +84,15 @@ __device__ __forceinline__ uint32_t swz(int row, int chunk) {
 // EXTRA: the instance adds an elementwise bias or ALiBi to the scaled scores and/or soft-caps them (the reference
 // compiles these as separate kernel instances too: bias_enum and has_logits_soft_cap are part of the instance name,
 // core/profiling/attention/fmha_fwd/fmha_fwd_problem.h:59-64).
-template <typename T, int D, bool EXTRA>
+// F8: 0 = Q/K/V/O are stored as T.  1 (E4M3) / 2 (E5M2): the 8-bit instances of the reference's FmhaFwdTypeConfig<fp8_t /
+// bf8_t> (attention_kernels/fmha_common_jinja.h:157-187): Q, K, V arrive as 8-bit floats and are widened to halves on
+// their way into shared memory (exact), so the two GEMMs multiply exactly the 8-bit values with fp32 accumulation; P is
+// rounded to the 8-bit type before the second GEMM; T must be __half.  (A tensor-core instance that keeps the operands
+// at 8 bits moves half the shared-memory bytes and doubles the MMA rate; this one covers the arithmetic.)
+template <typename T, int D, bool EXTRA, int F8 = 0>
 __global__ void __launch_bounds__(NWARP * 32)
 fmha_fwd_generic_kernel(const FwdDev p) {
+    static_assert(F8 == 0 || std::is_same<T, __half>::value, "the 8-bit instances compute in half precision");
     constexpr int CH = D / 8;                    // 16-byte chunks per row
     constexpr int TILE = BN * D * 2;             // bytes of one K or V tile
     extern __shared__ __align__(128) uint8_t smem[];
@@ -117,6 +152,12 @@ fmha_fwd_generic_kernel(const FwdDev p) {
         for (int e = tid; e < BM * CH; e += NWARP * 32) {
             const int r = e / CH, c = e % CH;
             const bool ok = m0 + r < sq;
+            if constexpr (F8 != 0) {
+                const uint8_t* src = (const uint8_t*)p.q + ((q0 + m0 + (ok ? r : 0)) * p.hq + h) * D + c * 8;
+                *reinterpret_cast<uint4*>(sQ + swz<D>(r, c)) =
+                    ok ? f8x8_to_half8<F8>(*reinterpret_cast<const uint2*>(src)) : make_uint4(0u, 0u, 0u, 0u);
+                continue;
+            }
             const T* src = (const T*)p.q + ((q0 + m0 + (ok ? r : 0)) * p.hq + h) * D + c * 8;
             cp_async_16(smem_u32(sQ) + swz<D>(r, c), src, ok);
         }
@@ -129,6 +170,14 @@ fmha_fwd_generic_kernel(const FwdDev p) {
             const bool ok = j < sk;
             const int64_t row = ok ? token_row(j) : 0;
             const size_t off = ((size_t)row * p.hkv + kh) * D + c * 8;
+            if constexpr (F8 != 0) {  // (synchronous: the widening happens in registers)
+                const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+                *reinterpret_cast<uint4*>(sK + buf * TILE + swz<D>(r, c)) =
+                    ok ? f8x8_to_half8<F8>(*reinterpret_cast<const uint2*>((const uint8_t*)p.k + off)) : zero;
+                *reinterpret_cast<uint4*>(sV + buf * TILE + swz<D>(r, c)) =
+                    ok ? f8x8_to_half8<F8>(*reinterpret_cast<const uint2*>((const uint8_t*)p.v + off)) : zero;
+                continue;
+            }
             cp_async_16(smem_u32(sK) + buf * TILE + swz<D>(r, c), (const T*)p.k + off, ok);
             cp_async_16(smem_u32(sV) + buf * TILE + swz<D>(r, c), (const T*)p.v + off, ok);
         }
@@ -263,10 +312,17 @@ fmha_fwd_generic_kernel(const FwdDev p) {
 #pragma unroll
         for (int kk = 0; kk < BN / 16; ++kk) {
             uint32_t pa[4];
-            pa[0] = Elem<T>::pack2(s[2 * kk][0], s[2 * kk][1]);
-            pa[1] = Elem<T>::pack2(s[2 * kk][2], s[2 * kk][3]);
-            pa[2] = Elem<T>::pack2(s[2 * kk + 1][0], s[2 * kk + 1][1]);
-            pa[3] = Elem<T>::pack2(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+            if constexpr (F8 != 0) {
+                pa[0] = quantize_p2<F8>(s[2 * kk][0] * p.scale_p, s[2 * kk][1] * p.scale_p);
+                pa[1] = quantize_p2<F8>(s[2 * kk][2] * p.scale_p, s[2 * kk][3] * p.scale_p);
+                pa[2] = quantize_p2<F8>(s[2 * kk + 1][0] * p.scale_p, s[2 * kk + 1][1] * p.scale_p);
+                pa[3] = quantize_p2<F8>(s[2 * kk + 1][2] * p.scale_p, s[2 * kk + 1][3] * p.scale_p);
+            } else {
+                pa[0] = Elem<T>::pack2(s[2 * kk][0], s[2 * kk][1]);
+                pa[1] = Elem<T>::pack2(s[2 * kk][2], s[2 * kk][3]);
+                pa[2] = Elem<T>::pack2(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+                pa[3] = Elem<T>::pack2(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+            }
 #pragma unroll
             for (int j = 0; j < D / 16; ++j) {
                 const int r = kk * 16 + (lm & 1) * 8 + lr;
@@ -287,6 +343,26 @@ fmha_fwd_generic_kernel(const FwdDev p) {
     l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
     const float inv0 = l0 > 0.f ? 1.f / l0 : 0.f, inv1 = l1 > 0.f ? 1.f / l1 : 0.f;
+    if constexpr (F8 != 0) {
+        // O = scale_o * acc / l in the output type the call names: 8-bit (saturating) or 16-bit; each thread stores its
+        // two neighbouring columns of its two rows
+        const float f0 = inv0 * p.scale_o, f1 = inv1 * p.scale_o;
+        auto put = [&](int row, int col, float a, float b) {
+            const int64_t idx = ((q0 + row) * p.hq + h) * D + col;
+            if (p.out_dtype == FLASHCK_DTYPE_FLOAT8 || p.out_dtype == FLASHCK_DTYPE_BFLOAT8)
+                *reinterpret_cast<uint16_t*>((uint8_t*)p.o + idx) = (uint16_t)__nv_cvt_float2_to_fp8x2(
+                    make_float2(a, b), __NV_SATFINITE, p.out_dtype == FLASHCK_DTYPE_FLOAT8 ? __NV_E4M3 : __NV_E5M2);
+            else if (p.out_dtype == FLASHCK_DTYPE_BFLOAT16)
+                *reinterpret_cast<uint32_t*>((__nv_bfloat16*)p.o + idx) = Elem<__nv_bfloat16>::pack2(a, b);
+            else
+                *reinterpret_cast<uint32_t*>((__half*)p.o + idx) = Elem<__half>::pack2(a, b);
+        };
+#pragma unroll
+        for (int j = 0; j < D / 8; ++j) {
+            if (i0 < sq) put(i0, j * 8 + qlane * 2, o[j][0] * f0, o[j][1] * f0);
+            if (i1 < sq) put(i1, j * 8 + qlane * 2, o[j][2] * f1, o[j][3] * f1);
+        }
+    } else {
     // stage the 16 x D tile of this warp in its own rows of the Q buffer, then store 16-byte vectors
     __syncwarp();
     {
@@ -304,6 +380,7 @@ fmha_fwd_generic_kernel(const FwdDev p) {
             const uint4 val = *reinterpret_cast<const uint4*>(sQ + swz<D>(r, c));
             *reinterpret_cast<uint4*>((T*)p.o + ((q0 + m0 + r) * p.hq + h) * D + c * 8) = val;
         }
+    }
     }
     if (p.lse && qlane == 0) {
         const float kLn2 = 0.6931471805599453f;
@@ -335,10 +412,30 @@ int launch_inst(const FwdParams& p, const FwdDev& dev, cudaStream_t stream) {
 
 }  // namespace
 
+template <int D, int F8>
+int launch_inst_f8(const FwdParams& p, const FwdDev& dev, cudaStream_t stream) {
+    auto kern = fmha_fwd_generic_kernel<__half, D, false, F8>;
+    const size_t smem = (size_t)(BM + 4 * BN) * D * 2;
+    static thread_local int configured_device = -1;
+    int devid = 0;
+    FCK_CUDA(cudaGetDevice(&devid));
+    if (configured_device != devid) {
+        FCK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        configured_device = devid;
+    }
+    const int mtiles = (int)((p.max_seqlen_q + BM - 1) / BM);
+    if (mtiles == 0 || p.batch == 0) return FLASHCK_OK;
+    FCK_REQUIRE(p.hq <= 65535 && p.batch <= 65535, FLASHCK_ERR_UNSUPPORTED, "fmha_fwd: nhead_q and batch must be <= 65535");
+    kern<<<dim3(mtiles, (unsigned)p.hq, (unsigned)p.batch), NWARP * 32, smem, stream>>>(dev);
+    FCK_CUDA(cudaGetLastError());
+    return FLASHCK_OK;
+}
+
 int launch_fwd_generic(const FwdParams& p, cudaStream_t stream) {
     FCK_REQUIRE(p.d == p.dv && (p.d == 64 || p.d == 128), FLASHCK_ERR_UNSUPPORTED,
                 "fmha_fwd: hdim_q == hdim_v in {64,128} required (got %lld/%lld)", (long long)p.d, (long long)p.dv);
     FwdDev dev;
+    dev.scale_p = p.scale_p; dev.scale_o = p.scale_o; dev.out_dtype = p.out_dtype;
     dev.q = p.q; dev.k = p.k; dev.v = p.v; dev.o = p.o; dev.lse = p.lse;
     dev.seqstart_q = p.seqstart_q; dev.seqstart_k = p.seqstart_k;
     dev.seqlen_k64 = p.seqlen_k64; dev.seqlen_k32 = p.seqlen_k32;
@@ -354,6 +451,13 @@ int launch_fwd_generic(const FwdParams& p, cudaStream_t stream) {
     dev.bias = p.bias; dev.bias_type = p.bias ? p.bias_type : 0; dev.bias_rank = p.bias_rank;
     dev.bias_sk = p.seqlen_k; dev.bias_sq = p.seqstart_q ? p.total_q : p.seqlen_q;
     dev.soft_cap = p.logits_soft_cap; dev.scale = p.scale;
+    if (p.dtype == FLASHCK_DTYPE_FLOAT8 || p.dtype == FLASHCK_DTYPE_BFLOAT8) {
+        FCK_REQUIRE(dev.bias_type == 0 && dev.soft_cap == 0.f, FLASHCK_ERR_UNSUPPORTED,
+                    "fmha_fwd: the 8-bit instances take no bias and no soft cap");
+        if (p.dtype == FLASHCK_DTYPE_FLOAT8)
+            return p.d == 128 ? launch_inst_f8<128, 1>(p, dev, stream) : launch_inst_f8<64, 1>(p, dev, stream);
+        return p.d == 128 ? launch_inst_f8<128, 2>(p, dev, stream) : launch_inst_f8<64, 2>(p, dev, stream);
+    }
     const bool bf16 = p.dtype == FLASHCK_DTYPE_BFLOAT16;
     if (dev.bias_type != 0 || dev.soft_cap > 0.f) {
         FCK_REQUIRE(dev.bias_type != 1 || !(p.block_table || p.kv_indptr || p.cache_batch_idx || p.seqlen_k32 || p.seqlen_k64),

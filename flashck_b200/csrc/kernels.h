@@ -102,6 +102,9 @@ struct FwdParams {
     const void* bias;
     int bias_type, bias_rank;
     float logits_soft_cap;
+    // 8-bit element types (dtype 1 / 2): static-quantisation scales of P and O, and the type O is stored in
+    float scale_p = 1.f, scale_o = 1.f;
+    int out_dtype = 0;
 };
 int launch_fwd_generic(const FwdParams& p, cudaStream_t stream);
 

@@ -24,6 +24,8 @@ from ..utils.enums import MaskEnum, RopeEnum
 __all__ = [
     "fmha_fwd",
     "fmha_fwd_var_len",
+    "fmha_fwd_fp8",
+    "quantize_fp8",
     "batch_prefill",
     "fmha_fwd_paged_kv_prefill",
     "fmha_fwd_splitkv",
@@ -190,6 +192,67 @@ def fmha_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, scale: Option
                                            hq, hkv, d, dv, sq, float(scale or 0.0), wl, wr, mt, _stream(), _ptr(lse),
                                            _dtype_code(q), bias_enum, bias_rank, float(logits_soft_cap)))
     _lib.check(rc, "FmhaFwd")
+    return (o, lse) if return_lse else o
+
+
+_F8_CODES = {torch.float8_e4m3fn: _lib.FLOAT8, torch.float8_e5m2: _lib.BFLOAT8}
+_F8_MAX = {torch.float8_e4m3fn: 448.0, torch.float8_e5m2: 57344.0}
+
+
+def quantize_fp8(x: torch.Tensor, dtype: torch.dtype = torch.float8_e4m3fn, amax: Optional[float] = None):
+    """Static per-tensor quantisation: ``(x8, descale)`` with ``x ~= x8.float() * descale``.  ``amax`` is the calibrated
+    range of the tensor (the reference's ``range_q`` / ``range_k`` / ``range_v``, fmha_fwd_jinja.h:27); by default the
+    tensor's own maximum magnitude.  Values are scaled to the type's largest finite number and rounded to nearest."""
+    fmax = _F8_MAX[dtype]
+    amax = float(amax) if amax is not None else float(x.abs().max())
+    amax = amax if amax > 0 else 1.0
+    scaled = (x.float() * (fmax / amax)).clamp(-fmax, fmax)
+    return scaled.to(dtype), amax / fmax
+
+
+def fmha_fwd_fp8(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, scale_s: float = 0.0, scale_p: float = 1.0,
+                 scale_o: float = 1.0, cu_seqlens_q: Optional[torch.Tensor] = None,
+                 cu_seqlens_k: Optional[torch.Tensor] = None, max_seqlen_q: int = 0, causal: bool = False,
+                 window_size: Sequence[int] = (-1, -1), mask_type: Optional[int] = None,
+                 out_dtype: Optional[torch.dtype] = None, return_lse: bool = False):
+    """Forward attention on 8-bit operands with static quantisation scales (C symbol ``FmhaFwdFp8``; the reference's
+    ``FmhaFwdTypeConfig<fp8_t / bf8_t>``).  q/k/v are ``torch.float8_e4m3fn`` or ``torch.float8_e5m2`` tensors, BSHD or
+    packed with ``cu_seqlens``.  ``S = scale_s * Q K^T`` (0: 1/sqrt(d)), ``P8 = round8(scale_p * p)``,
+    ``O = scale_o * (P8 V) / l`` stored as ``out_dtype`` (default: the input type; fp16 / bf16 also allowed).  With
+    tensors from :func:`quantize_fp8`: ``scale_s = softmax_scale * dq * dk``, ``scale_o = dv / (scale_p * do)``."""
+    for n, t in (("q", q), ("k", k), ("v", v)):
+        _check_cuda(n, t, getattr(q, "dtype", None))
+    code = _F8_CODES.get(q.dtype)
+    if code is None:
+        raise TypeError(f"fmha_fwd_fp8 takes float8_e4m3fn or float8_e5m2 tensors, got {q.dtype}")
+    out_dtype = out_dtype or q.dtype
+    out_code = {**_F8_CODES, torch.float16: _lib.FLOAT16, torch.bfloat16: _lib.BFLOAT16}.get(out_dtype)
+    if out_code is None:
+        raise TypeError(f"out_dtype must be an 8-bit float type, float16 or bfloat16, got {out_dtype}")
+    group = cu_seqlens_q is not None
+    if group:
+        if q.dim() != 3 or cu_seqlens_k is None:
+            raise ValueError("packed q/k/v [total, heads, hdim] need cu_seqlens_q and cu_seqlens_k")
+        cu_q, cu_k = _as_i64("cu_seqlens_q", cu_seqlens_q), _as_i64("cu_seqlens_k", cu_seqlens_k)
+        batch, (total_q, hq, d), (total_k, hkv, _) = cu_q.numel() - 1, q.shape, k.shape
+        sq, sk, max_sq = total_q, total_k, int(max_seqlen_q) or total_q
+        o_shape, lse_shape = (total_q, hq), (hq, total_q)
+    else:
+        if q.dim() != 4:
+            raise ValueError("q, k, v must be [batch, seqlen, heads, hdim]")
+        cu_q = cu_k = None
+        batch, sq, hq, d = q.shape
+        sk, hkv, max_sq = k.shape[1], k.shape[2], sq
+        o_shape, lse_shape = (batch, sq, hq), (batch, hq, sq)
+    dv = v.shape[-1]
+    mt, wl, wr = _mask(causal, window_size, mask_type)
+    o = torch.empty(o_shape + (dv,), dtype=out_dtype, device=q.device)
+    lse = torch.empty(lse_shape, dtype=torch.float32, device=q.device) if return_lse else None
+    with torch.cuda.device(q.device):
+        rc = _lib.lib().FmhaFwdFp8(_ptr(q), _ptr(k), _ptr(v), _ptr(o), _ptr(cu_q), _ptr(cu_k), batch, sq, sk, hq, hkv, d, dv,
+                                   max_sq, float(scale_s), float(scale_p), float(scale_o), wl, wr, mt, _stream(), _ptr(lse),
+                                   code, out_code)
+    _lib.check(rc, "FmhaFwdFp8")
     return (o, lse) if return_lse else o
 
 

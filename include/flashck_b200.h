@@ -42,6 +42,8 @@ extern "C" {
 #define FLASHCK_API
 #endif
 
+#define FLASHCK_DTYPE_FLOAT8 1   /* E4M3 (OCP, finite only) -- FmhaFwdFp8 and FmhaFwd */
+#define FLASHCK_DTYPE_BFLOAT8 2  /* E5M2 */
 #define FLASHCK_DTYPE_FLOAT16 3
 #define FLASHCK_DTYPE_BFLOAT16 4
 #define FLASHCK_DTYPE_FLOAT32 7 /* only as the output type of FmhaFwdSplitKVCombineStrided */
@@ -100,6 +102,26 @@ FLASHCK_API int FmhaFwdBias(void* q_buf_ptr, void* k_buf_ptr, void* v_buf_ptr, v
             int64_t v_head_dim, int64_t q_max_seq_len, float scale, int64_t window_left, int64_t window_right,
             uint32_t mask_type, void* stream, void* lse_ptr, int dtype, int bias_enum, int bias_rank_info,
             float logits_soft_cap);
+
+/*
+ * FmhaFwdFp8 -- forward attention on 8-bit operands with static quantisation scales: the reference's
+ * FmhaFwdTypeConfig<fp8_t> / <bf8_t> (attention_kernels/fmha_common_jinja.h:157-187: Q, K, V, P and O are 8-bit floats,
+ * S, softmax, O accumulator and LSE fp32) with the kernel arguments scale_s, scale_p, scale_o
+ * (attention_kernels/fmha_fwd/fmha_fwd_jinja.h:93,326-328) as call arguments.  dtype: 1 = E4M3 (FLOAT8), 2 = E5M2
+ * (BFLOAT8), the OCP formats; conversions round to nearest even and saturate.  Per row:
+ *     S = scale_s * Q K^T;  p = exp(S - max);  l = sum p;  P8 = round8(scale_p * p);  O = scale_o * (P8 V) / l
+ * so scale_s carries the softmax scale and the de-quantisation of Q and K (0 means 1/sqrt(hdim_q)), scale_p the stretch
+ * of the probabilities over the 8-bit range, scale_o = (V de-quantisation) / (scale_p * O quantisation).
+ * o_dtype: the type O is stored in -- 1 or 2 (one byte per element) or 3 / 4 (fp16 / bf16).  Batch mode or group mode
+ * (q_seq_start / k_seq_start int64 [batch+1]) on contiguous K/V; hdim 64 or 128.
+ * FmhaFwd called with dtype 1 or 2 is FmhaFwdFp8 with scale_s = scale, scale_p = scale_o = 1 and o_dtype = dtype (the
+ * constants the reference passes, fmha_fwd_jinja.h:326-328).
+ */
+FLASHCK_API int FmhaFwdFp8(void* q_buf_ptr, void* k_buf_ptr, void* v_buf_ptr, void* o_buf_ptr, int64_t* q_seq_start_ptr,
+               int64_t* k_seq_start_ptr, int64_t batch, int64_t q_seq_len, int64_t kv_seq_len, int64_t q_num_heads,
+               int64_t kv_num_heads, int64_t qk_head_dim, int64_t v_head_dim, int64_t q_max_seq_len, float scale_s,
+               float scale_p, float scale_o, int64_t window_left, int64_t window_right, uint32_t mask_type, void* stream,
+               void* lse_ptr, int dtype, int o_dtype);
 
 /*
  * FmhaFwdBatchPrefill -- varlen prefill whose K/V sit behind an SGLang-style page table.

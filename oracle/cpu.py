@@ -17,13 +17,16 @@ import torch
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _LIB: Optional[ctypes.CDLL] = None
 
-FLOAT16, BFLOAT16 = 3, 4  # core/utils/dtype.h:16-28
+FLOAT8, BFLOAT8, FLOAT16, BFLOAT16 = 1, 2, 3, 4  # core/utils/dtype.h:16-28
 
 
 def build(force: bool = False) -> str:
-    """Compile the oracle with the Makefile beside this file; returns the library path."""
+    """Compile the oracle with the Makefile beside this file (make rebuilds what is older than its source); returns
+    the library path."""
     path = os.path.join(_HERE, "liboracle.so")
-    if force or not os.path.exists(path):
+    sources = [os.path.join(_HERE, n) for n in os.listdir(_HERE) if n.endswith(".cpp") or n == "Makefile"]
+    stale = not os.path.exists(path) or os.path.getmtime(path) < max(os.path.getmtime(s) for s in sources)
+    if force or stale:
         subprocess.run(["make", "-C", _HERE], check=True, capture_output=True)
     return path
 
@@ -144,3 +147,46 @@ def fmha_fwd_appendkv(q, k_cache, knew, v_cache, vnew, seqlen_k, rotary_cos, rot
 
 def num_threads() -> int:
     return int(lib().oracle_num_threads())
+
+
+_F8 = {torch.float8_e4m3fn: FLOAT8, torch.float8_e5m2: BFLOAT8}
+_OUT = {torch.float8_e4m3fn: FLOAT8, torch.float8_e5m2: BFLOAT8, torch.float16: FLOAT16, torch.bfloat16: BFLOAT16}
+
+
+def f8_to_f32(bits: int, dtype=torch.float8_e4m3fn) -> float:
+    fn = lib().oracle_f8_to_f32
+    fn.restype = ctypes.c_float
+    return float(fn(ctypes.c_uint8(bits), ctypes.c_int(_F8[dtype])))
+
+
+def f32_to_f8(x: float, dtype=torch.float8_e4m3fn) -> int:
+    fn = lib().oracle_f32_to_f8
+    fn.restype = ctypes.c_uint8
+    return int(fn(ctypes.c_float(x), ctypes.c_int(_F8[dtype])))
+
+
+def fmha_fwd_fp8(q, k, v, *, scale_s, scale_p=1.0, scale_o=1.0, seqstart_q=None, seqstart_k=None, window=(-1, -1),
+                 mask_type=0, out_dtype=None, nthreads=0):
+    """8-bit (static-quantisation) forward attention; q/k/v are torch.float8_e4m3fn or float8_e5m2 tensors in BSHD
+    (or packed with seqstart arrays).  Returns (O in ``out_dtype`` (default: the input type), LSE fp32)."""
+    dt = _F8[q.dtype]
+    out_dtype = out_dtype or q.dtype
+    group = seqstart_q is not None
+    if group:
+        batch, sq, sk = seqstart_q.numel() - 1, 0, 0
+        total_q, hq, d = q.shape
+    else:
+        batch, sq, hq, d = q.shape
+        sk = k.shape[1]
+        total_q = batch * sq
+    hkv, dv = k.shape[-2], v.shape[-1]
+    o = torch.empty(q.shape[:-1] + (dv,), dtype=out_dtype)
+    lse = torch.empty((hq, total_q) if group else (batch, hq, sq), dtype=torch.float32)
+    rc = lib().oracle_fmha_fwd_fp8(
+        _p(q), _p(k), _p(v), _p(o), _p(lse), _p(seqstart_q), _p(seqstart_k), _i64(batch), _i64(sq), _i64(sk), _i64(hq),
+        _i64(hkv), _i64(d), _i64(dv), ctypes.c_float(scale_s), ctypes.c_float(scale_p), ctypes.c_float(scale_o),
+        _i64(window[0]), _i64(window[1]), ctypes.c_uint32(mask_type), ctypes.c_int(dt), ctypes.c_int(_OUT[out_dtype]),
+        ctypes.c_int(nthreads))
+    if rc != 0:
+        raise RuntimeError(f"oracle_fmha_fwd_fp8 failed with status {rc}")
+    return o, lse

@@ -189,3 +189,56 @@ def test_golden_fixtures():
                              block_table=cache.block_table, seqstart_q=cu, seqstart_knew=cu)
     assert np.array_equal(gen.words(q), g["q"])
     assert np.array_equal(gen.words(cache.k), g["k"]) and np.array_equal(gen.words(cache.v), g["v"])
+
+
+# ------------------------------------------------------------------------------------------------
+# 8-bit (static quantisation) forward attention
+# ------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", [torch.float8_e4m3fn, torch.float8_e5m2])
+def test_fp8_conversions_match_torch(dtype):
+    """The oracle's own E4M3 / E5M2 decode and encode (round to nearest even, saturating) against PyTorch's float8 types:
+    all 256 codes, and a sweep of magnitudes from the subnormal range to the largest finite value."""
+    codes = torch.arange(256, dtype=torch.uint8)
+    ref = codes.view(dtype).float()
+    mine = torch.tensor([oracle.f8_to_f32(int(c), dtype) for c in codes])
+    assert torch.equal(torch.nan_to_num(ref, nan=7e7), torch.nan_to_num(mine, nan=7e7))
+    fmax = 448.0 if dtype == torch.float8_e4m3fn else 57344.0
+    g = torch.Generator().manual_seed(3)
+    xs = torch.cat([torch.randn(500, generator=g) * s for s in (1e-3, 0.05, 1.0, 30.0, fmax / 3)]).clamp(-fmax, fmax)
+    want = xs.to(dtype).view(torch.uint8)
+    got = torch.tensor([oracle.f32_to_f8(float(x), dtype) for x in xs], dtype=torch.uint8)
+    assert torch.equal(got, want)
+    assert oracle.f8_to_f32(oracle.f32_to_f8(1e9, dtype), dtype) == fmax  # saturation, not infinity
+
+
+@pytest.mark.parametrize("dtype", [torch.float8_e4m3fn, torch.float8_e5m2])
+@pytest.mark.parametrize("causal", [False, True])
+def test_fp8_oracle_matches_a_torch_statement(dtype, causal):
+    """oracle_fmha_fwd_fp8 against the same algorithm written with torch ops (float8 casts for the roundings)."""
+    g = torch.Generator().manual_seed(11)
+    b, sq, sk, hq, hkv, d = 2, 33, 50, 4, 2, 64
+    q = (torch.randn(b, sq, hq, d, generator=g) * 1.5).to(dtype)
+    k = (torch.randn(b, sk, hkv, d, generator=g) * 1.5).to(dtype)
+    v = (torch.randn(b, sk, hkv, d, generator=g) * 2.0).to(dtype)
+    scale_s, scale_p, scale_o = 0.11, 16.0, 1.0 / 16.0
+    o, lse = oracle.fmha_fwd_fp8(q, k, v, scale_s=scale_s, scale_p=scale_p, scale_o=scale_o, mask_type=2 if causal else 0,
+                                 window=(-1, 0) if causal else (-1, -1), out_dtype=torch.bfloat16)
+    qf, kf, vf = q.float(), k.float().repeat_interleave(hq // hkv, dim=2), v.float().repeat_interleave(hq // hkv, dim=2)
+    s = torch.einsum("bihd,bjhd->bhij", qf, kf) * scale_s
+    if causal:
+        i, j = torch.arange(sq)[:, None], torch.arange(sk)[None, :]
+        s = s.masked_fill(j > i + sk - sq, float("-inf"))
+    m = s.max(dim=-1, keepdim=True).values
+    p = torch.exp(s - m)
+    l = p.sum(dim=-1)
+    p8 = (p * scale_p).to(dtype).float()
+    want = scale_o * torch.einsum("bhij,bjhd->bihd", p8, vf) / l.permute(0, 2, 1)[..., None]
+    assert torch.allclose(lse, m[..., 0] + torch.log(l), atol=1e-5)
+    assert torch.allclose(o.float(), want.to(torch.bfloat16).float(), atol=1e-2, rtol=1e-2)
+    # 8-bit output: the same values rounded to the 8-bit type
+    o8, _ = oracle.fmha_fwd_fp8(q, k, v, scale_s=scale_s, scale_p=scale_p, scale_o=scale_o, mask_type=2 if causal else 0,
+                                window=(-1, 0) if causal else (-1, -1))
+    assert o8.dtype == dtype
+    diff = (o8.float() - want).abs()
+    ulp = want.abs() * (2.0 ** -3 if dtype == torch.float8_e4m3fn else 2.0 ** -2) + 2.0 ** -9
+    assert bool((diff <= ulp).all())
