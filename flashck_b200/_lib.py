@@ -60,7 +60,17 @@ def lib() -> ctypes.CDLL:
             fn.argtypes = argtypes
             fn.restype = restype
         _LIB = handle
+        apply_logging_flag()
     return _LIB
+
+
+def apply_logging_flag() -> None:
+    """FC_TUNING_LOG (core/utils/flags.cc:229) switches on the library's note on stderr whenever a forward call leaves
+    the tcgen05 instance for the general one (the instance parameter ``log_fallback``).  No-op until the library is loaded."""
+    if _LIB is None:
+        return
+    from .utils import flags
+    _LIB.FlashckSetInstanceParam(0, b"log_fallback", 1 if flags.get_flag("FC_TUNING_LOG") else 0)
 
 
 def last_error() -> str:

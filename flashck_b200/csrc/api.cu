@@ -134,8 +134,24 @@ inline float resolve_scale(float scale, int64_t d) {
     return scale == 0.f ? 1.f / sqrtf((float)d) : scale;  // fmha_fwd_jinja.h:57-59
 }
 
+// which instance the last forward / prefill call of this process ran on: 1 tcgen05, 0 general (instance parameter
+// "last_instance" of family 0, read-only; the tests use it to pin a problem to the instance it is meant for)
+std::atomic<int64_t> g_last_fwd_instance{-1};
+std::atomic<int64_t> g_log_fallback{0};  // instance parameter "log_fallback": say on stderr why a call left the tcgen05 instance
+
 int run_fwd(const FwdParams& p, cudaStream_t stream) {
-    if (fwd_sm100_supported(p)) return launch_fwd_sm100(p, stream);
+    if (fwd_sm100_supported(p)) {
+        g_last_fwd_instance = 1;
+        return launch_fwd_sm100(p, stream);
+    }
+    g_last_fwd_instance = 0;
+    if (g_log_fallback.load())
+        fprintf(stderr,
+                "[flashck_b200] forward call on the general (mma.sync) instance: hdim %lld/%lld, batch %lld, max_seqlen_q %lld, "
+                "nhead %lld/%lld, bias_type %d, paged %d page %lld (the tcgen05 instance serves hdim 128, no elementwise bias, "
+                "batch <= 256, <= 1024 work items per SM, nhead_q <= 1023, pages of 16..128 tokens dividing 128 or multiples)\n",
+                (long long)p.d, (long long)p.dv, (long long)p.batch, (long long)p.max_seqlen_q, (long long)p.hq,
+                (long long)p.hkv, p.bias ? p.bias_type : 0, (p.block_table || p.kv_indptr) ? 1 : 0, (long long)p.page);
     return launch_fwd_generic(p, stream);
 }
 
@@ -518,6 +534,7 @@ int FlashckSetInstanceParam(int family, const char* key, int64_t value) {
         g_bias_rank_info = value;
         return FLASHCK_OK;
     }
+    if (family == 0 && !strcmp(key, "log_fallback")) { g_log_fallback = value; return FLASHCK_OK; }
     if (family == 0) rc = fwd_set_param(key, value);
     else if (family == 2) rc = split_key_of_sm100(key) ? fwd_set_param(key, value) : splitkv_set_param(key, value);
     if (rc) set_last_error("FlashckSetInstanceParam: unknown family/key %d/%s", family, key);
@@ -528,6 +545,8 @@ int FlashckGetInstanceParam(int family, const char* key, int64_t* value_out) {
     int rc = FLASHCK_ERR_INVALID_ARGUMENT;
     if (family == 0 && !strcmp(key, "bias_enum")) { *value_out = g_bias_enum; return FLASHCK_OK; }
     if (family == 0 && !strcmp(key, "bias_rank_info")) { *value_out = g_bias_rank_info; return FLASHCK_OK; }
+    if (family == 0 && !strcmp(key, "last_instance")) { *value_out = g_last_fwd_instance; return FLASHCK_OK; }
+    if (family == 0 && !strcmp(key, "log_fallback")) { *value_out = g_log_fallback; return FLASHCK_OK; }
     if (family == 0) rc = fwd_get_param(key, value_out);
     else if (family == 2) rc = split_key_of_sm100(key) ? fwd_get_param(key, value_out) : splitkv_get_param(key, value_out);
     if (rc) set_last_error("FlashckGetInstanceParam: unknown family/key %d/%s", family, key);

@@ -69,6 +69,7 @@ struct Elem<__half> {
         __half2 h = __floats2half2_rn(lo, hi);
         return *reinterpret_cast<uint32_t*>(&h);
     }
+    static __device__ __forceinline__ __half2 bcast2(float x) { return __float2half2_rn(x); }
 };
 template <>
 struct Elem<__nv_bfloat16> {
@@ -79,6 +80,7 @@ struct Elem<__nv_bfloat16> {
         __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
         return *reinterpret_cast<uint32_t*>(&h);
     }
+    static __device__ __forceinline__ __nv_bfloat162 bcast2(float x) { return __float2bfloat162_rn(x); }
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {

@@ -94,6 +94,10 @@ struct Sm100Dev {
     int num_levels;   // row blocks of the longest sequence (128 rows when heads are paired, else 256)
     int pair_heads;   // the two Q tiles of a work item are two q heads of one kv group
     float scale_log2;
+    float scale;            // EXTRA instances: the softmax scale itself
+    float soft_cap;         // EXTRA: 0 = off
+    const float* alibi;     // EXTRA: fp32 slopes [1,hq] (alibi_rank 0) or [batch,hq] (1), or nullptr
+    int alibi_rank;
     float rescale_thr;  // the running max is raised (and O rescaled) when the row max exceeds it by more than this (log2 units)
 };
 
@@ -417,7 +421,11 @@ __device__ __forceinline__ void get_item(const Ctrl* ctrl, const Sm100Dev& p, in
     else expand_item(ctrl, p, ctrl->items[rnd], it);
 }
 
-// WINDOW: the mask has a left window or a right window other than 0 (everything but no mask / causal); a separate
+// VAR bit 1 (EXTRA): the scaled scores get the reference's score additions that need no memory traffic -- a logits soft
+//          cap (cap * tanh(score / cap), core/profiling/attention/fmha_fwd/fmha_fwd_problem.h:81) and ALiBi
+//          (-slope * |i + sk - sq - j|, BiasEnum::ALIBI, fmha_library.h:124) -- applied to the score registers before
+//          the mask; an elementwise bias tensor stays on the general instance.
+// VAR bit 0 (WINDOW): the mask has a left window or a right window other than 0 (everything but no mask / causal); a separate
 // instance, so that the common masks do not carry the second bound of the visible range through the softmax loop.
 // SPLIT 1: the split-KV form described at Sm100Dev (one Q tile per item; work cut as described at kItemCostDefault).  The S
 //          columns of tile 1 are a second S buffer, its Q room a third K slot; K, V and Q have a producer warp each
@@ -430,13 +438,15 @@ __device__ __forceinline__ void get_item(const Ctrl* ctrl, const Sm100Dev& p, in
 // EXPM: how the softmax takes its exponentials.  0: one fp32 exp2 per element on the exp2 unit; 1: two per issue
 //       through the unit's packed f16x2 form (see pack_f16x2); 11, 12, 13: fp32, with 1, 2 or 3 of every 8 column pairs
 //       on a polynomial on the FMA pipe instead.
-template <typename T, int EXPM, bool WINDOW, int SPLIT>
+template <typename T, int EXPM, int VAR, int SPLIT>
 __global__ void __launch_bounds__(NTHREADS, 1)
 fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                       const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_o,
                       const Sm100Dev p) {
     extern __shared__ uint8_t smem_raw[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    constexpr bool WINDOW = (VAR & 1) != 0;  // the mask has a second bound (see above)
+    constexpr bool EXTRA = (VAR & 2) != 0;   // ALiBi and / or a logits soft cap on the scaled scores
     constexpr int NPOLY8 = EXPM >= 11 ? EXPM - 10 : 0;
     constexpr bool HEXP = EXPM == 1;
 
@@ -1006,6 +1016,10 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
 
             float m_used = -INFINITY;  // running max actually subtracted (scaled, base 2)
             float l = 0.f;
+            float slope = 0.f;
+            if constexpr (EXTRA) {
+                if (p.alibi) slope = p.alibi[(p.alibi_rank ? (int64_t)it.b * p.hq : 0) + head];
+            }
             for (int n = 0; n < Ni; ++n) {
                 // warp-uniform outcome: the loads, votes and stores below are warp-collective
                 // The split modes have one Q tile and use the other tile's S columns as a second S buffer: the QK^T of
@@ -1024,8 +1038,20 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                 for (int c = 0; c < NC / 32; ++c)
                     tmem_ld32(tSb + khalf * 64 + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&sreg[c * 32]));
                 tmem_wait_ld();
-                // mask the diagonal and tail tiles
                 const int key0 = (it.n0 + n) * BN + khalf * 64;
+                if constexpr (EXTRA) {
+                    // score additions on the raw scores, before the mask (which must leave -inf behind): the registers
+                    // then hold the finished scores in base-2 units, and the scale below becomes 1
+                    const float dist0 = (float)(row + sk - sq - key0);  // i + sk - sq - j at the first column
+#pragma unroll
+                    for (int j = 0; j < NC; ++j) {
+                        float x = __uint_as_float(sreg[j]) * p.scale;
+                        if (p.soft_cap > 0.f) x = p.soft_cap * tanhf(x / p.soft_cap);
+                        x -= slope * fabsf(dist0 - (float)j);
+                        sreg[j] = __float_as_uint(x * 1.4426950408889634f);
+                    }
+                }
+                // mask the diagonal and tail tiles
                 const bool need_mask = (key0 + NC > sk) ||
                                        (p.causal && wr >= 0 && key0 + NC - 1 > tile_first_row + shift + wr) ||
                                        (WINDOW && p.causal && wl >= 0 && key0 < tile_first_row + BM - 1 + shift - wl);
@@ -1046,7 +1072,8 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                     }
                     mx = fmaxf(max3(a0, a1, a2), a3);
                 }
-                mx *= p.scale_log2;  // scale > 0: max commutes with scaling
+                const float scale_eff = EXTRA ? 1.f : p.scale_log2;
+                mx *= scale_eff;  // scale > 0: max commutes with scaling
                 // raise the running max only on a jump of more than 2^8 (2^2 with the packed exp2); rescale O in TMEM then
                 const bool grow = mx > m_used + p.rescale_thr;
                 if (n > 0 && __any_sync(0xffffffffu, grow)) {
@@ -1073,7 +1100,7 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                 }
                 if (grow) m_used = mx;
                 const float msub = (m_used == -INFINITY) ? 0.f : m_used;
-                const float2 sc2 = make_float2(p.scale_log2, p.scale_log2), nm2 = make_float2(-msub, -msub);
+                const float2 sc2 = make_float2(scale_eff, scale_eff), nm2 = make_float2(-msub, -msub);
                 float2 psa = make_float2(0.f, 0.f), psb = make_float2(0.f, 0.f);
                 // P = 2^(S * scale - max) for the 128 columns of the row, 64 at a time.  NPOLY8 of every 8 column
                 // pairs take the polynomial; tiles with masked (-inf) entries use the exp2 unit only, which returns
@@ -1271,7 +1298,7 @@ int make_map_o(CUtensorMap* map, const void* base, int dtype, int64_t rows, int6
     return FLASHCK_OK;
 }
 
-template <typename T, int EXPM, bool WINDOW, int SPLIT>
+template <typename T, int EXPM, int VAR, int SPLIT>
 int launch_t(const FwdParams& p, const Sm100Dev& dev, cudaStream_t stream) {
     const int64_t rows_q = p.seqstart_q ? p.total_q : p.batch * p.seqlen_q;
     const bool paged = p.block_table || p.kv_indptr;
@@ -1286,7 +1313,7 @@ int launch_t(const FwdParams& p, const Sm100Dev& dev, cudaStream_t stream) {
     if ((rc = make_map_3d(&mk, p.k, p.dtype, rows_k, p.hkv, box_k))) return rc;
     if ((rc = make_map_3d(&mv, p.v, p.dtype, rows_k, p.hkv, box_k))) return rc;
     if ((rc = make_map_o(&mo, p.o, p.dtype, rows_q, p.hq))) return rc;
-    auto kern = fmha_fwd_sm100_kernel<T, EXPM, WINDOW, SPLIT>;
+    auto kern = fmha_fwd_sm100_kernel<T, EXPM, VAR, SPLIT>;
     const size_t smem = 1024 + (size_t)(2 + 2 * KV_SLOTS) * TILE_BYTES + 8 * STAGE_BYTES + sizeof(Ctrl);
     static thread_local int configured_device = -1;
     int devid = 0;
@@ -1307,7 +1334,8 @@ int launch_t(const FwdParams& p, const Sm100Dev& dev, cudaStream_t stream) {
 bool fwd_sm100_supported(const FwdParams& p) {
     if (!g_use_sm100.load()) return false;
     if (p.d != HD || p.dv != HD) return false;
-    if ((p.bias && p.bias_type != 0) || p.logits_soft_cap > 0.f) return false;  // instances of the general kernel
+    if (p.bias && p.bias_type == 1) return false;  // an elementwise bias tensor: the general instance
+    if (p.bias && p.bias_type == 2 && p.bias_rank > 1) return false;
     const bool paged = p.block_table || p.kv_indptr;
     if (paged) {
         // pages of 16 .. 128 tokens that divide a 128-key tile, or whole multiples of it
@@ -1357,20 +1385,27 @@ int launch_fwd_sm100(const FwdParams& p, cudaStream_t stream) {
     dev.scale_log2 = p.scale * 1.4426950408889634f;
     const bool bf16 = p.dtype == FLASHCK_DTYPE_BFLOAT16;
     const bool window = p.mask_type != 0 && !(p.wl < 0 && p.wr == 0);
-    const int expm = (int)g_exp_mode.load();
+    const bool extra = (p.bias && p.bias_type == 2) || p.logits_soft_cap > 0.f;
+    const int expm = extra ? 0 : (int)g_exp_mode.load();
     dev.rescale_thr = expm == 1 ? 0.01f * (float)g_rescale_half_x100.load() : kRescaleThreshold;
-#define FCK_SM100_LAUNCH(E, W) \
-    return bf16 ? launch_t<__nv_bfloat16, E, W, 0>(p, dev, stream) : launch_t<__half, E, W, 0>(p, dev, stream)
+    dev.scale = p.scale; dev.soft_cap = p.logits_soft_cap;
+    dev.alibi = (p.bias && p.bias_type == 2) ? (const float*)p.bias : nullptr; dev.alibi_rank = p.bias_rank;
+#define FCK_SM100_LAUNCH(E, V) \
+    return bf16 ? launch_t<__nv_bfloat16, E, V, 0>(p, dev, stream) : launch_t<__half, E, V, 0>(p, dev, stream)
+    if (extra) {  // (the score-addition instances take their exponentials in fp32 on the exp2 unit)
+        if (window) { FCK_SM100_LAUNCH(0, 3); }
+        FCK_SM100_LAUNCH(0, 2);
+    }
     if (window) {  // (the window instances come with the two exp2-unit forms only)
-        if (expm == 1) { FCK_SM100_LAUNCH(1, true); }
-        FCK_SM100_LAUNCH(0, true);
+        if (expm == 1) { FCK_SM100_LAUNCH(1, 1); }
+        FCK_SM100_LAUNCH(0, 1);
     }
     switch (expm) {
-        case 1: FCK_SM100_LAUNCH(1, false);
-        case 11: FCK_SM100_LAUNCH(11, false);
-        case 12: FCK_SM100_LAUNCH(12, false);
-        case 13: FCK_SM100_LAUNCH(13, false);
-        default: FCK_SM100_LAUNCH(0, false);
+        case 1: FCK_SM100_LAUNCH(1, 0);
+        case 11: FCK_SM100_LAUNCH(11, 0);
+        case 12: FCK_SM100_LAUNCH(12, 0);
+        case 13: FCK_SM100_LAUNCH(13, 0);
+        default: FCK_SM100_LAUNCH(0, 0);
     }
 #undef FCK_SM100_LAUNCH
 }
@@ -1418,7 +1453,7 @@ int launch_split_t(const SplitKVParams& p, const Sm100Dev& dev, cudaStream_t str
     const int64_t cache_rows = p.block_table ? std::max<int64_t>(p.num_pages, 1) * p.page : p.batch * p.seqlen_k_cap;
     if ((rc = make_map_3d(&mk, p.k, p.dtype, cache_rows, p.hkv, box_k))) return rc;
     if ((rc = make_map_3d(&mv, p.v, p.dtype, cache_rows, p.hkv, box_k))) return rc;
-    auto kern = fmha_fwd_sm100_kernel<T, EXPM, false, SPLIT>;
+    auto kern = fmha_fwd_sm100_kernel<T, EXPM, 0, SPLIT>;
     const size_t smem = 1024 + (size_t)(2 + 2 * KV_SLOTS) * TILE_BYTES + 8 * STAGE_BYTES + sizeof(Ctrl);
     static thread_local int configured_device = -1;
     int devid = 0;

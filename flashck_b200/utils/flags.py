@@ -101,6 +101,9 @@ def set_flag_value(name: str, value) -> None:
         raise RuntimeError(f"Failed to set flag: {name}")
     flag.value = value if isinstance(value, flag.type) and not (flag.type is int and isinstance(value, bool)) \
         else _parse(flag.type, str(value), name)
+    if name == "FC_TUNING_LOG":  # detailed logs include the library's own: which instance a call ran on, and why
+        from .. import _lib
+        _lib.apply_logging_flag()
 
 
 def print_flag_info(name: str) -> None:

@@ -533,9 +533,48 @@ def test_fmha_fwd_bias_alibi_and_soft_cap(dtype, d, kind):
                           alibi_slopes=_cu(slopes) if slopes is not None else None, logits_soft_cap=cap)
     assert_o_close(o, o_ref, kind)
     assert_lse_close(lse, lse_ref, kind)
+    # ALiBi and the soft cap are flags of the tcgen05 softmax at hdim 128; a bias tensor and hdim 64 use the general instance
+    assert _lib.get_instance_param(0, "last_instance") == (1 if d == 128 and "bias" not in kind else 0)
     # the additions change the result (the test would pass vacuously if they were dropped on both sides)
     o_plain, _ = oracle.fmha_fwd(q, k, v, mask_type=2, window=(-1, 0))
     assert (o_plain.float() - o_ref.float()).abs().max() > 0.05
+
+
+@pytest.mark.parametrize("window", [(-1, 0), (40, 0), (-1, -1)])
+def test_fmha_fwd_alibi_and_soft_cap_together_on_the_tcgen05_instance(window):
+    """ALiBi (per-batch slopes) and a soft cap in one call, group mode over several key tiles, with causal, sliding-window
+    and no mask: the score-addition instances of the tcgen05 kernel."""
+    dtype, hq, hkv, d = torch.bfloat16, 8, 2, 128
+    lens = [300, 129, 1, 640]
+    cu = to_seqstarts(lens)
+    q, k, v = (normal_tensor((sum(lens), h, d), dtype, 30 + i) for i, h in enumerate((hq, hkv, hkv)))
+    slopes = torch.rand((len(lens), hq), generator=torch.Generator().manual_seed(9)) * 0.3
+    mt = 0 if window == (-1, -1) else 2
+    o_ref, lse_ref = oracle.fmha_fwd(q, k, v, seqstart_q=cu, seqstart_k=cu, mask_type=mt, window=window, alibi_slopes=slopes,
+                                     logits_soft_cap=15.0)
+    o, lse = ops.fmha_fwd_var_len(_cu(q), _cu(k), _cu(v), _cu(cu), _cu(cu), max(lens), mask_type=mt, window_size=window,
+                                  return_lse=True, alibi_slopes=_cu(slopes), logits_soft_cap=15.0)
+    assert _lib.get_instance_param(0, "last_instance") == 1
+    assert_o_close(o, o_ref)
+    assert_lse_close(lse, lse_ref)
+
+
+def test_fallback_to_the_general_instance_is_reported_when_logging_is_on(capfd):
+    import flashck_b200 as fck
+    q = normal_tensor((1, 40, 4, 64), torch.bfloat16, 1)
+    old = fck.get_flag_value("FC_TUNING_LOG")
+    try:
+        fck.set_flag_value("FC_TUNING_LOG", True)
+        ops.fmha_fwd(_cu(q), _cu(q), _cu(q))
+        torch.cuda.synchronize()
+        assert "general (mma.sync) instance" in capfd.readouterr().err
+        fck.set_flag_value("FC_TUNING_LOG", False)
+        ops.fmha_fwd(_cu(q), _cu(q), _cu(q))
+        torch.cuda.synchronize()
+        assert "general" not in capfd.readouterr().err
+    finally:
+        fck.set_flag_value("FC_TUNING_LOG", old)
+    assert _lib.get_instance_param(0, "last_instance") == 0
 
 
 def test_fmha_fwd_var_len_bias_plane_and_alibi():
