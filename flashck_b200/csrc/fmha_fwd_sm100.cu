@@ -48,7 +48,7 @@ constexpr int BN = 128;        // keys per K/V tile
 constexpr int HD = 128;        // head dim
 constexpr int KV_SLOTS = 2;
 constexpr int TILE_BYTES = BM * HD * 2;   // 32 KB: one Q, K or V tile
-constexpr int HALF_BYTES = TILE_BYTES / 2;  // one 64-column block (128 rows x 128 B)
+constexpr int HALF_BYTES = BM * 128;      // one 64-column block (128 rows x 128 B); hdim 128 has two, hdim 64 one
 constexpr int NTHREADS = 384;
 constexpr float kRescaleThreshold = 8.f;  // log2 units; fp32 exponentials: P stays below 2^8
 // With the packed f16x2 exp2 the threshold also bounds the rounding of the arguments (f16 spacing grows with the
@@ -57,6 +57,7 @@ constexpr float kRescaleThreshold = 8.f;  // log2 units; fp32 exponentials: P st
 std::atomic<int64_t> g_rescale_half_x100{200};
 
 std::atomic<int64_t> g_use_sm100{1};
+std::atomic<int64_t> g_use_sm100_hdim64{1};  // hdim-64 prefill on the tcgen05 instance (0: on the general one)
 // exponentials of the softmax (template parameter EXPM of the kernel): 0 fp32 on the exp2 unit, 1 packed f16x2 on the
 // exp2 unit, 11 / 12 / 13 fp32 with 1 / 2 / 3 of every 8 column pairs on an FMA-pipe polynomial
 // (measured on B200, BASELINE config 2, bf16: 0 -> 962 TFLOP/s; 1 -> 915 at a rescale threshold of 4 and up, 866 at 2,
@@ -180,9 +181,9 @@ template <typename T> struct UmmaFmt;
 template <> struct UmmaFmt<__half> { static constexpr uint32_t v = 0u; };
 template <> struct UmmaFmt<__nv_bfloat16> { static constexpr uint32_t v = 1u; };
 template <typename T>
-__device__ __forceinline__ constexpr uint32_t make_idesc(bool b_mn_major) {
+__device__ __forceinline__ constexpr uint32_t make_idesc(bool b_mn_major, int n = BN) {
     return (1u << 4) | (UmmaFmt<T>::v << 7) | (UmmaFmt<T>::v << 10) | ((b_mn_major ? 1u : 0u) << 16) |
-           ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+           ((uint32_t)(n >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
 }
 
 __device__ __forceinline__ float max3(float a, float b, float c) {
@@ -438,13 +439,16 @@ __device__ __forceinline__ void get_item(const Ctrl* ctrl, const Sm100Dev& p, in
 // EXPM: how the softmax takes its exponentials.  0: one fp32 exp2 per element on the exp2 unit; 1: two per issue
 //       through the unit's packed f16x2 form (see pack_f16x2); 11, 12, 13: fp32, with 1, 2 or 3 of every 8 column pairs
 //       on a polynomial on the FMA pipe instead.
-template <typename T, int EXPM, int VAR, int SPLIT>
+template <typename T, int EXPM, int VAR, int SPLIT, int HDIM = 128>
 __global__ void __launch_bounds__(NTHREADS, 1)
 fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                       const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_o,
                       const Sm100Dev p) {
     extern __shared__ uint8_t smem_raw[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // head dim of this instance (128, or 64 for the prefill forms): the names below shadow the file-scope constants
+    constexpr int HD = HDIM, TILE_BYTES = BM * HD * 2, HB = HD / 64;
+    static_assert(HDIM == 128 || (HDIM == 64 && SPLIT == 0), "hdim 64 is built for the prefill forms only");
     constexpr bool WINDOW = (VAR & 1) != 0;  // the mask has a second bound (see above)
     constexpr bool EXTRA = (VAR & 2) != 0;   // ALiBi and / or a logits soft cap on the scaled scores
     constexpr int NPOLY8 = EXPM >= 11 ? EXPM - 10 : 0;
@@ -667,7 +671,7 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                         // one box of (64 columns, group heads, 128/group tokens) per half: the rows land in
                         // (token, group head) order
                         mbar_expect_tx(&ctrl->q_full, TILE_BYTES);
-                        for (int hb = 0; hb < 2; ++hb) {
+                        for (int hb = 0; hb < HB; ++hb) {
                             if (SPLIT == 2) {  // the box holds 64 rows: once for tile rows 0-63, once for 64-127
                                 tma_load_4d(sQ + hb * HALF_BYTES, &map_q, &ctrl->q_full, hb * 64, 0, it.kh, it.q0);
                                 tma_load_4d(sQ + hb * HALF_BYTES + 64 * 128, &map_q, &ctrl->q_full, hb * 64, 0, it.kh, it.q0);
@@ -678,10 +682,10 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                     } else if (ok) {
                         const int q_tiles = (it.row0[1] < it.sq) ? 2 : 1;
                         mbar_expect_tx(&ctrl->q_full, q_tiles * TILE_BYTES);
-                        for (int hb = 0; hb < 2; ++hb)
+                        for (int hb = 0; hb < HB; ++hb)
                             tma_load_3d(sQ + hb * HALF_BYTES, &map_q, &ctrl->q_full, hb * 64, it.h[0], it.q0 + it.row0[0]);
                         if (q_tiles == 2)
-                            for (int hb = 0; hb < 2; ++hb)
+                            for (int hb = 0; hb < HB; ++hb)
                                 tma_load_3d(sQ + TILE_BYTES + hb * HALF_BYTES, &map_q, &ctrl->q_full, hb * 64, it.h[1],
                                             it.q0 + it.row0[1]);
                     }
@@ -693,11 +697,11 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                             const int row = it.k0 + (it.n0 + n) * BN;
                             if (!(ok = mbar_wait_bounded(&ctrl->k_empty[sk_], phk ^ 1u, abort_flag, p.status, 0x10))) break;
                             mbar_expect_tx(&ctrl->k_full[sk_], TILE_BYTES);
-                            for (int hb = 0; hb < 2; ++hb)
+                            for (int hb = 0; hb < HB; ++hb)
                                 tma_load_3d(sK + sk_ * TILE_BYTES + hb * HALF_BYTES, &map_k, &ctrl->k_full[sk_], hb * 64, it.kh, row);
                             if (!(ok = mbar_wait_bounded(&ctrl->v_empty[s], ph ^ 1u, abort_flag, p.status, 0x20))) break;
                             mbar_expect_tx(&ctrl->v_full[s], TILE_BYTES);
-                            for (int hb = 0; hb < 2; ++hb)
+                            for (int hb = 0; hb < HB; ++hb)
                                 tma_load_3d(sV + s * TILE_BYTES + hb * HALF_BYTES, &map_v, &ctrl->v_full[s], hb * 64, it.kh, row);
                         }
                     }
@@ -735,7 +739,7 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                     ok = __shfl_sync(0xffffffffu, ok, 0);
                     if (!ok) break;
                     if (k_role && my_valid > 0)
-                        for (int hb = 0; hb < 2; ++hb)
+                        for (int hb = 0; hb < HB; ++hb)
                             tma_load_3d(sK + sk_ * TILE_BYTES + hb * HALF_BYTES + lane * chunk * 128, &map_k, &ctrl->k_full[sk_],
                                         hb * 64, it.kh, my_row);
                     if (!v_role) {
@@ -754,7 +758,7 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                         if (lane == 0) mbar_expect_tx(&ctrl->v_tail, __popc(any_mask) * chunk * HD * 2);
                         __syncwarp();
                         if (my_valid > 0)
-                            for (int hb = 0; hb < 2; ++hb)
+                            for (int hb = 0; hb < HB; ++hb)
                                 tma_load_3d(sV + s * TILE_BYTES + hb * HALF_BYTES + lane * chunk * 128, &map_v, &ctrl->v_tail,
                                             hb * 64, it.kh, my_row);
                         if (lane == 0) ok = mbar_wait_bounded(&ctrl->v_tail, tail_cnt & 1u, abort_flag, p.status, 0x21);
@@ -764,8 +768,8 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                         const int c = __ffs(part_mask) - 1;
                         const int v = __shfl_sync(0xffffffffu, my_valid, c);
                         uint8_t* dst = sV + s * TILE_BYTES + c * chunk * 128;
-                        for (int idx = lane; idx < (chunk - v) * 16; idx += 32) {  // a row is 128 bytes in either half
-                            const int r = v + (idx >> 4), piece = idx & 15;
+                        for (int idx = lane; idx < (chunk - v) * (HD / 8); idx += 32) {  // a row is 128 bytes in every 64-column block
+                            const int r = v + idx / (HD / 8), piece = idx % (HD / 8);
                             *reinterpret_cast<uint4*>(dst + (piece >> 3) * HALF_BYTES + r * 128 + ((piece & 7) << 4)) =
                                 make_uint4(0u, 0u, 0u, 0u);
                         }
@@ -776,7 +780,7 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                         if (lane == 0) mbar_expect_tx(&ctrl->v_full[s], __popc(full_mask) * chunk * HD * 2);
                         __syncwarp();
                         if (my_valid == chunk)
-                            for (int hb = 0; hb < 2; ++hb)
+                            for (int hb = 0; hb < HB; ++hb)
                                 tma_load_3d(sV + s * TILE_BYTES + hb * HALF_BYTES + lane * chunk * 128, &map_v, &ctrl->v_full[s],
                                             hb * 64, it.kh, my_row);
                     }
@@ -789,7 +793,7 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         } else if (warp == 8) {
             // ================================ MMA issuer ================================
             constexpr uint32_t idesc_qk = make_idesc<T>(false);
-            constexpr uint32_t idesc_pv = make_idesc<T>(true);
+            constexpr uint32_t idesc_pv = make_idesc<T>(true, HD);  // N = head dim of V
             const uint32_t tS[2] = {tmem, tmem + 128};
             const uint32_t tO[2] = {tmem + 256, tmem + 384};
             // Descriptors are built once; per MMA only the 14-bit start-address field (16-byte units) advances,
@@ -1088,7 +1092,7 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                     const float alpha = grow ? fast_exp2(m_used - mx) : 1.f;  // exp2(-inf) = 0
                     l *= alpha;
 #pragma unroll
-                    for (int c = 0; c < 4; ++c) {
+                    for (int c = 0; c < HD / 32; ++c) {
                         uint32_t t[32];
                         tmem_ld32(tO + c * 32, t);
                         tmem_wait_ld();
@@ -1211,7 +1215,7 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                 uint8_t* stage = sStage + warp * STAGE_BYTES;
                 T* orow = (T*)p.o + ((int64_t)(it.q0 + row) * p.hq + head) * HD;
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {
+                for (int c = 0; c < HD / 32; ++c) {
                     uint32_t t[32];
                     if (Ni > 0) {
                         tmem_ld32(tO + c * 32, t);
@@ -1264,11 +1268,11 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     }
 }
 
-int make_map_3d(CUtensorMap* map, const void* base, int dtype, int64_t rows, int64_t heads, int box_rows = BM) {
+int make_map_3d(CUtensorMap* map, const void* base, int dtype, int64_t rows, int64_t heads, int box_rows = BM, int hd = HD) {
     PFN_encodeTiled enc = get_encode_tiled();
     FCK_REQUIRE(enc != nullptr, FLASHCK_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
-    const cuuint64_t dims[3] = {(cuuint64_t)HD, (cuuint64_t)heads, (cuuint64_t)(rows > 0 ? rows : 1)};
-    const cuuint64_t strides[2] = {(cuuint64_t)(HD * 2), (cuuint64_t)(heads * HD * 2)};
+    const cuuint64_t dims[3] = {(cuuint64_t)hd, (cuuint64_t)heads, (cuuint64_t)(rows > 0 ? rows : 1)};
+    const cuuint64_t strides[2] = {(cuuint64_t)(hd * 2), (cuuint64_t)(heads * hd * 2)};
     const cuuint32_t box[3] = {64, 1, (cuuint32_t)box_rows};
     const cuuint32_t estr[3] = {1, 1, 1};
     const CUtensorMapDataType dt =
@@ -1282,11 +1286,11 @@ int make_map_3d(CUtensorMap* map, const void* base, int dtype, int64_t rows, int
 }
 
 // O [rows, heads, 128] as 32-row x 32-column boxes (64-byte rows, 64-byte swizzle) for the epilogue's TMA stores.
-int make_map_o(CUtensorMap* map, const void* base, int dtype, int64_t rows, int64_t heads) {
+int make_map_o(CUtensorMap* map, const void* base, int dtype, int64_t rows, int64_t heads, int hd = HD) {
     PFN_encodeTiled enc = get_encode_tiled();
     FCK_REQUIRE(enc != nullptr, FLASHCK_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
-    const cuuint64_t dims[3] = {(cuuint64_t)HD, (cuuint64_t)heads, (cuuint64_t)(rows > 0 ? rows : 1)};
-    const cuuint64_t strides[2] = {(cuuint64_t)(HD * 2), (cuuint64_t)(heads * HD * 2)};
+    const cuuint64_t dims[3] = {(cuuint64_t)hd, (cuuint64_t)heads, (cuuint64_t)(rows > 0 ? rows : 1)};
+    const cuuint64_t strides[2] = {(cuuint64_t)(hd * 2), (cuuint64_t)(heads * hd * 2)};
     const cuuint32_t box[3] = {32, 1, 32};
     const cuuint32_t estr[3] = {1, 1, 1};
     const CUtensorMapDataType dt =
@@ -1298,7 +1302,7 @@ int make_map_o(CUtensorMap* map, const void* base, int dtype, int64_t rows, int6
     return FLASHCK_OK;
 }
 
-template <typename T, int EXPM, int VAR, int SPLIT>
+template <typename T, int EXPM, int VAR, int SPLIT, int HDIM = 128>
 int launch_t(const FwdParams& p, const Sm100Dev& dev, cudaStream_t stream) {
     const int64_t rows_q = p.seqstart_q ? p.total_q : p.batch * p.seqlen_q;
     const bool paged = p.block_table || p.kv_indptr;
@@ -1309,12 +1313,12 @@ int launch_t(const FwdParams& p, const Sm100Dev& dev, cudaStream_t stream) {
     const int box_k = paged ? (int)std::min<int64_t>(p.page, BN) : BN;
     CUtensorMap mq, mk, mv, mo;
     int rc;
-    if ((rc = make_map_3d(&mq, p.q, p.dtype, rows_q, p.hq))) return rc;
-    if ((rc = make_map_3d(&mk, p.k, p.dtype, rows_k, p.hkv, box_k))) return rc;
-    if ((rc = make_map_3d(&mv, p.v, p.dtype, rows_k, p.hkv, box_k))) return rc;
-    if ((rc = make_map_o(&mo, p.o, p.dtype, rows_q, p.hq))) return rc;
-    auto kern = fmha_fwd_sm100_kernel<T, EXPM, VAR, SPLIT>;
-    const size_t smem = 1024 + (size_t)(2 + 2 * KV_SLOTS) * TILE_BYTES + 8 * STAGE_BYTES + sizeof(Ctrl);
+    if ((rc = make_map_3d(&mq, p.q, p.dtype, rows_q, p.hq, BM, HDIM))) return rc;
+    if ((rc = make_map_3d(&mk, p.k, p.dtype, rows_k, p.hkv, box_k, HDIM))) return rc;
+    if ((rc = make_map_3d(&mv, p.v, p.dtype, rows_k, p.hkv, box_k, HDIM))) return rc;
+    if ((rc = make_map_o(&mo, p.o, p.dtype, rows_q, p.hq, HDIM))) return rc;
+    auto kern = fmha_fwd_sm100_kernel<T, EXPM, VAR, SPLIT, HDIM>;
+    const size_t smem = 1024 + (size_t)(2 + 2 * KV_SLOTS) * (BM * HDIM * 2) + 8 * STAGE_BYTES + sizeof(Ctrl);
     static thread_local int configured_device = -1;
     int devid = 0;
     FCK_CUDA(cudaGetDevice(&devid));
@@ -1333,7 +1337,8 @@ int launch_t(const FwdParams& p, const Sm100Dev& dev, cudaStream_t stream) {
 
 bool fwd_sm100_supported(const FwdParams& p) {
     if (!g_use_sm100.load()) return false;
-    if (p.d != HD || p.dv != HD) return false;
+    if (p.d != p.dv || (p.d != 128 && p.d != 64)) return false;
+    if (p.d == 64 && !g_use_sm100_hdim64.load()) return false;
     if (p.bias && p.bias_type == 1) return false;  // an elementwise bias tensor: the general instance
     if (p.bias && p.bias_type == 2 && p.bias_rank > 1) return false;
     const bool paged = p.block_table || p.kv_indptr;
@@ -1392,6 +1397,15 @@ int launch_fwd_sm100(const FwdParams& p, cudaStream_t stream) {
     dev.alibi = (p.bias && p.bias_type == 2) ? (const float*)p.bias : nullptr; dev.alibi_rank = p.bias_rank;
 #define FCK_SM100_LAUNCH(E, V) \
     return bf16 ? launch_t<__nv_bfloat16, E, V, 0>(p, dev, stream) : launch_t<__half, E, V, 0>(p, dev, stream)
+    if (p.d == 64) {  // the hdim-64 instances: fp32 exponentials on the exp2 unit, every mask and score addition
+        dev.rescale_thr = kRescaleThreshold;
+        switch ((window ? 1 : 0) | (extra ? 2 : 0)) {
+            case 0: return bf16 ? launch_t<__nv_bfloat16, 0, 0, 0, 64>(p, dev, stream) : launch_t<__half, 0, 0, 0, 64>(p, dev, stream);
+            case 1: return bf16 ? launch_t<__nv_bfloat16, 0, 1, 0, 64>(p, dev, stream) : launch_t<__half, 0, 1, 0, 64>(p, dev, stream);
+            case 2: return bf16 ? launch_t<__nv_bfloat16, 0, 2, 0, 64>(p, dev, stream) : launch_t<__half, 0, 2, 0, 64>(p, dev, stream);
+            default: return bf16 ? launch_t<__nv_bfloat16, 0, 3, 0, 64>(p, dev, stream) : launch_t<__half, 0, 3, 0, 64>(p, dev, stream);
+        }
+    }
     if (extra) {  // (the score-addition instances take their exponentials in fp32 on the exp2 unit)
         if (window) { FCK_SM100_LAUNCH(0, 3); }
         FCK_SM100_LAUNCH(0, 2);
@@ -1542,6 +1556,7 @@ static bool valid_exp_mode(int64_t v) { return v == 0 || v == 1 || (v >= 11 && v
 
 int fwd_set_param(const char* key, int64_t value) {
     if (!strcmp(key, "use_sm100")) { g_use_sm100 = value; return FLASHCK_OK; }
+    if (!strcmp(key, "use_sm100_hdim64")) { g_use_sm100_hdim64 = value; return FLASHCK_OK; }
     if (!strcmp(key, "use_sm100_splitkv")) { g_use_sm100_splitkv = value; return FLASHCK_OK; }
     if (!strcmp(key, "exp_mode")) {
         if (!valid_exp_mode(value)) return FLASHCK_ERR_INVALID_ARGUMENT;
@@ -1577,6 +1592,7 @@ int fwd_set_param(const char* key, int64_t value) {
 }
 int fwd_get_param(const char* key, int64_t* value) {
     if (!strcmp(key, "use_sm100")) { *value = g_use_sm100; return FLASHCK_OK; }
+    if (!strcmp(key, "use_sm100_hdim64")) { *value = g_use_sm100_hdim64; return FLASHCK_OK; }
     if (!strcmp(key, "use_sm100_splitkv")) { *value = g_use_sm100_splitkv; return FLASHCK_OK; }
     if (!strcmp(key, "exp_mode")) { *value = g_exp_mode; return FLASHCK_OK; }
     if (!strcmp(key, "exp_mode_splitkv")) { *value = g_exp_mode_splitkv; return FLASHCK_OK; }

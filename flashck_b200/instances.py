@@ -183,8 +183,10 @@ def _why_invalid_fwd(t: FmhaFwdInstance, p: FmhaProblem) -> Optional[str]:
         return "rescale_log2_x100 outside [0, 1400]"
     esize = 2
     if t.pipeline == 1:
-        if (t.block_m, t.block_n, t.head_dim) != (128, 128, 128):
-            return "the tcgen05 instance is built for 128 x 128 tiles at head_dim 128"
+        if (t.block_m, t.block_n) != (128, 128) or t.head_dim not in (64, 128):
+            return "the tcgen05 instance is built for 128 x 128 tiles at head_dim 128 or 64"
+        if t.head_dim == 64 and t.exp_mode != 0:
+            return "the hdim-64 tcgen05 instances take their exponentials in fp32 on the exp2 unit"
         if t.kv_stages != 2 or t.softmax_wgs != 2 or t.min_block_per_cu != 1:
             return "the tcgen05 instance is built with a 2-slot K/V ring, 2 softmax warpgroups, 384 threads, 1 CTA per SM"
         # S and O accumulators of two Q tiles: fp32 columns of tensor memory
@@ -194,8 +196,10 @@ def _why_invalid_fwd(t: FmhaFwdInstance, p: FmhaProblem) -> Optional[str]:
         smem = (2 * t.block_m + 2 * t.kv_stages * t.block_n) * t.head_dim * esize + 16 * 1024 + 1024 + 17 * 1024
         if smem > SMEM_PER_CTA:
             return f"tiles, staging and schedule need {smem} bytes of shared memory"
-        if p.bias != "none" or p.soft_cap:
-            return "bias, ALiBi and soft cap run on the general instance"
+        if p.bias == "elementwise":
+            return "an elementwise bias tensor runs on the general instance"
+        if (p.bias != "none" or p.soft_cap) and t.exp_mode != 0:
+            return "the score-addition instances (ALiBi, soft cap) take their exponentials in fp32 on the exp2 unit"
         if p.batch > 256 or (p.max_seqlen_q + 127) // 128 > 512 or p.hq > 1023:
             return "beyond the on-chip schedule (256 sequences, 512 row blocks, 1023 heads)"
         if p.paged and (p.page < 16 or not (128 % p.page == 0 or p.page % 128 == 0)):

@@ -174,6 +174,28 @@ def test_fmha_fwd_packed_exp2_lse_with_one_dominant_late_key(dtype):
     print("max LSE error: fp32 exp2 %.3g, packed f16x2 exp2 %.3g" % (worst[0], worst[1]))
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_fmha_fwd_hdim64_runs_on_the_tcgen05_instance_and_agrees_with_the_general_one(dtype):
+    """BASELINE config 1's geometry (hdim 64) and a longer varlen GQA problem at hdim 64: served by the tcgen05 kernel's
+    hdim-64 instances (instance parameter use_sm100_hdim64), equal to the oracle and to the general instance."""
+    lens = [128, 700, 1, 333]
+    cu = to_seqstarts(lens)
+    q, k, v = (normal_tensor((sum(lens), h, 64), dtype, 40 + i) for i, h in enumerate((8, 2, 2)))
+    o_ref, lse_ref = oracle.fmha_fwd(q, k, v, seqstart_q=cu, seqstart_k=cu, mask_type=1, window=(-1, 0))
+    outs = {}
+    for use in (1, 0):
+        _lib.set_instance_param(0, "use_sm100_hdim64", use)
+        try:
+            outs[use] = ops.fmha_fwd_var_len(_cu(q), _cu(k), _cu(v), _cu(cu), _cu(cu), max(lens), causal=True, return_lse=True)
+            assert _lib.get_instance_param(0, "last_instance") == use
+        finally:
+            _lib.set_instance_param(0, "use_sm100_hdim64", 1)
+    for use in (1, 0):
+        assert_o_close(outs[use][0], o_ref, f"use_sm100_hdim64={use}")
+        assert_lse_close(outs[use][1], lse_ref, f"use_sm100_hdim64={use}")
+    assert _lib.device_status() == 0
+
+
 def test_fmha_fwd_var_len_gqa():
     dtype = torch.bfloat16
     lens = [1, 64, 65, 200, 0, 333]
@@ -533,8 +555,8 @@ def test_fmha_fwd_bias_alibi_and_soft_cap(dtype, d, kind):
                           alibi_slopes=_cu(slopes) if slopes is not None else None, logits_soft_cap=cap)
     assert_o_close(o, o_ref, kind)
     assert_lse_close(lse, lse_ref, kind)
-    # ALiBi and the soft cap are flags of the tcgen05 softmax at hdim 128; a bias tensor and hdim 64 use the general instance
-    assert _lib.get_instance_param(0, "last_instance") == (1 if d == 128 and "bias" not in kind else 0)
+    # ALiBi and the soft cap are flags of the tcgen05 softmax; a bias tensor uses the general instance
+    assert _lib.get_instance_param(0, "last_instance") == (0 if "bias" in kind else 1)
     # the additions change the result (the test would pass vacuously if they were dropped on both sides)
     o_plain, _ = oracle.fmha_fwd(q, k, v, mask_type=2, window=(-1, 0))
     assert (o_plain.float() - o_ref.float()).abs().max() > 0.05
@@ -562,14 +584,15 @@ def test_fmha_fwd_alibi_and_soft_cap_together_on_the_tcgen05_instance(window):
 def test_fallback_to_the_general_instance_is_reported_when_logging_is_on(capfd):
     import flashck_b200 as fck
     q = normal_tensor((1, 40, 4, 64), torch.bfloat16, 1)
+    bias = _cu(normal_tensor((1, 1, 40, 40), torch.bfloat16, 2))  # a bias tensor is served by the general instance
     old = fck.get_flag_value("FC_TUNING_LOG")
     try:
         fck.set_flag_value("FC_TUNING_LOG", True)
-        ops.fmha_fwd(_cu(q), _cu(q), _cu(q))
+        ops.fmha_fwd(_cu(q), _cu(q), _cu(q), bias=bias)
         torch.cuda.synchronize()
         assert "general (mma.sync) instance" in capfd.readouterr().err
         fck.set_flag_value("FC_TUNING_LOG", False)
-        ops.fmha_fwd(_cu(q), _cu(q), _cu(q))
+        ops.fmha_fwd(_cu(q), _cu(q), _cu(q), bias=bias)
         torch.cuda.synchronize()
         assert "general" not in capfd.readouterr().err
     finally:

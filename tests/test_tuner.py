@@ -41,12 +41,13 @@ def test_instances_validity_names_and_heuristics():
     assert len(valid) == 7 and len(set(names)) == 7
     # what cannot work says why
     assert "128 x 128" in I.why_invalid(I.FmhaFwdInstance(block_m=64), p)
+    assert "exp2 unit" in I.why_invalid(I.FmhaFwdInstance(head_dim=64, exp_mode=1), _prefill_problem(d=64, dv=64))
     assert I.why_invalid(I.FmhaFwdInstance(), p) is None
     assert "head_dim" in I.why_invalid(I.FmhaFwdInstance(head_dim=64), p)
     assert "positive" in I.why_invalid(I.FmhaFwdInstance(kv_stages=0), p)
-    # hdim 64 and bias problems have the general instance only
-    assert [t.pipeline for t in cands if I.is_valid(t, _prefill_problem(d=64, dv=64))] == [0]
-    assert [t.pipeline for t in cands if I.is_valid(t, _prefill_problem(bias="alibi"))] == [0]
+    # hdim 64 has one tcgen05 instance and the general one; a bias tensor has the general instance only
+    assert sorted(t.pipeline for t in cands if I.is_valid(t, _prefill_problem(d=64, dv=64))) == [0, 1]
+    assert [t.pipeline for t in cands if I.is_valid(t, _prefill_problem(bias="elementwise"))] == [0]
     # rules of thumb: tensor-memory pipeline with the plain exp2 unit first
     kept = I.heuristic_filter(valid, p)
     assert kept[0].pipeline == 1 and kept[0].exp_mode == 0 and all(t.pipeline == 1 for t in kept)
