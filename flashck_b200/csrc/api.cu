@@ -225,7 +225,7 @@ int FmhaFwdFp8(void* q, void* k, void* v, void* o, int64_t* q_seq_start, int64_t
     p.scale = resolve_scale(scale_s, d);
     p.mask_type = (int)mask_type; p.wl = window_left; p.wr = window_right; p.dtype = dtype;
     p.scale_p = scale_p; p.scale_o = scale_o; p.out_dtype = o_dtype;
-    return launch_fwd_generic(p, (cudaStream_t)stream);  // (the tcgen05 instance is built for 16-bit operands)
+    return run_fwd(p, (cudaStream_t)stream);  // (hdim 128 contiguous: the kind::f8f6f4 tcgen05 instance; else the general one)
 }
 
 int FmhaFwdBias(void* q, void* k, void* v, void* bias, void* o, int64_t* q_seq_start, int64_t* k_seq_start,

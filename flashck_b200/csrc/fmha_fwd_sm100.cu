@@ -37,6 +37,8 @@
 #include <string.h>
 #include <type_traits>
 
+#include <cuda_fp8.h>
+
 #include "kernels.h"
 
 namespace fck {
@@ -57,6 +59,7 @@ constexpr float kRescaleThreshold = 8.f;  // log2 units; fp32 exponentials: P st
 std::atomic<int64_t> g_rescale_half_x100{200};
 
 std::atomic<int64_t> g_use_sm100{1};
+std::atomic<int64_t> g_use_sm100_fp8{1};     // 8-bit prefill (hdim 128, contiguous) on the tcgen05 instance (0: general)
 std::atomic<int64_t> g_use_sm100_hdim64{1};  // hdim-64 prefill on the tcgen05 instance (0: on the general one)
 // exponentials of the softmax (template parameter EXPM of the kernel): 0 fp32 on the exp2 unit, 1 packed f16x2 on the
 // exp2 unit, 11 / 12 / 13 fp32 with 1 / 2 / 3 of every 8 column pairs on an FMA-pipe polynomial
@@ -100,6 +103,10 @@ struct Sm100Dev {
     const float* alibi;     // EXTRA: fp32 slopes [1,hq] (alibi_rank 0) or [batch,hq] (1), or nullptr
     int alibi_rank;
     float rescale_thr;  // the running max is raised (and O rescaled) when the row max exceeds it by more than this (log2 units)
+    // 8-bit instances: P is stretched by scale_p before it is rounded to 8 bits, the accumulator is taken to the range of
+    // O by scale_o; O leaves as out_dtype (a FLASHCK_DTYPE_* code: 8-bit saturating, or 16-bit)
+    float scale_p, scale_o;
+    int out_dtype;
 };
 
 // ---- PTX wrappers ---------------------------------------------------------------------------------------------
@@ -112,19 +119,36 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_
     d |= (uint64_t)2 << 61;  // 128-byte swizzle
     return d;
 }
+// F8 = false: kind::f16 (16-bit operands, K = 16 per instruction); true: kind::f8f6f4 (8-bit operands, K = 32).
+template <bool F8 = false>
 __device__ __forceinline__ void umma_ss(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
-    asm volatile(
-        "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(d_tmem),
-        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc)
-        : "memory");
+    if constexpr (F8)
+        asm volatile(
+            "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+            "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n}\n" ::"r"(d_tmem),
+            "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc)
+            : "memory");
+    else
+        asm volatile(
+            "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(d_tmem),
+            "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc)
+            : "memory");
 }
+template <bool F8 = false>
 __device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
-    asm volatile(
-        "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n" ::"r"(d_tmem),
-        "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(acc)
-        : "memory");
+    if constexpr (F8)
+        asm volatile(
+            "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+            "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], [%1], %2, %3, p;\n}\n" ::"r"(d_tmem),
+            "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(acc)
+            : "memory");
+    else
+        asm volatile(
+            "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n" ::"r"(d_tmem),
+            "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(acc)
+            : "memory");
 }
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_u32(bar))
@@ -158,6 +182,14 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
         "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
         : "memory");
 }
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};\n" ::"r"(taddr),
+        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+        "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
 __device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2) {
     asm volatile(
         "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3,%4,%5}], [%2];\n" ::
@@ -175,11 +207,21 @@ __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk
 __device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;\n" ::: "memory"); }
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
 
-// Instruction descriptor of tcgen05.mma kind::f16: D = f32 (bits 4-5 = 1); A/B format at bits 7-9 / 10-12
-// (0 = f16, 1 = bf16); bit 16: B is MN-major; N >> 3 at bits 17-22; M >> 4 at bits 24-28.
+// Element tags of the 8-bit instances (Q, K, V and P in one of the two OCP 8-bit float formats; kind::f8f6f4).
+struct f8e4m3_t {};
+struct f8e5m2_t {};
+template <typename T> struct ElemInfo { static constexpr int bytes = 2; static constexpr bool f8 = false; };
+template <> struct ElemInfo<f8e4m3_t> { static constexpr int bytes = 1; static constexpr bool f8 = true; };
+template <> struct ElemInfo<f8e5m2_t> { static constexpr int bytes = 1; static constexpr bool f8 = true; };
+
+// Instruction descriptor of tcgen05.mma kind::f16 / kind::f8f6f4: D = f32 (bits 4-5 = 1); A/B format at bits 7-9 /
+// 10-12 (kind::f16: 0 = f16, 1 = bf16; kind::f8f6f4: 0 = E4M3, 1 = E5M2); bit 16: B is MN-major; N >> 3 at bits 17-22;
+// M >> 4 at bits 24-28.
 template <typename T> struct UmmaFmt;
 template <> struct UmmaFmt<__half> { static constexpr uint32_t v = 0u; };
 template <> struct UmmaFmt<__nv_bfloat16> { static constexpr uint32_t v = 1u; };
+template <> struct UmmaFmt<f8e4m3_t> { static constexpr uint32_t v = 0u; };
+template <> struct UmmaFmt<f8e5m2_t> { static constexpr uint32_t v = 1u; };
 template <typename T>
 __device__ __forceinline__ constexpr uint32_t make_idesc(bool b_mn_major, int n = BN) {
     return (1u << 4) | (UmmaFmt<T>::v << 7) | (UmmaFmt<T>::v << 10) | ((b_mn_major ? 1u : 0u) << 16) |
@@ -447,8 +489,14 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     extern __shared__ uint8_t smem_raw[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // head dim of this instance (128, or 64 for the prefill forms): the names below shadow the file-scope constants
-    constexpr int HD = HDIM, TILE_BYTES = BM * HD * 2, HB = HD / 64;
+    // RB: bytes of one row of Q, K or V; HB: its 128-byte blocks; XB: elements per block (the TMA x step); KK: keys
+    // (PV) or head-dim elements (QK^T) one MMA instruction contracts: 32 bytes of a row either way
+    constexpr bool F8 = ElemInfo<T>::f8;
+    constexpr int ES = ElemInfo<T>::bytes;
+    constexpr int HD = HDIM, RB = HD * ES, TILE_BYTES = BM * RB, HB = RB / 128, XB = 128 / ES, KK = 32 / ES;
     static_assert(HDIM == 128 || (HDIM == 64 && SPLIT == 0), "hdim 64 is built for the prefill forms only");
+    static_assert(!F8 || (HDIM == 128 && SPLIT == 0 && (VAR & 2) == 0 && EXPM == 0),
+                  "the 8-bit instances: hdim 128, prefill forms, fp32 exponentials, no score additions");
     constexpr bool WINDOW = (VAR & 1) != 0;  // the mask has a second bound (see above)
     constexpr bool EXTRA = (VAR & 2) != 0;   // ALiBi and / or a logits soft cap on the scaled scores
     constexpr int NPOLY8 = EXPM >= 11 ? EXPM - 10 : 0;
@@ -673,20 +721,20 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                         mbar_expect_tx(&ctrl->q_full, TILE_BYTES);
                         for (int hb = 0; hb < HB; ++hb) {
                             if (SPLIT == 2) {  // the box holds 64 rows: once for tile rows 0-63, once for 64-127
-                                tma_load_4d(sQ + hb * HALF_BYTES, &map_q, &ctrl->q_full, hb * 64, 0, it.kh, it.q0);
-                                tma_load_4d(sQ + hb * HALF_BYTES + 64 * 128, &map_q, &ctrl->q_full, hb * 64, 0, it.kh, it.q0);
+                                tma_load_4d(sQ + hb * HALF_BYTES, &map_q, &ctrl->q_full, hb * XB, 0, it.kh, it.q0);
+                                tma_load_4d(sQ + hb * HALF_BYTES + 64 * 128, &map_q, &ctrl->q_full, hb * XB, 0, it.kh, it.q0);
                             } else {
-                                tma_load_4d(sQ + hb * HALF_BYTES, &map_q, &ctrl->q_full, hb * 64, 0, it.kh, it.q0 + it.row0[0] / p.group);
+                                tma_load_4d(sQ + hb * HALF_BYTES, &map_q, &ctrl->q_full, hb * XB, 0, it.kh, it.q0 + it.row0[0] / p.group);
                             }
                         }
                     } else if (ok) {
                         const int q_tiles = (it.row0[1] < it.sq) ? 2 : 1;
                         mbar_expect_tx(&ctrl->q_full, q_tiles * TILE_BYTES);
                         for (int hb = 0; hb < HB; ++hb)
-                            tma_load_3d(sQ + hb * HALF_BYTES, &map_q, &ctrl->q_full, hb * 64, it.h[0], it.q0 + it.row0[0]);
+                            tma_load_3d(sQ + hb * HALF_BYTES, &map_q, &ctrl->q_full, hb * XB, it.h[0], it.q0 + it.row0[0]);
                         if (q_tiles == 2)
                             for (int hb = 0; hb < HB; ++hb)
-                                tma_load_3d(sQ + TILE_BYTES + hb * HALF_BYTES, &map_q, &ctrl->q_full, hb * 64, it.h[1],
+                                tma_load_3d(sQ + TILE_BYTES + hb * HALF_BYTES, &map_q, &ctrl->q_full, hb * XB, it.h[1],
                                             it.q0 + it.row0[1]);
                     }
                     if (p.page == 0) {  // contiguous K/V: one box per tile and 64-column half
@@ -698,11 +746,11 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                             if (!(ok = mbar_wait_bounded(&ctrl->k_empty[sk_], phk ^ 1u, abort_flag, p.status, 0x10))) break;
                             mbar_expect_tx(&ctrl->k_full[sk_], TILE_BYTES);
                             for (int hb = 0; hb < HB; ++hb)
-                                tma_load_3d(sK + sk_ * TILE_BYTES + hb * HALF_BYTES, &map_k, &ctrl->k_full[sk_], hb * 64, it.kh, row);
+                                tma_load_3d(sK + sk_ * TILE_BYTES + hb * HALF_BYTES, &map_k, &ctrl->k_full[sk_], hb * XB, it.kh, row);
                             if (!(ok = mbar_wait_bounded(&ctrl->v_empty[s], ph ^ 1u, abort_flag, p.status, 0x20))) break;
                             mbar_expect_tx(&ctrl->v_full[s], TILE_BYTES);
                             for (int hb = 0; hb < HB; ++hb)
-                                tma_load_3d(sV + s * TILE_BYTES + hb * HALF_BYTES, &map_v, &ctrl->v_full[s], hb * 64, it.kh, row);
+                                tma_load_3d(sV + s * TILE_BYTES + hb * HALF_BYTES, &map_v, &ctrl->v_full[s], hb * XB, it.kh, row);
                         }
                     }
                 }
@@ -741,7 +789,7 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                     if (k_role && my_valid > 0)
                         for (int hb = 0; hb < HB; ++hb)
                             tma_load_3d(sK + sk_ * TILE_BYTES + hb * HALF_BYTES + lane * chunk * 128, &map_k, &ctrl->k_full[sk_],
-                                        hb * 64, it.kh, my_row);
+                                        hb * XB, it.kh, my_row);
                     if (!v_role) {
                         my_row = next_row;
                         my_valid = next_valid;
@@ -760,7 +808,7 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                         if (my_valid > 0)
                             for (int hb = 0; hb < HB; ++hb)
                                 tma_load_3d(sV + s * TILE_BYTES + hb * HALF_BYTES + lane * chunk * 128, &map_v, &ctrl->v_tail,
-                                            hb * 64, it.kh, my_row);
+                                            hb * XB, it.kh, my_row);
                         if (lane == 0) ok = mbar_wait_bounded(&ctrl->v_tail, tail_cnt & 1u, abort_flag, p.status, 0x21);
                         ++tail_cnt;
                         ok = __shfl_sync(0xffffffffu, ok, 0);
@@ -782,7 +830,7 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                         if (my_valid == chunk)
                             for (int hb = 0; hb < HB; ++hb)
                                 tma_load_3d(sV + s * TILE_BYTES + hb * HALF_BYTES + lane * chunk * 128, &map_v, &ctrl->v_full[s],
-                                            hb * 64, it.kh, my_row);
+                                            hb * XB, it.kh, my_row);
                     }
                     my_row = next_row;
                     my_valid = next_valid;
@@ -807,25 +855,25 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                 const uint64_t qd = i ? dQ1 : dQ0, kd = dK0 + (uint64_t)((s * TILE_BYTES) >> 4);
                 const uint32_t d = tS[i];
 #pragma unroll
-                for (int ks = 0; ks < HD / 16; ++ks) {
+                for (int ks = 0; ks < RB / 32; ++ks) {
                     const uint64_t off = (uint64_t)(((ks / 4) * HALF_BYTES + (ks % 4) * 32) >> 4);
-                    umma_ss(d, qd + off, kd + off, idesc_qk, ks > 0 ? 1u : 0u);
+                    umma_ss<F8>(d, qd + off, kd + off, idesc_qk, ks > 0 ? 1u : 0u);
                 }
             };
             auto issue_pv = [&](int i, int s, bool accumulate) {  // O_i += P_i V : 8 steps of 16 keys
                 const uint64_t vd = s ? dV1 : dV0;
                 const uint32_t d = tO[i], a = tS[i];
 #pragma unroll
-                for (int ks = 0; ks < BN / 16; ++ks)
-                    umma_ts(d, a + ks * 8, vd + (uint64_t)((ks * 2048) >> 4), idesc_pv, (accumulate || ks > 0) ? 1u : 0u);
+                for (int ks = 0; ks < BN / KK; ++ks)  // KK keys = KK rows of 128 bytes of the V tile, 8 columns of P
+                    umma_ts<F8>(d, a + ks * 8, vd + (uint64_t)((ks * KK * 128) >> 4), idesc_pv, (accumulate || ks > 0) ? 1u : 0u);
             };
             // split modes: tile 0's Q against S buffer `buf` (the S columns of either tile), P read from the same buffer
             auto issue_qk_to = [&](uint32_t buf, int s) {
                 const uint64_t kd = dK0 + (uint64_t)((s * TILE_BYTES) >> 4);
 #pragma unroll
-                for (int ks = 0; ks < HD / 16; ++ks) {
+                for (int ks = 0; ks < RB / 32; ++ks) {
                     const uint64_t off = (uint64_t)(((ks / 4) * HALF_BYTES + (ks % 4) * 32) >> 4);
-                    umma_ss(tS[0] + buf * 128, dQ0 + off, kd + off, idesc_qk, ks > 0 ? 1u : 0u);
+                    umma_ss<F8>(tS[0] + buf * 128, dQ0 + off, kd + off, idesc_qk, ks > 0 ? 1u : 0u);
                 }
             };
             // running counts give ring slots and barrier parities across work items
@@ -1111,7 +1159,26 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                 // exact zeros for them.  The two variants are separate straight-line loops so that the scheduler
                 // can interleave exp2-unit and FMA-pipe work across column pairs.
                 auto exp_half = [&](int c, auto use_poly_tag) {
-                    constexpr int NP = decltype(use_poly_tag)::value;
+                    [[maybe_unused]] constexpr int NP = decltype(use_poly_tag)::value;
+                    if constexpr (F8) {
+                        // 8-bit P: stretched by scale_p, rounded (saturating) to the operand format, four keys per
+                        // TMEM column; the row sum takes the unrounded values
+                        constexpr __nv_fp8_interpretation_t kind = std::is_same<T, f8e4m3_t>::value ? __NV_E4M3 : __NV_E5M2;
+                        const float2 sp2 = make_float2(p.scale_p, p.scale_p);
+                        uint32_t pk8[16];
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            const int e = c * 64 + 2 * j;
+                            const float2 x = __ffma2_rn(make_float2(__uint_as_float(sreg[e]), __uint_as_float(sreg[e + 1])), sc2, nm2);
+                            float2 pr;
+                            pr.x = ex2_fast(x.x);
+                            pr.y = ex2_fast(x.y);
+                            if (j & 1) psb = __fadd2_rn(psb, pr); else psa = __fadd2_rn(psa, pr);
+                            const uint32_t q2 = (uint32_t)__nv_cvt_float2_to_fp8x2(__fmul2_rn(pr, sp2), __NV_SATFINITE, kind);
+                            if (j & 1) pk8[j >> 1] |= q2 << 16; else pk8[j >> 1] = q2;
+                        }
+                        tmem_st16(tSb + c * 16, pk8);
+                    } else {
                     uint32_t pk[32];
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
@@ -1136,6 +1203,7 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                         pk[j] = Elem<T>::pack2(pr.x, pr.y);
                     }
                     tmem_st32(tSb + (SPLIT == 2 ? khalf : c) * 32, pk);
+                    }
                 };
                 if (need_mask) {
                     exp_half(0, std::integral_constant<int, 0>{});
@@ -1211,6 +1279,50 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                 // Whole tiles leave through shared memory and TMA stores (32 rows x 32 columns per warp and store), which
                 // keeps the load/store unit free for the other warps; a tile that reaches past the end of its sequence
                 // is written row by row, because its surplus rows belong to the next sequence of the packed buffer.
+                if constexpr (F8) {
+                    // 8-bit instances: O = scale_o * acc / l in the output type the call names, written row by row
+                    // (a row of 128 values is 128 or 256 contiguous bytes)
+                    const float f = inv * p.scale_o;
+                    const int64_t orow_elems = ((int64_t)(it.q0 + row) * p.hq + head) * HD;
+#pragma unroll
+                    for (int c = 0; c < HD / 32; ++c) {
+                        uint32_t t[32];
+                        if (Ni > 0) {
+                            tmem_ld32(tO + c * 32, t);
+                            tmem_wait_ld();
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) t[j] = 0u;
+                        }
+                        if (!row_ok) continue;
+                        if (p.out_dtype == FLASHCK_DTYPE_FLOAT8 || p.out_dtype == FLASHCK_DTYPE_BFLOAT8) {
+                            const __nv_fp8_interpretation_t okind = p.out_dtype == FLASHCK_DTYPE_FLOAT8 ? __NV_E4M3 : __NV_E5M2;
+                            uint32_t w[8];
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) {
+                                const uint32_t lo = __nv_cvt_float2_to_fp8x2(
+                                    make_float2(__uint_as_float(t[4 * j]) * f, __uint_as_float(t[4 * j + 1]) * f), __NV_SATFINITE, okind);
+                                const uint32_t hi = __nv_cvt_float2_to_fp8x2(
+                                    make_float2(__uint_as_float(t[4 * j + 2]) * f, __uint_as_float(t[4 * j + 3]) * f), __NV_SATFINITE, okind);
+                                w[j] = lo | (hi << 16);
+                            }
+                            uint8_t* dst = (uint8_t*)p.o + orow_elems + c * 32;
+                            *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
+                            *reinterpret_cast<uint4*>(dst + 16) = make_uint4(w[4], w[5], w[6], w[7]);
+                        } else {
+                            uint32_t w[16];
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) {
+                                const float a = __uint_as_float(t[2 * j]) * f, b = __uint_as_float(t[2 * j + 1]) * f;
+                                w[j] = p.out_dtype == FLASHCK_DTYPE_BFLOAT16 ? Elem<__nv_bfloat16>::pack2(a, b) : Elem<__half>::pack2(a, b);
+                            }
+                            uint8_t* dst = (uint8_t*)p.o + (orow_elems + c * 32) * 2;
+#pragma unroll
+                            for (int v4 = 0; v4 < 4; ++v4)
+                                *reinterpret_cast<uint4*>(dst + v4 * 16) = make_uint4(w[4 * v4], w[4 * v4 + 1], w[4 * v4 + 2], w[4 * v4 + 3]);
+                        }
+                    }
+                } else {
                 const bool whole_tile = tile_first_row + BM <= sq;
                 uint8_t* stage = sStage + warp * STAGE_BYTES;
                 T* orow = (T*)p.o + ((int64_t)(it.q0 + row) * p.hq + head) * HD;
@@ -1249,6 +1361,7 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                         for (int v4 = 0; v4 < 4; ++v4) *reinterpret_cast<uint4*>(orow + c * 32 + v4 * 8) = pk[v4];
                     }
                 }
+                }
                 if (p.lse && row_ok) {
                     float* lp = p.seqstart_q ? p.lse + (int64_t)head * p.total_q + it.q0 + row
                                              : p.lse + ((int64_t)it.b * p.hq + head) * p.seqlen_q + row;
@@ -1271,12 +1384,15 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
 int make_map_3d(CUtensorMap* map, const void* base, int dtype, int64_t rows, int64_t heads, int box_rows = BM, int hd = HD) {
     PFN_encodeTiled enc = get_encode_tiled();
     FCK_REQUIRE(enc != nullptr, FLASHCK_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    // boxes of 128 bytes of a row (64 16-bit or 128 8-bit elements; the 8-bit formats travel as plain bytes)
+    const bool f8 = dtype == FLASHCK_DTYPE_FLOAT8 || dtype == FLASHCK_DTYPE_BFLOAT8;
+    const int es = f8 ? 1 : 2;
     const cuuint64_t dims[3] = {(cuuint64_t)hd, (cuuint64_t)heads, (cuuint64_t)(rows > 0 ? rows : 1)};
-    const cuuint64_t strides[2] = {(cuuint64_t)(hd * 2), (cuuint64_t)(heads * hd * 2)};
-    const cuuint32_t box[3] = {64, 1, (cuuint32_t)box_rows};
+    const cuuint64_t strides[2] = {(cuuint64_t)(hd * es), (cuuint64_t)(heads * hd * es)};
+    const cuuint32_t box[3] = {(cuuint32_t)(128 / es), 1, (cuuint32_t)box_rows};
     const cuuint32_t estr[3] = {1, 1, 1};
-    const CUtensorMapDataType dt =
-        dtype == FLASHCK_DTYPE_BFLOAT16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    const CUtensorMapDataType dt = f8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+        : dtype == FLASHCK_DTYPE_BFLOAT16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
     const CUresult r = enc(map, dt, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -1316,9 +1432,10 @@ int launch_t(const FwdParams& p, const Sm100Dev& dev, cudaStream_t stream) {
     if ((rc = make_map_3d(&mq, p.q, p.dtype, rows_q, p.hq, BM, HDIM))) return rc;
     if ((rc = make_map_3d(&mk, p.k, p.dtype, rows_k, p.hkv, box_k, HDIM))) return rc;
     if ((rc = make_map_3d(&mv, p.v, p.dtype, rows_k, p.hkv, box_k, HDIM))) return rc;
-    if ((rc = make_map_o(&mo, p.o, p.dtype, rows_q, p.hq, HDIM))) return rc;
+    if constexpr (ElemInfo<T>::f8) mo = mq;  // (the 8-bit instances write O with plain stores: the map is not used)
+    else if ((rc = make_map_o(&mo, p.o, p.dtype, rows_q, p.hq, HDIM))) return rc;
     auto kern = fmha_fwd_sm100_kernel<T, EXPM, VAR, SPLIT, HDIM>;
-    const size_t smem = 1024 + (size_t)(2 + 2 * KV_SLOTS) * (BM * HDIM * 2) + 8 * STAGE_BYTES + sizeof(Ctrl);
+    const size_t smem = 1024 + (size_t)(2 + 2 * KV_SLOTS) * (BM * HDIM * ElemInfo<T>::bytes) + 8 * STAGE_BYTES + sizeof(Ctrl);
     static thread_local int configured_device = -1;
     int devid = 0;
     FCK_CUDA(cudaGetDevice(&devid));
@@ -1339,6 +1456,10 @@ bool fwd_sm100_supported(const FwdParams& p) {
     if (!g_use_sm100.load()) return false;
     if (p.d != p.dv || (p.d != 128 && p.d != 64)) return false;
     if (p.d == 64 && !g_use_sm100_hdim64.load()) return false;
+    if (p.dtype == FLASHCK_DTYPE_FLOAT8 || p.dtype == FLASHCK_DTYPE_BFLOAT8) {
+        // the 8-bit instances: hdim 128, contiguous K/V, no score additions
+        if (!g_use_sm100_fp8.load() || p.d != 128 || p.bias || p.logits_soft_cap > 0.f || p.block_table || p.kv_indptr) return false;
+    }
     if (p.bias && p.bias_type == 1) return false;  // an elementwise bias tensor: the general instance
     if (p.bias && p.bias_type == 2 && p.bias_rank > 1) return false;
     const bool paged = p.block_table || p.kv_indptr;
@@ -1395,6 +1516,15 @@ int launch_fwd_sm100(const FwdParams& p, cudaStream_t stream) {
     dev.rescale_thr = expm == 1 ? 0.01f * (float)g_rescale_half_x100.load() : kRescaleThreshold;
     dev.scale = p.scale; dev.soft_cap = p.logits_soft_cap;
     dev.alibi = (p.bias && p.bias_type == 2) ? (const float*)p.bias : nullptr; dev.alibi_rank = p.bias_rank;
+    if (p.dtype == FLASHCK_DTYPE_FLOAT8 || p.dtype == FLASHCK_DTYPE_BFLOAT8) {
+        // P must stay within [0, 1] before it is stretched by scale_p (the 8-bit formats saturate a few binades above
+        // scale_p), so the running max follows every increase here instead of lagging by the 16-bit instances' threshold
+        dev.rescale_thr = 0.f;
+        dev.scale_p = p.scale_p; dev.scale_o = p.scale_o; dev.out_dtype = p.out_dtype;
+        const bool e4 = p.dtype == FLASHCK_DTYPE_FLOAT8;
+        if (window) return e4 ? launch_t<f8e4m3_t, 0, 1, 0>(p, dev, stream) : launch_t<f8e5m2_t, 0, 1, 0>(p, dev, stream);
+        return e4 ? launch_t<f8e4m3_t, 0, 0, 0>(p, dev, stream) : launch_t<f8e5m2_t, 0, 0, 0>(p, dev, stream);
+    }
 #define FCK_SM100_LAUNCH(E, V) \
     return bf16 ? launch_t<__nv_bfloat16, E, V, 0>(p, dev, stream) : launch_t<__half, E, V, 0>(p, dev, stream)
     if (p.d == 64) {  // the hdim-64 instances: fp32 exponentials on the exp2 unit, every mask and score addition
@@ -1557,6 +1687,7 @@ static bool valid_exp_mode(int64_t v) { return v == 0 || v == 1 || (v >= 11 && v
 int fwd_set_param(const char* key, int64_t value) {
     if (!strcmp(key, "use_sm100")) { g_use_sm100 = value; return FLASHCK_OK; }
     if (!strcmp(key, "use_sm100_hdim64")) { g_use_sm100_hdim64 = value; return FLASHCK_OK; }
+    if (!strcmp(key, "use_sm100_fp8")) { g_use_sm100_fp8 = value; return FLASHCK_OK; }
     if (!strcmp(key, "use_sm100_splitkv")) { g_use_sm100_splitkv = value; return FLASHCK_OK; }
     if (!strcmp(key, "exp_mode")) {
         if (!valid_exp_mode(value)) return FLASHCK_ERR_INVALID_ARGUMENT;
@@ -1593,6 +1724,7 @@ int fwd_set_param(const char* key, int64_t value) {
 int fwd_get_param(const char* key, int64_t* value) {
     if (!strcmp(key, "use_sm100")) { *value = g_use_sm100; return FLASHCK_OK; }
     if (!strcmp(key, "use_sm100_hdim64")) { *value = g_use_sm100_hdim64; return FLASHCK_OK; }
+    if (!strcmp(key, "use_sm100_fp8")) { *value = g_use_sm100_fp8; return FLASHCK_OK; }
     if (!strcmp(key, "use_sm100_splitkv")) { *value = g_use_sm100_splitkv; return FLASHCK_OK; }
     if (!strcmp(key, "exp_mode")) { *value = g_exp_mode; return FLASHCK_OK; }
     if (!strcmp(key, "exp_mode_splitkv")) { *value = g_exp_mode_splitkv; return FLASHCK_OK; }
