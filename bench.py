@@ -582,15 +582,16 @@ def main():
                                     cu_seqlens_k=w["cu"], max_seqlen_q=w["max_len"], causal=True, out_dtype=torch.bfloat16,
                                     return_lse=True)
 
-        ms_8 = max_over_ranks(time_steps(fp8_step, max(3, steps // 4), 3, barrier))
-        n8 = max(3, steps // 4)
+        n8 = max(3, steps // 2)
+        ms_8 = max_over_ranks(time_steps(fp8_step, n8, 3, barrier))
+        inst8 = _lib.get_instance_param(0, "last_instance")
         t8 = w["flops"] * n8 / (ms_8 * 1e-3) / 1e12
         extra["prefill_fp8"] = {
             "metric": "prefill_fmha_fp8_tflops", "value": total_flops * n8 / (ms_8 * 1e-3) / 1e12, "unit": "TFLOP/s",
             "ms_per_step": ms_8 / n8, "steps": n8, "dtype": "f8e4m3",
             "config": {"workload": "the headline prefill with Q, K, V quantised to E4M3 (static per-tensor scales), P rounded "
-                                   "to E4M3, O in bf16 (FmhaFwdFp8); runs on the general mma.sync instance, which widens "
-                                   "the 8-bit operands to halves in shared memory"},
+                                   "to E4M3 into TMEM, O in bf16 (FmhaFwdFp8): the kind::f8f6f4 instance of the tcgen05 kernel",
+                       "instance": "tcgen05 kind::f8f6f4" if inst8 == 1 else "general (mma.sync on widened halves)"},
             "roofline": {"bound": "tensor", "achieved": t8, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
                          "frac": t8 / peaks["bf16_tflops"], "traffic": None,
                          "peak_source": peaks["source"] + " (burst bf16 GEMM; no 8-bit peak was measured on this pool)"},

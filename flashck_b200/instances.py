@@ -35,7 +35,7 @@ class FmhaProblem:
     select or size an instance (``fmha_fwd_problem.h:59-95``, ``fmha_fwd_split_kv_problem.h``).  Lengths are bucketed to
     powers of two so that neighbouring problems share a record."""
     family: str            # "fmha_fwd" | "fmha_fwd_split_kv"
-    dtype: str             # "fp16" | "bf16"
+    dtype: str             # "fp16" | "bf16" | "fp8" (E4M3) | "bf8" (E5M2)
     mode: str              # "batch" | "group"
     batch: int
     hq: int
@@ -181,10 +181,15 @@ def _why_invalid_fwd(t: FmhaFwdInstance, p: FmhaProblem) -> Optional[str]:
         return f"exp_mode {t.exp_mode} is not built"
     if not 0 <= t.rescale_log2_x100 <= 1400:
         return "rescale_log2_x100 outside [0, 1400]"
-    esize = 2
+    f8 = p.dtype in ("fp8", "bf8")
+    esize = 1 if f8 else 2
+    if f8 and (p.bias != "none" or p.soft_cap):
+        return "the 8-bit element types take no bias and no soft cap"
     if t.pipeline == 1:
         if (t.block_m, t.block_n) != (128, 128) or t.head_dim not in (64, 128):
             return "the tcgen05 instance is built for 128 x 128 tiles at head_dim 128 or 64"
+        if f8 and (t.head_dim != 128 or p.paged or t.exp_mode != 0):
+            return "the kind::f8f6f4 tcgen05 instances: head_dim 128, contiguous K/V, fp32 exponentials on the exp2 unit"
         if t.head_dim == 64 and t.exp_mode != 0:
             return "the hdim-64 tcgen05 instances take their exponentials in fp32 on the exp2 unit"
         if t.kv_stages != 2 or t.softmax_wgs != 2 or t.min_block_per_cu != 1:

@@ -1,5 +1,6 @@
 """Tuner host logic (no GPU): search-space expansion in the reference's JSON form, selection by metric, and the
 SQLite cache round trip."""
+import dataclasses
 import os
 
 import pytest
@@ -48,6 +49,13 @@ def test_instances_validity_names_and_heuristics():
     # hdim 64 has one tcgen05 instance and the general one; a bias tensor has the general instance only
     assert sorted(t.pipeline for t in cands if I.is_valid(t, _prefill_problem(d=64, dv=64))) == [0, 1]
     assert [t.pipeline for t in cands if I.is_valid(t, _prefill_problem(bias="elementwise"))] == [0]
+    # 8-bit operands: the kind::f8f6f4 instance (plain exp2 unit, hdim 128, contiguous) and the general one
+    p8 = dataclasses.replace(p, dtype="fp8")
+    v8 = [t for t in cands if I.is_valid(t, p8)]
+    assert sorted((t.pipeline, t.exp_mode) for t in v8) == [(0, 0), (1, 0)]
+    assert "f8f6f4" in I.why_invalid(I.FmhaFwdInstance(exp_mode=11), p8)
+    assert [t.pipeline for t in cands if I.is_valid(t, dataclasses.replace(p8, paged=True, page=16))] == [0]
+    assert "no bias" in I.why_invalid(I.FmhaFwdInstance(), dataclasses.replace(p8, bias="alibi"))
     # rules of thumb: tensor-memory pipeline with the plain exp2 unit first
     kept = I.heuristic_filter(valid, p)
     assert kept[0].pipeline == 1 and kept[0].exp_mode == 0 and all(t.pipeline == 1 for t in kept)
