@@ -35,6 +35,9 @@ int cuda_fail(cudaError_t e, const char* what) {
     return FLASHCK_ERR_CUDA;
 }
 
+static std::atomic<int64_t> g_use_pdl{1};  // instance parameter "use_pdl"
+bool use_pdl() { return g_use_pdl.load() != 0; }
+
 int sm_count() {
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return 148;
@@ -536,6 +539,7 @@ int FlashckSetInstanceParam(int family, const char* key, int64_t value) {
         return FLASHCK_OK;
     }
     if (family == 0 && !strcmp(key, "log_fallback")) { g_log_fallback = value; return FLASHCK_OK; }
+    if (!strcmp(key, "use_pdl")) { g_use_pdl = value; return FLASHCK_OK; }
     if (family == 0) rc = fwd_set_param(key, value);
     else if (family == 2) rc = split_key_of_sm100(key) ? fwd_set_param(key, value) : splitkv_set_param(key, value);
     if (rc) set_last_error("FlashckSetInstanceParam: unknown family/key %d/%s", family, key);
@@ -548,6 +552,7 @@ int FlashckGetInstanceParam(int family, const char* key, int64_t* value_out) {
     if (family == 0 && !strcmp(key, "bias_rank_info")) { *value_out = g_bias_rank_info; return FLASHCK_OK; }
     if (family == 0 && !strcmp(key, "last_instance")) { *value_out = g_last_fwd_instance; return FLASHCK_OK; }
     if (family == 0 && !strcmp(key, "log_fallback")) { *value_out = g_log_fallback; return FLASHCK_OK; }
+    if (!strcmp(key, "use_pdl")) { *value_out = g_use_pdl; return FLASHCK_OK; }
     if (family == 0) rc = fwd_get_param(key, value_out);
     else if (family == 2) rc = split_key_of_sm100(key) ? fwd_get_param(key, value_out) : splitkv_get_param(key, value_out);
     if (rc) set_last_error("FlashckGetInstanceParam: unknown family/key %d/%s", family, key);

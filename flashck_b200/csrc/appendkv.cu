@@ -9,7 +9,11 @@
 //
 // One CTA per token: CTAs [0, total_new) write K/V rows, CTAs [total_new, total_new + total_q) rotate Q rows.
 // Each rotation pair is read and written by exactly one thread, so the in-place Q update has no hazard.
-// Traffic is a few MB; the kernel is launch-latency bound.
+// Traffic is a few MB; the kernel is bound by its chain of dependent loads, which is kept to three round trips:
+// (1) the token's sequence is found by counting the sequence starts at or below it, one start per thread
+// (__syncthreads_count), not by a binary search of dependent loads; (2) the sequence's length and starts; (3) the
+// block-table entry and the cos/sin row.  The token's own row is read in 16-byte pieces (four or eight rotation pairs
+// per thread) when the rotary width allows it.
 #include "kernels.h"
 
 namespace fck {
@@ -32,17 +36,18 @@ struct AppendDev {
     int64_t total_new, total_q;
     int64_t capacity;  // tokens one sequence's cache can hold: pages_per_sequence * page, or the contiguous row length
     int* status;       // device status word: FLASHCK_STATUS_APPEND_OVERFLOW is ORed in when a token is skipped
+    int vec;           // rows, tables and the rotary width allow the 16-byte form of the rotation
 };
 
-// largest b with seqstart[b] <= t
+// largest b with seqstart[b] <= t, found by the whole CTA: the starts are sorted, so b is the number of entries
+// 1 .. batch-1 at or below t.  Every pass is one round of independent loads (one pass up to 129 sequences).
 __device__ __forceinline__ int find_batch(const int64_t* seqstart, int batch, int64_t t) {
-    int lo = 0, hi = batch - 1;
-    while (lo < hi) {
-        const int mid = (lo + hi + 1) >> 1;
-        if (seqstart[mid] <= t) lo = mid;
-        else hi = mid - 1;
+    int b = 0;
+    for (int base = 1; base < batch; base += (int)blockDim.x) {
+        const int i = base + (int)threadIdx.x;
+        b += __syncthreads_count(i < batch && seqstart[i] <= t);
     }
-    return lo;
+    return b;
 }
 
 template <typename T>
@@ -69,8 +74,70 @@ __device__ __forceinline__ void rope_heads(const T* src, T* dst, int heads, int 
     }
 }
 
+// The same rotation on 16-byte pieces: piece c of a head covers elements [8c, 8c + 8).  Interleaved pairs sit inside a
+// piece (four pairs, cos/sin entries 4c .. 4c+3); half-rotated pairs are piece c of the first half with piece
+// c + half/8 of the second (eight pairs, entries 8c .. 8c+7).  Needs rotary_dim % 8 == 0 (interleaved) or % 16 == 0
+// (half-rotated) and 16-byte aligned rows and tables.  The arithmetic per pair is that of rope_heads.
+template <typename T>
+__device__ __forceinline__ void rope_pair(T x0, T x1, T c_, T s_, T& y0, T& y1) {
+    const float a0 = Elem<T>::to_f32(x0), a1 = Elem<T>::to_f32(x1), c = Elem<T>::to_f32(c_), s = Elem<T>::to_f32(s_);
+    y0 = Elem<T>::from_f32(__fsub_rn(__fmul_rn(a0, c), __fmul_rn(a1, s)));
+    y1 = Elem<T>::from_f32(__fadd_rn(__fmul_rn(a0, s), __fmul_rn(a1, c)));
+}
+union Piece16 {
+    uint4 v;
+    uint2 h[2];
+};
+template <typename T>
+__device__ __forceinline__ void rope_heads_vec(const T* src, T* dst, int heads, int d, int half, int rope_type,
+                                               const T* cosr, const T* sinr, bool copy_tail) {
+    const int rotary_dim = 2 * half, pieces = d / 8;
+    for (int p = threadIdx.x; p < heads * pieces; p += blockDim.x) {
+        const int h = p / pieces, c = p - h * pieces, e0 = 8 * c;
+        const T* srow = src + (int64_t)h * d;
+        T* drow = dst + (int64_t)h * d;
+        if (e0 >= rotary_dim) {
+            if (copy_tail) *reinterpret_cast<uint4*>(drow + e0) = *reinterpret_cast<const uint4*>(srow + e0);
+            continue;
+        }
+        if (rope_type == 1) {
+            Piece16 x, y;
+            uint2 cw, sw;
+            x.v = *reinterpret_cast<const uint4*>(srow + e0);
+            cw = *reinterpret_cast<const uint2*>(cosr + e0 / 2);
+            sw = *reinterpret_cast<const uint2*>(sinr + e0 / 2);
+            const T* xe = reinterpret_cast<const T*>(&x);
+            const T* ce = reinterpret_cast<const T*>(&cw);
+            const T* se = reinterpret_cast<const T*>(&sw);
+            T* ye = reinterpret_cast<T*>(&y);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) rope_pair<T>(xe[2 * i], xe[2 * i + 1], ce[i], se[i], ye[2 * i], ye[2 * i + 1]);
+            *reinterpret_cast<uint4*>(drow + e0) = y.v;
+        } else if (e0 < half) {
+            Piece16 x0, x1, y0, y1, cw, sw;
+            x0.v = *reinterpret_cast<const uint4*>(srow + e0);
+            x1.v = *reinterpret_cast<const uint4*>(srow + e0 + half);
+            cw.v = *reinterpret_cast<const uint4*>(cosr + e0);
+            sw.v = *reinterpret_cast<const uint4*>(sinr + e0);
+            const T* a0 = reinterpret_cast<const T*>(&x0);
+            const T* a1 = reinterpret_cast<const T*>(&x1);
+            const T* ce = reinterpret_cast<const T*>(&cw);
+            const T* se = reinterpret_cast<const T*>(&sw);
+            T* b0 = reinterpret_cast<T*>(&y0);
+            T* b1 = reinterpret_cast<T*>(&y1);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) rope_pair<T>(a0[i], a1[i], ce[i], se[i], b0[i], b1[i]);
+            *reinterpret_cast<uint4*>(drow + e0) = y0.v;
+            *reinterpret_cast<uint4*>(drow + e0 + half) = y1.v;
+        }
+        // (pieces of the second half of a half-rotated head are written by their partners)
+    }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(128) appendkv_kernel(const AppendDev a) {
+    pdl_launch_dependents();  // the split-KV kernel that follows may set itself up while the tokens are written
+    pdl_wait();               // the kernel before this one has completed (no-op after an ordinary launch)
     const int64_t t = blockIdx.x;
     const int half = a.rope_type == 0 ? 0 : a.rotary_dim / 2;
     if (t < a.total_new) {
@@ -107,8 +174,12 @@ __global__ void __launch_bounds__(128) appendkv_kernel(const AppendDev a) {
         }
         const T* ksrc = (const T*)a.knew + t * a.hkv * a.d;
         T* kdst = (T*)a.k_cache + row * a.hkv * a.d;
-        rope_heads<T>(ksrc, kdst, a.hkv, a.d, half, a.rope_type, (const T*)a.cosr + pos * half,
-                      (const T*)a.sinr + pos * half, true);
+        if (a.vec)
+            rope_heads_vec<T>(ksrc, kdst, a.hkv, a.d, half, a.rope_type, (const T*)a.cosr + pos * half,
+                              (const T*)a.sinr + pos * half, true);
+        else
+            rope_heads<T>(ksrc, kdst, a.hkv, a.d, half, a.rope_type, (const T*)a.cosr + pos * half,
+                          (const T*)a.sinr + pos * half, true);
         // V row: 16-byte copies (dv is a multiple of 8)
         const uint4* vsrc = reinterpret_cast<const uint4*>((const T*)a.vnew + t * a.hkv * a.dv);
         uint4* vdst = reinterpret_cast<uint4*>((T*)a.v_cache + row * a.hkv * a.dv);
@@ -133,8 +204,12 @@ __global__ void __launch_bounds__(128) appendkv_kernel(const AppendDev a) {
         n = a.seqstart_knew ? a.seqstart_knew[b + 1] - a.seqstart_knew[b] : a.seqlen_knew;
         const int64_t pos = (int64_t)a.seqlen_k[b] + n - sq + i;
         T* qrow = (T*)a.q + tq * a.hq * a.d;
-        rope_heads<T>(qrow, qrow, a.hq, a.d, half, a.rope_type, (const T*)a.cosr + pos * half,
-                      (const T*)a.sinr + pos * half, false);
+        if (a.vec)
+            rope_heads_vec<T>(qrow, qrow, a.hq, a.d, half, a.rope_type, (const T*)a.cosr + pos * half,
+                              (const T*)a.sinr + pos * half, false);
+        else
+            rope_heads<T>(qrow, qrow, a.hq, a.d, half, a.rope_type, (const T*)a.cosr + pos * half,
+                          (const T*)a.sinr + pos * half, false);
     }
 }
 
@@ -159,14 +234,19 @@ int launch_appendkv(const AppendKVParams& p, cudaStream_t stream) {
     // group mode: the scalar lengths are the packed totals; batch mode: per-sequence lengths
     a.total_new = p.seqstart_knew ? p.seqlen_knew : p.batch * p.seqlen_knew;
     a.total_q = p.seqstart_q ? p.seqlen_q : p.batch * p.seqlen_q;
+    {
+        const auto al16 = [](const void* x) { return (reinterpret_cast<uintptr_t>(x) & 15u) == 0; };
+        const int unit = p.rope_type == 1 ? 8 : 16;  // rotary widths the 16-byte form covers
+        a.vec = (p.rope_type == 0 || p.rotary_dim % unit == 0) && al16(p.q) && al16(p.k_cache) && al16(p.knew) &&
+                (p.rope_type == 0 || (al16(p.rotary_cos) && al16(p.rotary_sin)));
+    }
     const int64_t blocks = a.total_new + (p.rope_type != 0 ? a.total_q : 0);
     if (blocks == 0) return FLASHCK_OK;
     FCK_REQUIRE(blocks < (1ll << 31), FLASHCK_ERR_UNSUPPORTED, "appendkv: too many tokens");
     if (p.dtype == FLASHCK_DTYPE_BFLOAT16)
-        appendkv_kernel<__nv_bfloat16><<<(unsigned)blocks, 128, 0, stream>>>(a);
+        FCK_CUDA(launch_dependent(appendkv_kernel<__nv_bfloat16>, dim3((unsigned)blocks), dim3(128), 0, stream, a));
     else
-        appendkv_kernel<__half><<<(unsigned)blocks, 128, 0, stream>>>(a);
-    FCK_CUDA(cudaGetLastError());
+        FCK_CUDA(launch_dependent(appendkv_kernel<__half>, dim3((unsigned)blocks), dim3(128), 0, stream, a));
     return FLASHCK_OK;
 }
 

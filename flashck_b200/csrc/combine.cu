@@ -40,6 +40,7 @@ struct CombineDev {
 
 template <typename T>
 __global__ void __launch_bounds__(128) combine_kernel(const CombineDev p) {
+    pdl_wait();  // the split kernel's partials are complete and visible (no-op after an ordinary launch)
     const int lane = threadIdx.x & 31;
     const int64_t item = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (item >= p.items) return;
@@ -143,10 +144,10 @@ int launch_combine(const CombineParams& p, cudaStream_t stream) {
     if (d.items == 0) return FLASHCK_OK;
     const int warps = 4;
     const unsigned grid = (unsigned)((d.items + warps - 1) / warps);
-    if (p.dtype == FLASHCK_DTYPE_BFLOAT16) combine_kernel<__nv_bfloat16><<<grid, warps * 32, 0, stream>>>(d);
-    else if (p.dtype == FLASHCK_DTYPE_FLOAT16) combine_kernel<__half><<<grid, warps * 32, 0, stream>>>(d);
-    else combine_kernel<float><<<grid, warps * 32, 0, stream>>>(d);
-    FCK_CUDA(cudaGetLastError());
+    const dim3 g(grid), b(warps * 32);
+    if (p.dtype == FLASHCK_DTYPE_BFLOAT16) FCK_CUDA(launch_dependent(combine_kernel<__nv_bfloat16>, g, b, 0, stream, d));
+    else if (p.dtype == FLASHCK_DTYPE_FLOAT16) FCK_CUDA(launch_dependent(combine_kernel<__half>, g, b, 0, stream, d));
+    else FCK_CUDA(launch_dependent(combine_kernel<float>, g, b, 0, stream, d));
     return FLASHCK_OK;
 }
 

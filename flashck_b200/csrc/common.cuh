@@ -34,6 +34,35 @@ int cuda_fail(cudaError_t e, const char* what);
 // Number of SMs of the current device (cached per device).
 int sm_count();
 
+// Programmatic dependent launch between the kernels of a decode step (append -> split-KV -> merge / exchange).  A kernel
+// launched through launch_dependent() may become resident while the kernel before it in the stream still runs: it sets up
+// its shared memory, barriers and tensor memory, and calls pdl_wait() before it touches global memory -- the wait returns
+// when the kernel before it has completed and its writes are visible.  Every kernel launched this way calls pdl_wait()
+// in all of its threads before any return, so completion stays transitive along the stream.  pdl_launch_dependents()
+// tells the scheduler that the next kernel may be made resident as SM resources allow.  Both are no-ops in a kernel
+// launched the ordinary way.  Instance parameter "use_pdl" (default 1) switches the launch attribute off.
+bool use_pdl();
+#ifdef __CUDACC__
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_dependent(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                    Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = use_pdl() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+#endif
+
 // Device status word of the current device: kernels OR a code into it when a bounded wait runs out.
 // Returns nullptr (and sets the error text) when the address cannot be resolved.
 int* device_status_ptr();

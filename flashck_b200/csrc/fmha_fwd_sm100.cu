@@ -547,6 +547,10 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
             reinterpret_cast<uint4*>(sK)[idx] = make_uint4(0u, 0u, 0u, 0u);
         fence_proxy_async_smem();
     }
+    // Barriers, tensor memory and the cleared slots are this CTA's own; everything below reads global memory, which the
+    // kernel before this one in the stream (an append, the previous step's merge) may still have been writing.
+    pdl_launch_dependents();
+    pdl_wait();
     // ---- schedule: blocks per sequence, then the first work item of every level ----
     for (int b = threadIdx.x; b < p.batch; b += NTHREADS) {
         const int64_t q0 = p.seqstart_q ? p.seqstart_q[b] : (int64_t)b * p.seqlen_q;
@@ -1445,8 +1449,7 @@ int launch_t(const FwdParams& p, const Sm100Dev& dev, cudaStream_t stream) {
     }
     if (p.max_seqlen_q == 0 || p.batch == 0) return FLASHCK_OK;
     // persistent: one CTA per SM walks the device-side work list
-    kern<<<sm_count(), NTHREADS, smem, stream>>>(mq, mk, mv, mo, dev);
-    FCK_CUDA(cudaGetLastError());
+    FCK_CUDA(launch_dependent(kern, dim3(sm_count()), dim3(NTHREADS), smem, stream, mq, mk, mv, mo, dev));
     return FLASHCK_OK;
 }
 
@@ -1606,8 +1609,7 @@ int launch_split_t(const SplitKVParams& p, const Sm100Dev& dev, cudaStream_t str
         FCK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         configured_device = devid;
     }
-    kern<<<sm_count(), NTHREADS, smem, stream>>>(mq, mk, mv, mq, dev);
-    FCK_CUDA(cudaGetLastError());
+    FCK_CUDA(launch_dependent(kern, dim3(sm_count()), dim3(NTHREADS), smem, stream, mq, mk, mv, mq, dev));
     return FLASHCK_OK;
 }
 

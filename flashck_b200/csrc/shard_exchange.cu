@@ -104,6 +104,7 @@ __global__ void __launch_bounds__(kWarps * 32) shard_exchange_kernel(const Shard
     __shared__ float4 part[kWarps][64];  // per warp: its share of sum_s w_s * O_s, dv <= 256 floats
     __shared__ float wsm[kMaxSplits];    // exp(LSE_s - max) of every split
     __shared__ float red[2 * kWarps];
+    pdl_wait();  // the split-KV kernel's partials (and the previous step's header) are complete and visible
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int lr = blockIdx.y;               // local rank played by this CTA
     const int me = p.first_rank + lr;        // its rank in the group
@@ -346,7 +347,14 @@ int FmhaFwdSplitKVShardedCombine(void* const* lse_acc_ptrs, void* const* o_acc_p
         // are resident together (it fails instead of deadlocking when they do not fit)
         FCK_CUDA(cudaLaunchCooperativeKernel(kern, grid, block, args, 0, (cudaStream_t)stream));
     } else {
-        FCK_CUDA(cudaLaunchKernel(kern, grid, block, args, 0, (cudaStream_t)stream));
+        // one rank per launch: the kernel may become resident under the tail of the split-KV kernel before it
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = 0; cfg.stream = (cudaStream_t)stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr; cfg.numAttrs = use_pdl() ? 1 : 0;
+        FCK_CUDA(cudaLaunchKernelExC(&cfg, kern, args));
     }
     return FLASHCK_OK;
 }

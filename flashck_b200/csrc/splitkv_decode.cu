@@ -110,6 +110,10 @@ splitkv_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
         *abort_flag = 0;
         mbar_fence_init();
     }
+    // the kernel before this one in the stream (an append, the previous step's merge) has completed beyond this point;
+    // the merge kernel that follows may take its place on the SMs as their CTAs retire
+    pdl_launch_dependents();
+    pdl_wait();
     // ---- schedule: tiles per sequence, prefix sum (warp 0) ---------------------------------------
     if (warp == 0) {
         int run = 0, mx = 0;
@@ -592,8 +596,7 @@ int launch_inst(const SplitKVParams& p, const DecodeDev& dev_in, cudaStream_t st
     int gx = (int)((int64_t)sm_count() * g_ctas_per_sm_x100.load() / 100);
     if (gx < 1) gx = 1;
     dim3 grid(gx, mtiles, (unsigned)(p.hkv / HK));
-    kern<<<grid, (HK * MT + 1) * 32, smem, stream>>>(mk, mv, dev);
-    FCK_CUDA(cudaGetLastError());
+    FCK_CUDA(launch_dependent(kern, grid, dim3((HK * MT + 1) * 32), smem, stream, mk, mv, dev));
     return FLASHCK_OK;
 }
 

@@ -947,6 +947,56 @@ def test_append_then_decode_config4_small():
     assert_lse_close(lse, lse_ref)
 
 
+def test_dependent_launches_do_not_change_a_serving_loop():
+    """Four append -> split-KV -> merge steps enqueued back to back without a synchronisation, once with programmatic
+    dependent launches (instance parameter use_pdl = 1, the default: each kernel sets itself up under the tail of the one
+    before it) and once with ordinary launches: every step's O and LSE and the final caches are bit for bit the same,
+    and the last step matches the oracle."""
+    dtype = torch.bfloat16
+    b, hq, hkv, d, page, steps = 5, 32, 8, 128, 16, 4
+    lens = uniform_seqlens(b, 300, 2500, seed=24)
+    news = [uniform_seqlens(b, 1, 8, seed=30 + i) for i in range(steps)]
+    cap = [l + sum(n[j] for n in news) for j, l in enumerate(lens)]
+    cache = make_paged_cache(lens, hkv, d, d, page, dtype, seed=17, capacity=cap)
+    cos, sin = rotary_cos_sin(max(cap) + 1, d, dtype)
+    toks = [(normal_tensor((sum(n), hq, d), dtype, 200 + i), normal_tensor((sum(n), hkv, d), dtype, 300 + i),
+             normal_tensor((sum(n), hkv, d), dtype, 400 + i)) for i, n in enumerate(news)]
+    assert _lib.get_instance_param(0, "use_pdl") == 1
+
+    def loop(pdl):
+        _lib.set_instance_param(0, "use_pdl", pdl)
+        try:
+            kd, vd, cur = _cu(cache.k.clone()), _cu(cache.v.clone()), list(lens)
+            outs = []
+            for n, (q, kn, vn) in zip(news, toks):
+                cu_n = _cu(to_seqstarts(n))
+                qd = _cu(q.clone())
+                ops.fmha_fwd_append_kv(qd, kd, vd, _cu(kn), _cu(vn), _cu(torch.tensor(cur, dtype=torch.int32)), _cu(cos), _cu(sin),
+                                       block_table=_cu(cache.block_table), cu_seqlens_q=cu_n, cu_seqlens_knew=cu_n)
+                cur = [c + x for c, x in zip(cur, n)]
+                outs.append(ops.fmha_fwd_splitkv(qd, kd, vd, seqlen_k=_cu(torch.tensor(cur, dtype=torch.int32)),
+                                                 block_table=_cu(cache.block_table), cu_seqlens_q=cu_n, max_seqlen_q=max(n),
+                                                 causal=True, return_lse=True) + (qd,))
+            torch.cuda.synchronize()
+            return outs, kd, vd
+        finally:
+            _lib.set_instance_param(0, "use_pdl", 1)
+
+    outs1, k1, v1 = loop(1)
+    outs0, k0, v0 = loop(0)
+    assert _lib.device_status() == 0
+    assert torch.equal(k1, k0) and torch.equal(v1, v0)
+    for (o1, l1, _), (o0, l0, _) in zip(outs1, outs0):
+        assert torch.equal(o1, o0) and torch.equal(l1, l0)
+    # the last step against the oracle, on the caches the loop left behind
+    n, (o, lse, q_rot) = news[-1], outs1[-1]
+    o_ref, lse_ref = oracle.fmha_fwd(q_rot.cpu(), k1.cpu(), v1.cpu(), seqstart_q=to_seqstarts(n),
+                                     seqlen_k=torch.tensor(cap, dtype=torch.int32), block_table=cache.block_table,
+                                     mask_type=2, window=(-1, 0))
+    assert_o_close(o, o_ref)
+    assert_lse_close(lse, lse_ref)
+
+
 def test_errors_are_loud():
     q = torch.zeros(1, 1, 3, 128, dtype=torch.bfloat16, device=DEV)
     k = torch.zeros(1, 16, 2, 128, dtype=torch.bfloat16, device=DEV)
