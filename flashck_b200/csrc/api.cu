@@ -151,8 +151,8 @@ int run_fwd(const FwdParams& p, cudaStream_t stream) {
     if (g_log_fallback.load())
         fprintf(stderr,
                 "[flashck_b200] forward call on the general (mma.sync) instance: dtype %d, hdim %lld/%lld, batch %lld, max_seqlen_q %lld, "
-                "nhead %lld/%lld, bias_type %d, paged %d page %lld (the tcgen05 instances serve hdim 128 and 64, no elementwise "
-                "bias, batch <= 256, <= 1024 work items per SM, nhead_q <= 1023, pages of 16..128 tokens dividing 128 or "
+                "nhead %lld/%lld, bias_type %d, paged %d page %lld (the tcgen05 instances serve hdim 128 and 64, an elementwise bias "
+                "only at hdim 128 on contiguous K/V, batch <= 256, <= 1024 work items per SM, nhead_q <= 1023, pages of 16..128 tokens dividing 128 or "
                 "multiples; 8-bit operands at hdim 128 with contiguous K/V)\n",
                 p.dtype, (long long)p.d, (long long)p.dv, (long long)p.batch, (long long)p.max_seqlen_q, (long long)p.hq,
                 (long long)p.hkv, p.bias ? p.bias_type : 0, (p.block_table || p.kv_indptr) ? 1 : 0, (long long)p.page);

@@ -257,7 +257,7 @@ fmha_fwd_generic_kernel(const FwdDev p) {
                 if (EXTRA) {
                     const int key = k0 + j * 8 + qlane * 2 + (e & 1), row = (e < 2) ? i0 : i1;
                     float y = s[j][e] * p.scale;
-                    if (p.soft_cap > 0.f) y = p.soft_cap * tanhf(y / p.soft_cap);
+                    if (p.soft_cap > 0.f) y = p.soft_cap * tanh_inline(y / p.soft_cap);
                     if (p.bias_type == 1) {
                         if (row < sq && key < sk) y += Elem<T>::to_f32(bias_el[(int64_t)row * p.bias_sk + key]);
                     } else if (p.bias_type == 2) {

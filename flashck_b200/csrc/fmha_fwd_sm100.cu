@@ -59,6 +59,7 @@ constexpr float kRescaleThreshold = 8.f;  // log2 units; fp32 exponentials: P st
 std::atomic<int64_t> g_rescale_half_x100{200};
 
 std::atomic<int64_t> g_use_sm100{1};
+std::atomic<int64_t> g_use_sm100_bias{1};    // elementwise bias tensors (hdim 128, contiguous) on the tcgen05 instance (0: general)
 std::atomic<int64_t> g_use_sm100_fp8{1};     // 8-bit prefill (hdim 128, contiguous) on the tcgen05 instance (0: general)
 std::atomic<int64_t> g_use_sm100_hdim64{1};  // hdim-64 prefill on the tcgen05 instance (0: on the general one)
 // exponentials of the softmax (template parameter EXPM of the kernel): 0 fp32 on the exp2 unit, 1 packed f16x2 on the
@@ -107,6 +108,12 @@ struct Sm100Dev {
     // O by scale_o; O leaves as out_dtype (a FLASHCK_DTYPE_* code: 8-bit saturating, or 16-bit)
     float scale_p, scale_o;
     int out_dtype;
+    // BIAS instances: an elementwise bias in the element type, planes of bias_sq rows x bias_sk keys (the packed totals in
+    // group mode, where a sequence's block starts at (seqstart_q[b], seqstart_k[b])); rank 0 = one plane, 1 = one per
+    // head, 2 = one per (batch, head) (batch mode only)
+    const void* bias_el;
+    int bias_el_rank;
+    int64_t bias_sk, bias_sq;
 };
 
 // ---- PTX wrappers ---------------------------------------------------------------------------------------------
@@ -226,6 +233,34 @@ template <typename T>
 __device__ __forceinline__ constexpr uint32_t make_idesc(bool b_mn_major, int n = BN) {
     return (1u << 4) | (UmmaFmt<T>::v << 7) | (UmmaFmt<T>::v << 10) | ((b_mn_major ? 1u : 0u) << 16) |
            ((uint32_t)(n >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
+
+// Eight bias values (16 bytes) of one score row starting at element `row + col`, of which the first `nvalid` exist: one
+// 16-byte load when the piece is aligned and whole, element loads (zeros past the end) otherwise.  row == nullptr (a
+// row past the end of its sequence): zeros.
+__device__ __forceinline__ uint4 load_bias_piece(const unsigned short* row, int col, int nvalid) {
+    uint4 r = make_uint4(0u, 0u, 0u, 0u);
+    if (row == nullptr || nvalid <= 0) return r;
+    const unsigned short* ptr = row + col;
+    if (nvalid >= 8 && (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0) return __ldg(reinterpret_cast<const uint4*>(ptr));
+    uint32_t w[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const uint32_t lo = 2 * j < nvalid ? (uint32_t)__ldg(ptr + 2 * j) : 0u;
+        const uint32_t hi = 2 * j + 1 < nvalid ? (uint32_t)__ldg(ptr + 2 * j + 1) : 0u;
+        w[j] = lo | (hi << 16);
+    }
+    return make_uint4(w[0], w[1], w[2], w[3]);
+}
+template <typename T>
+__device__ __forceinline__ float bias_elem(uint32_t w, int hi);
+template <>
+__device__ __forceinline__ float bias_elem<__nv_bfloat16>(uint32_t w, int hi) {
+    return __uint_as_float(hi ? (w & 0xffff0000u) : (w << 16));
+}
+template <>
+__device__ __forceinline__ float bias_elem<__half>(uint32_t w, int hi) {
+    return __half2float(__ushort_as_half((unsigned short)(hi ? (w >> 16) : (w & 0xffffu))));
 }
 
 __device__ __forceinline__ float max3(float a, float b, float c) {
@@ -467,7 +502,14 @@ __device__ __forceinline__ void get_item(const Ctrl* ctrl, const Sm100Dev& p, in
 // VAR bit 1 (EXTRA): the scaled scores get the reference's score additions that need no memory traffic -- a logits soft
 //          cap (cap * tanh(score / cap), core/profiling/attention/fmha_fwd/fmha_fwd_problem.h:81) and ALiBi
 //          (-slope * |i + sk - sq - j|, BiasEnum::ALIBI, fmha_library.h:124) -- applied to the score registers before
-//          the mask; an elementwise bias tensor stays on the general instance.
+//          the mask.
+// VAR bit 2 (BIAS): an elementwise bias tensor (BiasEnum::ELEMENTWISE_BIAS) is added to the scaled (and capped) scores.
+//          A softmax warp fetches the 32 x 128 bias values of its rows and key tile before it waits for S, so the
+//          loads travel under the QK^T: four lanes read 64 contiguous bytes of one row, eight rows per instruction (a
+//          thread reading its own row would touch 32 cache lines per instruction and thrash the small L1 that the
+//          tiles leave).  S is then read 32 columns at a time; the matching 32 x 32 bias block goes through the warp's
+//          2 KB of O staging (free until the epilogue) to the thread that owns the row.  Implies the score arithmetic of
+//          EXTRA.
 // VAR bit 0 (WINDOW): the mask has a left window or a right window other than 0 (everything but no mask / causal); a separate
 // instance, so that the common masks do not carry the second bound of the visible range through the softmax loop.
 // SPLIT 1: the split-KV form described at Sm100Dev (one Q tile per item; work cut as described at kItemCostDefault).  The S
@@ -495,10 +537,12 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     constexpr int ES = ElemInfo<T>::bytes;
     constexpr int HD = HDIM, RB = HD * ES, TILE_BYTES = BM * RB, HB = RB / 128, XB = 128 / ES, KK = 32 / ES;
     static_assert(HDIM == 128 || (HDIM == 64 && SPLIT == 0), "hdim 64 is built for the prefill forms only");
-    static_assert(!F8 || (HDIM == 128 && SPLIT == 0 && (VAR & 2) == 0 && EXPM == 0),
+    static_assert(!F8 || (HDIM == 128 && SPLIT == 0 && (VAR & 6) == 0 && EXPM == 0),
                   "the 8-bit instances: hdim 128, prefill forms, fp32 exponentials, no score additions");
     constexpr bool WINDOW = (VAR & 1) != 0;  // the mask has a second bound (see above)
-    constexpr bool EXTRA = (VAR & 2) != 0;   // ALiBi and / or a logits soft cap on the scaled scores
+    constexpr bool BIAS = (VAR & 4) != 0;    // an elementwise bias tensor on the scaled scores
+    constexpr bool EXTRA = (VAR & 2) != 0 || BIAS;   // ALiBi and / or a logits soft cap on the scaled scores
+    static_assert(!BIAS || (SPLIT == 0 && EXPM == 0 && !F8), "the bias instances are prefill forms with fp32 exponentials");
     constexpr int NPOLY8 = EXPM >= 11 ? EXPM - 10 : 0;
     constexpr bool HEXP = EXPM == 1;
 
@@ -1076,6 +1120,22 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
             if constexpr (EXTRA) {
                 if (p.alibi) slope = p.alibi[(p.alibi_rank ? (int64_t)it.b * p.hq : 0) + head];
             }
+            [[maybe_unused]] const unsigned short* bias_row = nullptr;  // this row's bias values at key 0 of its sequence
+            if constexpr (BIAS) {
+                const int64_t plane = p.bias_sq * p.bias_sk;
+                int64_t off = p.bias_el_rank >= 1 ? (int64_t)head * plane : 0;
+                if (p.seqstart_q) off += (int64_t)(it.q0 + row) * p.bias_sk + it.k0;
+                else off += (p.bias_el_rank == 2 ? (int64_t)it.b * p.hq * plane : 0) + (int64_t)row * p.bias_sk;
+                if (row_ok) bias_row = reinterpret_cast<const unsigned short*>(p.bias_el) + off;
+            }
+            // the rows whose bias this lane fetches: rows 8 i + lane / 4 of the warp, 16-byte piece lane % 4 of each chunk
+            [[maybe_unused]] const unsigned short* fetch_row[BIAS ? 4 : 1];
+            if constexpr (BIAS) {
+#pragma unroll
+                for (int fi = 0; fi < 4; ++fi)
+                    fetch_row[fi] = reinterpret_cast<const unsigned short*>(
+                        __shfl_sync(0xffffffffu, (unsigned long long)bias_row, fi * 8 + (lane >> 2)));
+            }
             for (int n = 0; n < Ni; ++n) {
                 // warp-uniform outcome: the loads, votes and stores below are warp-collective
                 // The split modes have one Q tile and use the other tile's S columns as a second S buffer: the QK^T of
@@ -1084,27 +1144,75 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                 const uint32_t gstep = sc + n;
                 const int sb = SPLIT ? (int)(gstep & 1u) : i;
                 const uint32_t tSb = SPLIT ? lane_addr + sb * 128 : tS;
+                const int key0 = (it.n0 + n) * BN + khalf * 64;
+                [[maybe_unused]] const bool capped = EXTRA && p.soft_cap > 0.f;
+                [[maybe_unused]] const float inv_cap = capped ? 1.f / p.soft_cap : 0.f;
+                [[maybe_unused]] uint4 bw[BIAS ? 16 : 1];  // [chunk of 32 keys][row group]
+                if constexpr (BIAS) {  // (issued before the wait: the bytes arrive while the QK^T runs)
+#pragma unroll
+                    for (int c = 0; c < 4; ++c)
+#pragma unroll
+                        for (int fi = 0; fi < 4; ++fi) {
+                            const int col = key0 + c * 32 + (lane & 3) * 8;
+                            bw[c * 4 + fi] = load_bias_piece(fetch_row[fi], col, sk - col);
+                        }
+                }
                 ok = __all_sync(0xffffffffu, mbar_wait_bounded(&ctrl->s_full[sb], (SPLIT ? (gstep >> 1) : gstep) & 1u, abort_flag,
                                                                p.status, 0x100 << i));
                 if (!ok) break;
                 tc_fence_after();
                 constexpr int NC = SPLIT == 2 ? 64 : 128;  // columns of the row this thread handles
                 uint32_t sreg[NC];
+                if constexpr (BIAS) {
+                    uint8_t* stage = sStage + warp * STAGE_BYTES;  // 32 rows x 64 bytes, 16-byte pieces rotated by row pair
+                    if (n == 0) {  // the previous item's last O store has read the staging buffer
+                        if (lane == 0) tma_store_wait_read();
+                        __syncwarp();
+                    }
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        tmem_ld32(tSb + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&sreg[c * 32]));
+#pragma unroll
+                        for (int fi = 0; fi < 4; ++fi) {
+                            const int r = fi * 8 + (lane >> 2);
+                            *reinterpret_cast<uint4*>(stage + r * 64 + (((lane & 3) ^ (r >> 1)) & 3) * 16) = bw[c * 4 + fi];
+                        }
+                        __syncwarp();
+                        uint32_t mine[16];  // this row's 32 values
+#pragma unroll
+                        for (int v4 = 0; v4 < 4; ++v4) {
+                            const uint4 x = *reinterpret_cast<const uint4*>(stage + lane * 64 + ((v4 ^ (lane >> 1)) & 3) * 16);
+                            mine[4 * v4] = x.x; mine[4 * v4 + 1] = x.y; mine[4 * v4 + 2] = x.z; mine[4 * v4 + 3] = x.w;
+                        }
+                        __syncwarp();  // (the rows are read before the next chunk overwrites them)
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            const float bj = bias_elem<T>(mine[j >> 1], j & 1), sj = __uint_as_float(sreg[c * 32 + j]);
+                            float x;
+                            if (capped) x = (p.soft_cap * tanh_inline(sj * p.scale * inv_cap) + bj) * kLog2e;
+                            else x = fmaf(sj, p.scale_log2, bj * kLog2e);  // (the two products of the sum in base-2 units)
+                            sreg[c * 32 + j] = __float_as_uint(x);
+                        }
+                    }
+                } else {
 #pragma unroll
                 for (int c = 0; c < NC / 32; ++c)
                     tmem_ld32(tSb + khalf * 64 + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&sreg[c * 32]));
                 tmem_wait_ld();
-                const int key0 = (it.n0 + n) * BN + khalf * 64;
-                if constexpr (EXTRA) {
+                }
+                if constexpr (EXTRA && !BIAS) {
                     // score additions on the raw scores, before the mask (which must leave -inf behind): the registers
                     // then hold the finished scores in base-2 units, and the scale below becomes 1
                     const float dist0 = (float)(row + sk - sq - key0);  // i + sk - sq - j at the first column
+                    const float slope_l2 = slope * kLog2e;
 #pragma unroll
                     for (int j = 0; j < NC; ++j) {
-                        float x = __uint_as_float(sreg[j]) * p.scale;
-                        if (p.soft_cap > 0.f) x = p.soft_cap * tanhf(x / p.soft_cap);
-                        x -= slope * fabsf(dist0 - (float)j);
-                        sreg[j] = __float_as_uint(x * 1.4426950408889634f);
+                        const float sj = __uint_as_float(sreg[j]), dj = fabsf(dist0 - (float)j);
+                        float x;
+                        if (capped) x = (p.soft_cap * tanh_inline(sj * p.scale * inv_cap) - slope * dj) * kLog2e;
+                        else x = fmaf(-slope_l2, dj, sj * p.scale_log2);  // (scale, slope and distance in base-2 units)
+                        sreg[j] = __float_as_uint(x);
                     }
                 }
                 // mask the diagonal and tail tiles
@@ -1463,7 +1571,11 @@ bool fwd_sm100_supported(const FwdParams& p) {
         // the 8-bit instances: hdim 128, contiguous K/V, no score additions
         if (!g_use_sm100_fp8.load() || p.d != 128 || p.bias || p.logits_soft_cap > 0.f || p.block_table || p.kv_indptr) return false;
     }
-    if (p.bias && p.bias_type == 1) return false;  // an elementwise bias tensor: the general instance
+    if (p.bias && p.bias_type == 1) {
+        // an elementwise bias tensor: the BIAS instances (hdim 128, contiguous K/V of the stated length, 16-bit elements)
+        if (!g_use_sm100_bias.load() || p.d != 128 || p.block_table || p.kv_indptr || p.bias_rank > 2) return false;
+        if (p.bias_rank == 2 && p.seqstart_q) return false;
+    }
     if (p.bias && p.bias_type == 2 && p.bias_rank > 1) return false;
     const bool paged = p.block_table || p.kv_indptr;
     if (paged) {
@@ -1496,7 +1608,7 @@ bool fwd_sm100_supported(const FwdParams& p) {
 int launch_fwd_sm100(const FwdParams& p, cudaStream_t stream) {
     int* status = device_status_ptr();
     if (!status) return FLASHCK_ERR_CUDA;
-    Sm100Dev dev;
+    Sm100Dev dev{};
     dev.o = p.o; dev.lse = p.lse; dev.seqstart_q = p.seqstart_q; dev.seqstart_k = p.seqstart_k; dev.status = status;
     dev.batch = (int)p.batch; dev.seqlen_q = (int)p.seqlen_q; dev.seqlen_k = (int)p.seqlen_k;
     dev.hq = (int)p.hq; dev.hkv = (int)p.hkv; dev.total_q = (int)p.total_q;
@@ -1514,6 +1626,7 @@ int launch_fwd_sm100(const FwdParams& p, cudaStream_t stream) {
     dev.scale_log2 = p.scale * 1.4426950408889634f;
     const bool bf16 = p.dtype == FLASHCK_DTYPE_BFLOAT16;
     const bool window = p.mask_type != 0 && !(p.wl < 0 && p.wr == 0);
+    const bool ebias = p.bias && p.bias_type == 1;
     const bool extra = (p.bias && p.bias_type == 2) || p.logits_soft_cap > 0.f;
     const int expm = extra ? 0 : (int)g_exp_mode.load();
     dev.rescale_thr = expm == 1 ? 0.01f * (float)g_rescale_half_x100.load() : kRescaleThreshold;
@@ -1527,6 +1640,13 @@ int launch_fwd_sm100(const FwdParams& p, cudaStream_t stream) {
         const bool e4 = p.dtype == FLASHCK_DTYPE_FLOAT8;
         if (window) return e4 ? launch_t<f8e4m3_t, 0, 1, 0>(p, dev, stream) : launch_t<f8e5m2_t, 0, 1, 0>(p, dev, stream);
         return e4 ? launch_t<f8e4m3_t, 0, 0, 0>(p, dev, stream) : launch_t<f8e5m2_t, 0, 0, 0>(p, dev, stream);
+    }
+    if (ebias) {  // (an elementwise bias: fp32 exponentials on the exp2 unit, with or without a second mask bound)
+        dev.rescale_thr = kRescaleThreshold;
+        dev.bias_el = p.bias; dev.bias_el_rank = p.bias_rank;
+        dev.bias_sk = p.seqlen_k; dev.bias_sq = p.seqstart_q ? p.total_q : p.seqlen_q;
+        if (window) return bf16 ? launch_t<__nv_bfloat16, 0, 5, 0>(p, dev, stream) : launch_t<__half, 0, 5, 0>(p, dev, stream);
+        return bf16 ? launch_t<__nv_bfloat16, 0, 4, 0>(p, dev, stream) : launch_t<__half, 0, 4, 0>(p, dev, stream);
     }
 #define FCK_SM100_LAUNCH(E, V) \
     return bf16 ? launch_t<__nv_bfloat16, E, V, 0>(p, dev, stream) : launch_t<__half, E, V, 0>(p, dev, stream)
@@ -1690,6 +1810,7 @@ int fwd_set_param(const char* key, int64_t value) {
     if (!strcmp(key, "use_sm100")) { g_use_sm100 = value; return FLASHCK_OK; }
     if (!strcmp(key, "use_sm100_hdim64")) { g_use_sm100_hdim64 = value; return FLASHCK_OK; }
     if (!strcmp(key, "use_sm100_fp8")) { g_use_sm100_fp8 = value; return FLASHCK_OK; }
+    if (!strcmp(key, "use_sm100_bias")) { g_use_sm100_bias = value; return FLASHCK_OK; }
     if (!strcmp(key, "use_sm100_splitkv")) { g_use_sm100_splitkv = value; return FLASHCK_OK; }
     if (!strcmp(key, "exp_mode")) {
         if (!valid_exp_mode(value)) return FLASHCK_ERR_INVALID_ARGUMENT;
@@ -1727,6 +1848,7 @@ int fwd_get_param(const char* key, int64_t* value) {
     if (!strcmp(key, "use_sm100")) { *value = g_use_sm100; return FLASHCK_OK; }
     if (!strcmp(key, "use_sm100_hdim64")) { *value = g_use_sm100_hdim64; return FLASHCK_OK; }
     if (!strcmp(key, "use_sm100_fp8")) { *value = g_use_sm100_fp8; return FLASHCK_OK; }
+    if (!strcmp(key, "use_sm100_bias")) { *value = g_use_sm100_bias; return FLASHCK_OK; }
     if (!strcmp(key, "use_sm100_splitkv")) { *value = g_use_sm100_splitkv; return FLASHCK_OK; }
     if (!strcmp(key, "exp_mode")) { *value = g_exp_mode; return FLASHCK_OK; }
     if (!strcmp(key, "exp_mode_splitkv")) { *value = g_exp_mode_splitkv; return FLASHCK_OK; }

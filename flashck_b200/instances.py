@@ -201,8 +201,8 @@ def _why_invalid_fwd(t: FmhaFwdInstance, p: FmhaProblem) -> Optional[str]:
         smem = (2 * t.block_m + 2 * t.kv_stages * t.block_n) * t.head_dim * esize + 16 * 1024 + 1024 + 17 * 1024
         if smem > SMEM_PER_CTA:
             return f"tiles, staging and schedule need {smem} bytes of shared memory"
-        if p.bias == "elementwise":
-            return "an elementwise bias tensor runs on the general instance"
+        if p.bias == "elementwise" and (t.head_dim != 128 or p.paged or t.exp_mode != 0):
+            return "the elementwise-bias tcgen05 instances: head_dim 128, contiguous K/V, fp32 exponentials on the exp2 unit"
         if (p.bias != "none" or p.soft_cap) and t.exp_mode != 0:
             return "the score-addition instances (ALiBi, soft cap) take their exponentials in fp32 on the exp2 unit"
         if p.batch > 256 or (p.max_seqlen_q + 127) // 128 > 512 or p.hq > 1023:

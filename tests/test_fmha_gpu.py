@@ -555,8 +555,8 @@ def test_fmha_fwd_bias_alibi_and_soft_cap(dtype, d, kind):
                           alibi_slopes=_cu(slopes) if slopes is not None else None, logits_soft_cap=cap)
     assert_o_close(o, o_ref, kind)
     assert_lse_close(lse, lse_ref, kind)
-    # ALiBi and the soft cap are flags of the tcgen05 softmax; a bias tensor uses the general instance
-    assert _lib.get_instance_param(0, "last_instance") == (0 if "bias" in kind else 1)
+    # ALiBi and the soft cap are flags of the tcgen05 softmax; a bias tensor has tcgen05 instances at hdim 128
+    assert _lib.get_instance_param(0, "last_instance") == (0 if "bias" in kind and d == 64 else 1)
     # the additions change the result (the test would pass vacuously if they were dropped on both sides)
     o_plain, _ = oracle.fmha_fwd(q, k, v, mask_type=2, window=(-1, 0))
     assert (o_plain.float() - o_ref.float()).abs().max() > 0.05
@@ -622,6 +622,42 @@ def test_fmha_fwd_var_len_bias_plane_and_alibi():
                                   alibi_slopes=_cu(slopes))
     assert_o_close(o, o_ref)
     assert_lse_close(lse, lse_ref)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("rank,sq,sk,mask,window,cap", [
+    (1, 300, 512, 2, (-1, 0), 0.0),     # rows of 512 keys: 16-byte loads; the last row block is ragged
+    (2, 256, 640, 0, (-1, -1), 0.0),    # per-batch planes, no mask, whole tiles only
+    (0, 200, 392, 2, (-1, 0), 3.0),     # shared plane, soft cap, sk a multiple of 8 but not of 128 (tail tile by elements)
+    (1, 384, 384, 1, (100, 0), 0.0),    # sliding window: the instance with the second mask bound
+    (1, 130, 259, 2, (-1, 0), 0.0),     # odd key count: every row starts unaligned
+])
+def test_fmha_fwd_elementwise_bias_on_the_tcgen05_instance(dtype, rank, sq, sk, mask, window, cap):
+    """An elementwise bias tensor at hdim 128 runs on the tcgen05 kernel's BIAS instances (each softmax thread reads its
+    row's 128 bias values per key tile): equal to the oracle, and to the general instance on the same call."""
+    b, hq, hkv, d = 2, 4, 2, 128
+    q, k, v = (normal_tensor(sh, dtype, sd) for sh, sd in (((b, sq, hq, d), 31), ((b, sk, hkv, d), 32), ((b, sk, hkv, d), 33)))
+    bias = normal_tensor(((1, 1), (1, hq), (b, hq))[rank] + (sq, sk), dtype, 34)
+    o_ref, lse_ref = oracle.fmha_fwd(q, k, v, mask_type=mask, window=window, bias=bias, logits_soft_cap=cap)
+    kw = dict(return_lse=True, bias=_cu(bias), logits_soft_cap=cap)
+    if mask:
+        kw.update(window_size=window, mask_type=mask)
+
+    def run():
+        return ops.fmha_fwd(_cu(q), _cu(k), _cu(v), **kw)
+    o, lse = run()
+    assert _lib.get_instance_param(0, "last_instance") == 1
+    assert_o_close(o, o_ref)
+    assert_lse_close(lse, lse_ref)
+    _lib.set_instance_param(0, "use_sm100_bias", 0)
+    try:
+        o_gen, lse_gen = run()
+        assert _lib.get_instance_param(0, "last_instance") == 0
+    finally:
+        _lib.set_instance_param(0, "use_sm100_bias", 1)
+    assert_o_close(o, o_gen, "tcgen05 against the general instance")
+    assert_lse_close(lse, lse_gen)
+    assert _lib.device_status() == 0
 
 
 def test_fmha_fwd_bias_pointer_read_as_the_instance_parameters_say():

@@ -46,9 +46,10 @@ def test_instances_validity_names_and_heuristics():
     assert I.why_invalid(I.FmhaFwdInstance(), p) is None
     assert "head_dim" in I.why_invalid(I.FmhaFwdInstance(head_dim=64), p)
     assert "positive" in I.why_invalid(I.FmhaFwdInstance(kv_stages=0), p)
-    # hdim 64 has one tcgen05 instance and the general one; a bias tensor has the general instance only
+    # hdim 64 has one tcgen05 instance and the general one; a bias tensor has a tcgen05 instance at hdim 128 only
     assert sorted(t.pipeline for t in cands if I.is_valid(t, _prefill_problem(d=64, dv=64))) == [0, 1]
-    assert [t.pipeline for t in cands if I.is_valid(t, _prefill_problem(bias="elementwise"))] == [0]
+    assert sorted((t.pipeline, t.exp_mode) for t in cands if I.is_valid(t, _prefill_problem(bias="elementwise"))) == [(0, 0), (1, 0)]
+    assert [t.pipeline for t in cands if I.is_valid(t, _prefill_problem(d=64, dv=64, bias="elementwise"))] == [0]
     # 8-bit operands: the kind::f8f6f4 instance (plain exp2 unit, hdim 128, contiguous) and the general one
     p8 = dataclasses.replace(p, dtype="fp8")
     v8 = [t for t in cands if I.is_valid(t, p8)]
