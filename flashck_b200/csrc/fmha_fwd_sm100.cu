@@ -467,8 +467,9 @@ __device__ __forceinline__ void expand_item(const Ctrl* ctrl, const Sm100Dev& p,
     }
     it.kh = it.h[0] / (p.hq / p.hkv);
     // key tiles each Q tile needs: from the first key its first row sees to the last key its last row sees.  The two
-    // tiles of an item walk the same tiles n0 .. n0+N-1: with paired heads their ranges are equal, and without them a
-    // left window is not served by this instance (n0 = 0).
+    // tiles of an item walk the same tiles n0 .. n0+N-1, n0 being tile 0's first: with paired heads their ranges are
+    // equal; without them (two row blocks of one head) a left window lets tile 1 start one key tile later, and it
+    // walks that tile with every key masked instead (P = 0, running max untouched).
     it.shift = (p.causal == 2) ? it.sk - it.sq : 0;
     it.n0 = 0;
 #pragma unroll
@@ -1588,8 +1589,6 @@ bool fwd_sm100_supported(const FwdParams& p) {
         if ((p.seqstart_q == nullptr) != (p.seqstart_k == nullptr)) return false;
     }
     if (p.mask_type > 3) return false;
-    // a left window needs the two Q tiles of an item to see the same key tiles: paired heads (even GQA ratio)
-    if (p.mask_type != 0 && p.wl >= 0 && (p.hq / p.hkv) % 2 != 0) return false;
     if (p.wl >= (1ll << 30) || p.wr >= (1ll << 30)) return false;
     if (p.batch > kMaxBatch || (p.max_seqlen_q + BM - 1) / BM > kMaxLevels) return false;  // on-chip schedule
     if (p.hq > 1023) return false;

@@ -209,8 +209,6 @@ def _why_invalid_fwd(t: FmhaFwdInstance, p: FmhaProblem) -> Optional[str]:
             return "beyond the on-chip schedule (256 sequences, 512 row blocks, 1023 heads)"
         if p.paged and (p.page < 16 or not (128 % p.page == 0 or p.page % 128 == 0)):
             return "paged K/V needs pages of 16..128 tokens dividing 128, or multiples of 128"
-        if p.mask == "window" and (p.hq // max(p.hkv, 1)) % 2 != 0:
-            return "a left window needs an even GQA ratio on the tcgen05 instance"
     else:
         if (t.block_m, t.block_n) != (64, 64) or t.head_dim not in (64, 128):
             return "the general instance is built for 64 x 64 tiles at head_dim 64 or 128"

@@ -80,8 +80,8 @@ def test_fmha_fwd_hdim128_many_tiles(dtype, sq, sk, mt):
     (257, 257, (1, -1, 100)),     # right window only
 ])
 def test_fmha_fwd_hdim128_window_masks(hq, hkv, sq, sk, mask):
-    # window masks at hdim 128: the tcgen05 instance when the GQA ratio is even (or there is no left window), the
-    # general instance otherwise; both against the oracle
+    # window masks at hdim 128 on the tcgen05 instance, with paired heads (even GQA ratio) and with two row blocks of one
+    # head per work item (odd ratio: the second block walks its first key tile fully masked under a left window)
     dtype = torch.bfloat16
     b, d = 2, 128
     q = normal_tensor((b, sq, hq, d), dtype, 11)
@@ -91,6 +91,7 @@ def test_fmha_fwd_hdim128_window_masks(hq, hkv, sq, sk, mask):
     o_ref, lse_ref = oracle.fmha_fwd(q, k, v, mask_type=mt, window=(wl, wr))
     o, lse = ops.fmha_fwd(_cu(q), _cu(k), _cu(v), window_size=(wl, wr), mask_type=mt, return_lse=True)
     assert _lib.device_status() == 0
+    assert _lib.get_instance_param(0, "last_instance") == 1
     assert_o_close(o, o_ref)
     assert_lse_close(lse, lse_ref)
 
