@@ -1632,9 +1632,14 @@ int launch_fwd_sm100(const FwdParams& p, cudaStream_t stream) {
     dev.scale = p.scale; dev.soft_cap = p.logits_soft_cap;
     dev.alibi = (p.bias && p.bias_type == 2) ? (const float*)p.bias : nullptr; dev.alibi_rank = p.bias_rank;
     if (p.dtype == FLASHCK_DTYPE_FLOAT8 || p.dtype == FLASHCK_DTYPE_BFLOAT8) {
-        // P must stay within [0, 1] before it is stretched by scale_p (the 8-bit formats saturate a few binades above
-        // scale_p), so the running max follows every increase here instead of lagging by the 16-bit instances' threshold
-        dev.rescale_thr = 0.f;
+        // The running max may lag the row max by `thr` (P up to 2^thr) only as far as P * scale_p stays inside the 8-bit
+        // format: thr = log2(largest finite value / scale_p), at most the 16-bit instances' threshold, at least 0 (the
+        // max then follows every increase).  scale_p = 256: 0.8 for E4M3 (max 448), 7.8 for E5M2 (max 57344).
+        {
+            const float fmt_max = p.dtype == FLASHCK_DTYPE_FLOAT8 ? 448.f : 57344.f;
+            const float thr = log2f(fmt_max / p.scale_p);
+            dev.rescale_thr = thr < 0.f ? 0.f : (thr > kRescaleThreshold ? kRescaleThreshold : thr);
+        }
         dev.scale_p = p.scale_p; dev.scale_o = p.scale_o; dev.out_dtype = p.out_dtype;
         const bool e4 = p.dtype == FLASHCK_DTYPE_FLOAT8;
         if (window) return e4 ? launch_t<f8e4m3_t, 0, 1, 0>(p, dev, stream) : launch_t<f8e5m2_t, 0, 1, 0>(p, dev, stream);
