@@ -986,15 +986,20 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                             const uint32_t kc = kv_cnt + n;
                             const int s = kc % KV_SLOTS, s1 = (kc + 1) % KS;           // V slot of this step, K slot of the next
                             const uint32_t ph = (kc / KV_SLOTS) & 1u, ph1 = ((kc + 1) / KS) & 1u;
+                            // V of this step and K of the next have been on their way for more than a step: both
+                            // barriers are looked at here, under the wait for P that follows, because even a passing
+                            // probe costs the issuing thread ~100 clocks -- between PV0 and QK0 those would be idle
+                            // clocks of the tensor pipe
                             if (!(ok = mbar_wait_bounded(&ctrl->v_full[s], ph, abort_flag, p.status, 0x42))) break;
+                            if (n + 1 < N) {
+                                if (!(ok = mbar_wait_bounded(&ctrl->k_full[s1], ph1, abort_flag, p.status, 0x44))) break;
+                            }
                             if (n < N0) {
                                 if (!(ok = mbar_wait_bounded(&ctrl->p_full[0], (sc0 + n) & 1u, abort_flag, p.status, 0x43))) break;
                                 tc_fence_after();
                                 issue_pv(0, s, n > 0);
                                 if (n == N0 - 1) umma_commit(&ctrl->o_full[0]);
-                            }
-                            if (n + 1 < N) {
-                                if (!(ok = mbar_wait_bounded(&ctrl->k_full[s1], ph1, abort_flag, p.status, 0x44))) break;
+                            } else {
                                 tc_fence_after();
                             }
                             if (n + 1 < N0) { issue_qk(0, s1); umma_commit(&ctrl->s_full[0]); }
