@@ -274,6 +274,26 @@ def library_prefill_baselines(w, steps):
     except Exception as e:  # noqa: BLE001 -- a missing backend must not take the bench down
         out["torch_sdpa_cudnn"] = {"unavailable": f"{type(e).__name__}: {str(e)[:120]}"}
     try:
+        # one batched call (4 x 4096 tokens, the head geometry of config 2): the library kernel without its 16 launches,
+        # next to this repository's kernel on the same tensors
+        import torch.nn.functional as F
+        from torch.nn.attention import SDPBackend, sdpa_kernel
+        from flashck_b200 import ops
+        b, L = 4, 4096
+        g = torch.Generator(device=w["q"].device).manual_seed(99)
+        q, k, v = (torch.randn(b, L, h, D, generator=g, device=w["q"].device, dtype=torch.float32).to(torch.bfloat16)
+                   for h in (HQ, HKV, HKV))
+        qt, kt, vt = (x.transpose(1, 2) for x in (q, k, v))
+        fl = 4.0 * D * HQ * b * L * (L + 1) / 2
+        ms_own = time_steps(lambda: ops.fmha_fwd(q, k, v, causal=True, return_lse=True), steps, 3) / steps
+        with sdpa_kernel(SDPBackend.CUDNN_ATTENTION):
+            ms_lib = time_steps(lambda: F.scaled_dot_product_attention(qt, kt, vt, is_causal=True, enable_gqa=True), steps, 3) / steps
+        out["batched_4x4096_causal"] = {"this_repo": {"ms": ms_own, "tflops": fl / ms_own / 1e9},
+                                        "torch_sdpa_cudnn": {"ms": ms_lib, "tflops": fl / ms_lib / 1e9}}
+        del q, k, v, qt, kt, vt
+    except Exception as e:  # noqa: BLE001
+        out["batched_4x4096_causal"] = {"unavailable": f"{type(e).__name__}: {str(e)[:120]}"}
+    try:
         from flash_attn import flash_attn_varlen_func
         cu32 = w["cu"].to(torch.int32)
 
