@@ -321,11 +321,21 @@ FLASHCK_API int FmhaFwdSplitKVStatic(void* q_buf_ptr, void* k_buf_ptr, void* v_b
 /*
  * Instance selection (the reference picks a tile instance per problem through its tuner,
  * core/profiling/attention/fmha_fwd/fmha_fwd_emitter.cc:325-466).  `family`: 0 fmha_fwd, 2 fmha_fwd_split_kv
- * (FmhaKind values, fmha_library.h:17-25).  Keys: family 0 -- "use_sm100" (1: hdim-128 problems run on the tcgen05
- * instance, 0: on the general one), "poly8" (0 or 3: column pairs of every 8 whose exp2 is a polynomial);
- * family 2 -- "stages" (0 = as many as fit), "ctas_per_sm_x100", "use_sm100_splitkv" (1: calls with more than 16
- * query rows per kv head run on the tcgen05 instance).  Unknown keys return FLASHCK_ERR_INVALID_ARGUMENT.
- * Process-wide, set before launching; not thread-safe against launches.
+ * (FmhaKind values, fmha_library.h:17-25).  Keys, all process-wide integers:
+ *   family 0 -- "use_sm100" (1: the tcgen05 instances serve what they can, 0: everything on the general instance),
+ *     "use_sm100_hdim64", "use_sm100_fp8", "use_sm100_bias" (1: hdim 64 / 8-bit operands / elementwise bias tensors on
+ *     their tcgen05 instances, 0: on the general one), "exp_mode" (0: fp32 exponentials on the exp2 unit; 1: packed
+ *     f16x2; 11, 12, 13: 1, 2 or 3 of every 8 column pairs on an FMA-pipe polynomial), "rescale_log2_x100" (lag of the
+ *     running max for exp_mode 1), "poly8" (read-only view of the polynomial share), "bias_enum" / "bias_rank_info"
+ *     (meaning of the bias pointer of the reference-shaped FmhaFwd symbol), "log_fallback" (1: a call that leaves the
+ *     tcgen05 instances says why on stderr), "last_instance" (read-only: 1 if the last forward call ran on a tcgen05
+ *     instance);
+ *   family 2 -- "stages" (0 = as many as fit), "ctas_per_sm_x100", "heads_per_cta", "row_tiles" (decode kernel tiling; 0 =
+ *     chosen per call), "use_sm100_splitkv" (1: calls with more than 16 query rows per kv head run on the tcgen05 split
+ *     modes), "exp_mode_splitkv", "split_item_cost", "split_min_piece_tiles" (work cut of the split modes);
+ *   any family -- "use_pdl" (1: the kernels of a decode step and the prefill kernel are launched as programmatic
+ *     dependents of the kernel before them in the stream, see csrc/common.cuh).
+ * Unknown keys return FLASHCK_ERR_INVALID_ARGUMENT.  Set before launching; not thread-safe against launches.
  */
 FLASHCK_API int FlashckSetInstanceParam(int family, const char* key, int64_t value);
 FLASHCK_API int FlashckGetInstanceParam(int family, const char* key, int64_t* value_out);
