@@ -156,3 +156,50 @@ def test_config4_full_size_append_then_decode_both_instances_and_oracle_on_short
         o_ref, lse_ref = oracle.fmha_fwd(q_rot[sl].cpu()[None], k[None], v[None], mask_type=2, window=(-1, 0))
         assert_o_close(o[sl], o_ref[0], f"sequence {b} against the oracle")
         assert_lse_close(lse[:, sl], lse_ref[0], f"LSE of sequence {b} against the oracle")
+
+
+def test_config2_full_size_on_8bit_operands_instances_agree_and_sampled_rows_match_the_oracle():
+    """BASELINE config 2 quantised to E4M3 (the bench's 8-bit leg): the kind::f8f6f4 tcgen05 instance against the general
+    instance on the whole problem, and against the oracle on sampled rows of the longest sequence (a causal row is an
+    unmasked attention of one query over the keys before it).  Bound: one 8-bit unit of P per key, i.e. the attention of
+    the same weights over |V| (see tests/test_fp8_gpu.py)."""
+    bench = _bench()
+    dev = torch.device("cuda:0")
+    w = bench.make_prefill(1234, dev)
+    dtype = torch.float8_e4m3fn
+    (q8, dq), (k8, dk), (v8, dv8) = (ops.quantize_fp8(w[n], dtype) for n in ("q", "k", "v"))
+    scale_s, scale_p = dq * dk / 128 ** 0.5, 256.0
+    scale_o = dv8 / scale_p
+
+    def run():
+        return ops.fmha_fwd_fp8(q8, k8, v8, scale_s=scale_s, scale_p=scale_p, scale_o=scale_o, cu_seqlens_q=w["cu"],
+                                cu_seqlens_k=w["cu"], max_seqlen_q=w["max_len"], causal=True, out_dtype=torch.bfloat16,
+                                return_lse=True)
+    o, lse = run()
+    assert _lib.get_instance_param(0, "last_instance") == 1
+    _lib.set_instance_param(0, "use_sm100_fp8", 0)
+    try:
+        o_gen, lse_gen = run()
+        assert _lib.get_instance_param(0, "last_instance") == 0
+    finally:
+        _lib.set_instance_param(0, "use_sm100_fp8", 1)
+    assert _lib.device_status() == 0
+    assert torch.isfinite(o.float()).all()
+    assert_lse_close(lse, lse_gen, "LSE, tcgen05 8-bit instance against the general one")
+    # both round P to 8 bits relative to their own running maximum: two units of P apart at most, measured against |O|
+    # of the weights over |V| -- bounded here by the mean magnitude of V's rows times two units (a loose global bound)
+    diff = (o.float() - o_gen.float()).abs()
+    assert float(diff.max()) < 0.25 and float(diff.mean()) < 0.01
+    cu = w["cu"].cpu()
+    b = _longest(w["lens"], 1)[0]
+    s0, L = int(cu[b]), w["lens"][b]
+    qb, kb, vb = (t[s0:s0 + L].cpu() for t in (q8, k8, v8))
+    o_c, lse_c = o.cpu(), lse.cpu()
+    kw = dict(scale_s=scale_s, scale_p=scale_p, scale_o=scale_o, mask_type=0, window=(-1, -1), out_dtype=torch.bfloat16)
+    for i in _sample_rows(L, 10, seed=5):
+        kk, vv = kb[None, :i + 1].contiguous(), vb[None, :i + 1].contiguous()
+        o_ref, lse_ref = oracle.fmha_fwd_fp8(qb[i:i + 1][None], kk, vv, **kw)
+        o_abs, _ = oracle.fmha_fwd_fp8(qb[i:i + 1][None], kk, vv.float().abs().to(dtype), **kw)
+        err = (o_c[s0 + i].float() - o_ref[0, 0].float()).abs()
+        assert bool((err <= 2.0 ** -3 * o_abs[0, 0].float() + 1e-2).all()), f"row {i}: max err {float(err.max()):.4g}"
+        assert_lse_close(lse_c[:, s0 + i], lse_ref[0, :, 0], f"LSE of row {i}")
