@@ -732,8 +732,12 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     if (warp >= 8) {
         // Register budget.  The CTA is launched with 384 x 168 = 64512 registers; setmaxnreg.dec returns registers
         // to the CTA's pool and setmaxnreg.inc waits -- without a bound -- until the pool can serve it, so the sum
-        // after the moves must stay below the launch allocation: 256 x 208 + 128 x 80 = 63488.
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 80;\n" ::);
+        // after the moves must not exceed the launch allocation.  Prefill forms: 256 x 208 + 128 x 88 = 64512, the
+        // whole pool -- at 80 registers the producer and the issuing thread spill ~90 bytes, which costs the kernel
+        // 1-2 % (the issuing thread's time between MMAs is idle time of the tensor pipe); the softmax warps would need
+        // 216 to be free of spills, which the pool does not hold.  Split modes: 256 x 208 + 128 x 80.
+        if constexpr (SPLIT == 0) asm volatile("setmaxnreg.dec.sync.aligned.u32 88;\n" ::);
+        else asm volatile("setmaxnreg.dec.sync.aligned.u32 80;\n" ::);
         // In the split modes a step is short and the copies are many small boxes whose issue takes a warp a good part
         // of it, so K, V and Q have a producer warp each (9, 10, 11): the K producer then runs ahead into the next item
         // (its first page-id lookup is a round trip to memory) instead of waiting for the Q buffer, which frees late.
