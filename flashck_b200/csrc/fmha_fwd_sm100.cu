@@ -157,6 +157,11 @@ __device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64
             "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(acc)
             : "memory");
 }
+__device__ __forceinline__ bool elect_one_sync() {  // true in exactly one lane of a converged warp
+    uint32_t pred;
+    asm volatile("{\n.reg .pred p;\nelect.sync _|p, 0xffffffff;\nselp.u32 %0, 1, 0, p;\n}\n" : "=r"(pred));
+    return pred != 0;
+}
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_u32(bar))
                  : "memory");
@@ -904,21 +909,27 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
             const uint64_t dK0 = make_smem_desc(smem_u32(sK), 0, 1024);
             const uint64_t dV0 = make_smem_desc(smem_u32(sV), HALF_BYTES, 1024);
             const uint64_t dV1 = make_smem_desc(smem_u32(sV + TILE_BYTES), HALF_BYTES, 1024);
+            const bool leader = elect_one_sync();  // (the prefill forms; the split modes run on lane 0 below)
+            auto commit = [&](uint64_t* bar) { if (leader) umma_commit(bar); };
             auto issue_qk = [&](int i, int s) {  // S_i = Q_i K^T : 8 steps of 16 along the head dim
                 const uint64_t qd = i ? dQ1 : dQ0, kd = dK0 + (uint64_t)((s * TILE_BYTES) >> 4);
                 const uint32_t d = tS[i];
+                if (leader) {
 #pragma unroll
-                for (int ks = 0; ks < RB / 32; ++ks) {
-                    const uint64_t off = (uint64_t)(((ks / 4) * HALF_BYTES + (ks % 4) * 32) >> 4);
-                    umma_ss<F8>(d, qd + off, kd + off, idesc_qk, ks > 0 ? 1u : 0u);
+                    for (int ks = 0; ks < RB / 32; ++ks) {
+                        const uint64_t off = (uint64_t)(((ks / 4) * HALF_BYTES + (ks % 4) * 32) >> 4);
+                        umma_ss<F8>(d, qd + off, kd + off, idesc_qk, ks > 0 ? 1u : 0u);
+                    }
                 }
             };
             auto issue_pv = [&](int i, int s, bool accumulate) {  // O_i += P_i V : 8 steps of 16 keys
                 const uint64_t vd = s ? dV1 : dV0;
                 const uint32_t d = tO[i], a = tS[i];
+                if (leader) {
 #pragma unroll
-                for (int ks = 0; ks < BN / KK; ++ks)  // KK keys = KK rows of 128 bytes of the V tile, 8 columns of P
-                    umma_ts<F8>(d, a + ks * 8, vd + (uint64_t)((ks * KK * 128) >> 4), idesc_pv, (accumulate || ks > 0) ? 1u : 0u);
+                    for (int ks = 0; ks < BN / KK; ++ks)  // KK keys = KK rows of 128 bytes of the V tile, 8 columns of P
+                        umma_ts<F8>(d, a + ks * 8, vd + (uint64_t)((ks * KK * 128) >> 4), idesc_pv, (accumulate || ks > 0) ? 1u : 0u);
+                }
             };
             // split modes: tile 0's Q against S buffer `buf` (the S columns of either tile), P read from the same buffer
             auto issue_qk_to = [&](uint32_t buf, int s) {
@@ -959,7 +970,11 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                     sc0 += N;
                     ++q_cnt;
                 }
-            } else if (lane == 0) {  // the whole loop is one thread's; an item with N == 0 is skipped by every role
+            } else if (!SPLIT) {
+                // All 32 lanes walk the loop and poll the barriers together; one elected lane issues the MMAs and the
+                // commits.  The control flow, the counters and the descriptors are then the same in every lane, which
+                // lets them live in the warp's uniform registers instead of one thread's vector registers (an item with
+                // N == 0 is skipped by every role).
                 int N = 0, N0 = 0, N1 = 0;
                 if (rounds > 0) {
                     Item it;
@@ -975,10 +990,10 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                              mbar_wait_bounded(&ctrl->k_full[s0], (kv_cnt / KS) & 1u, abort_flag, p.status, 0x41);
                         if (ok) {
                             tc_fence_after();
-                            if (N0 > 0) { issue_qk(0, s0); umma_commit(&ctrl->s_full[0]); }
-                            if (N1 > 0) { issue_qk(1, s0); umma_commit(&ctrl->s_full[1]); }
-                            umma_commit(&ctrl->k_empty[s0]);
-                            if (N == 1) umma_commit(&ctrl->q_empty);  // Q may be replaced once these MMAs are done
+                            if (N0 > 0) { issue_qk(0, s0); commit(&ctrl->s_full[0]); }
+                            if (N1 > 0) { issue_qk(1, s0); commit(&ctrl->s_full[1]); }
+                            commit(&ctrl->k_empty[s0]);
+                            if (N == 1) commit(&ctrl->q_empty);  // Q may be replaced once these MMAs are done
                         }
                         // the step counts of the next item, worked out while the first softmax of this one runs
                         if (rnd + 1 < rounds) {
@@ -1002,21 +1017,21 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                                 if (!(ok = mbar_wait_bounded(&ctrl->p_full[0], (sc0 + n) & 1u, abort_flag, p.status, 0x43))) break;
                                 tc_fence_after();
                                 issue_pv(0, s, n > 0);
-                                if (n == N0 - 1) umma_commit(&ctrl->o_full[0]);
+                                if (n == N0 - 1) commit(&ctrl->o_full[0]);
                             } else {
                                 tc_fence_after();
                             }
-                            if (n + 1 < N0) { issue_qk(0, s1); umma_commit(&ctrl->s_full[0]); }
+                            if (n + 1 < N0) { issue_qk(0, s1); commit(&ctrl->s_full[0]); }
                             if (n < N1) {
                                 if (!(ok = mbar_wait_bounded(&ctrl->p_full[1], (sc1 + n) & 1u, abort_flag, p.status, 0x45))) break;
                                 tc_fence_after();
                                 issue_pv(1, s, n > 0);
-                                if (n == N1 - 1) umma_commit(&ctrl->o_full[1]);
+                                if (n == N1 - 1) commit(&ctrl->o_full[1]);
                             }
-                            umma_commit(&ctrl->v_empty[s]);
-                            if (n + 1 < N1) { issue_qk(1, s1); umma_commit(&ctrl->s_full[1]); }
-                            if (n + 1 < N) umma_commit(&ctrl->k_empty[s1]);
-                            if (n + 2 == N) umma_commit(&ctrl->q_empty);  // the last QK^T of the item has been issued
+                            commit(&ctrl->v_empty[s]);
+                            if (n + 1 < N1) { issue_qk(1, s1); commit(&ctrl->s_full[1]); }
+                            if (n + 1 < N) commit(&ctrl->k_empty[s1]);
+                            if (n + 2 == N) commit(&ctrl->q_empty);  // the last QK^T of the item has been issued
                         }
                         kv_cnt += N;
                         sc0 += N0;
