@@ -909,7 +909,7 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
             const uint64_t dK0 = make_smem_desc(smem_u32(sK), 0, 1024);
             const uint64_t dV0 = make_smem_desc(smem_u32(sV), HALF_BYTES, 1024);
             const uint64_t dV1 = make_smem_desc(smem_u32(sV + TILE_BYTES), HALF_BYTES, 1024);
-            const bool leader = elect_one_sync();  // (the prefill forms; the split modes run on lane 0 below)
+            const bool leader = elect_one_sync();
             auto commit = [&](uint64_t* bar) { if (leader) umma_commit(bar); };
             auto issue_qk = [&](int i, int s) {  // S_i = Q_i K^T : 8 steps of 16 along the head dim
                 const uint64_t qd = i ? dQ1 : dQ0, kd = dK0 + (uint64_t)((s * TILE_BYTES) >> 4);
@@ -934,16 +934,18 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
             // split modes: tile 0's Q against S buffer `buf` (the S columns of either tile), P read from the same buffer
             auto issue_qk_to = [&](uint32_t buf, int s) {
                 const uint64_t kd = dK0 + (uint64_t)((s * TILE_BYTES) >> 4);
+                if (leader) {
 #pragma unroll
-                for (int ks = 0; ks < RB / 32; ++ks) {
-                    const uint64_t off = (uint64_t)(((ks / 4) * HALF_BYTES + (ks % 4) * 32) >> 4);
-                    umma_ss<F8>(tS[0] + buf * 128, dQ0 + off, kd + off, idesc_qk, ks > 0 ? 1u : 0u);
+                    for (int ks = 0; ks < RB / 32; ++ks) {
+                        const uint64_t off = (uint64_t)(((ks / 4) * HALF_BYTES + (ks % 4) * 32) >> 4);
+                        umma_ss<F8>(tS[0] + buf * 128, dQ0 + off, kd + off, idesc_qk, ks > 0 ? 1u : 0u);
+                    }
                 }
             };
             // running counts give ring slots and barrier parities across work items
             uint32_t kv_cnt = 0, q_cnt = 0, sc0 = 0, sc1 = 0;
-            if (SPLIT && lane == 0) {
-                // Split modes: this thread issues only the QK^T, warp 4's first thread the PV (the warps of tile 1's
+            if (SPLIT) {
+                // Split modes: this warp issues only the QK^T (all lanes walk the loop, the elected one issues), warp 4 the PV (the warps of tile 1's
                 // softmax warpgroup have nothing else to do there).  Each polls its own barriers while the other's
                 // block of MMAs runs, which a single issuer could not do (the tensor pipe takes instructions only about
                 // one ahead).  The two S buffers are handed back by pv_done: S of step g goes into buffer g & 1 once
@@ -961,9 +963,9 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                         if (g >= 2 && !(ok = mbar_wait_bounded(&ctrl->pv_done[b], ((g >> 1) + 1u) & 1u, abort_flag, p.status, 0x44))) break;
                         tc_fence_after();
                         issue_qk_to(b, s);
-                        umma_commit(&ctrl->s_full[b]);
-                        umma_commit(&ctrl->k_empty[s]);
-                        if (n + 1 == N) umma_commit(&ctrl->q_empty);  // Q may be replaced once these MMAs are done
+                        commit(&ctrl->s_full[b]);
+                        commit(&ctrl->k_empty[s]);
+                        if (n + 1 == N) commit(&ctrl->q_empty);  // Q may be replaced once these MMAs are done
                     }
                     if (!ok) break;
                     kv_cnt += N;
@@ -1061,7 +1063,8 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
             // (the QK^T come from warp 8): O += P V from S/P buffer g & 1 once V has landed and the softmax has
             // handed P over, then pv_done tells the softmax (which may rescale O) and the QK^T issuer (which may
             // overwrite the buffer) that this product is complete.
-            if (warp == 4 && lane == 0) {
+            if (warp == 4) {  // (all lanes walk the loop, the elected one issues)
+                const bool lead4 = elect_one_sync();
                 constexpr uint32_t idesc_pv = make_idesc<T>(true);
                 const uint64_t dV0 = make_smem_desc(smem_u32(sV), HALF_BYTES, 1024);
                 const uint64_t dV1 = make_smem_desc(smem_u32(sV + TILE_BYTES), HALF_BYTES, 1024);
@@ -1078,13 +1081,15 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                         if (!(ok = mbar_wait_bounded(&ctrl->p_full[b], (g >> 1) & 1u, abort_flag, p.status, 0x43))) break;
                         tc_fence_after();
                         const uint64_t vd = s ? dV1 : dV0;
+                        if (lead4) {
 #pragma unroll
-                        for (int ks = 0; ks < BN / 16; ++ks)
-                            umma_ts(tmem + 256, tmem + b * 128 + ks * 8, vd + (uint64_t)((ks * 2048) >> 4), idesc_pv,
-                                    (n > 0 || ks > 0) ? 1u : 0u);
-                        umma_commit(&ctrl->pv_done[b]);
-                        if (n + 1 == N) umma_commit(&ctrl->o_full[0]);
-                        umma_commit(&ctrl->v_empty[s]);
+                            for (int ks = 0; ks < BN / 16; ++ks)
+                                umma_ts(tmem + 256, tmem + b * 128 + ks * 8, vd + (uint64_t)((ks * 2048) >> 4), idesc_pv,
+                                        (n > 0 || ks > 0) ? 1u : 0u);
+                            umma_commit(&ctrl->pv_done[b]);
+                            if (n + 1 == N) umma_commit(&ctrl->o_full[0]);
+                            umma_commit(&ctrl->v_empty[s]);
+                        }
                     }
                     kv_cnt += N;
                 }
