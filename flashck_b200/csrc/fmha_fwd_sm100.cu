@@ -349,6 +349,7 @@ struct Ctrl {
     uint64_t q_full, q_empty;
     uint64_t k_full[3], k_empty[3], v_full[KV_SLOTS], v_empty[KV_SLOTS];  // (the split modes use a third K slot)
     uint64_t s_full[2], p_full[2], o_full[2];
+    uint64_t p_full2[2];  // prefill forms: the second half of P (keys 64-127) has been written (p_full: the first half)
     uint64_t pv_done[2];  // split modes: the PV that read S/P buffer b is complete (buffer b may take the next S)
     uint64_t v_tail;      // paged V: the copies of a tile that holds the end of its sequence (cleaned up before v_full)
     uint32_t tmem_base;
@@ -529,6 +530,9 @@ __device__ __forceinline__ void get_item(const Ctrl* ctrl, const Sm100Dev& p, in
 // EXPM: how the softmax takes its exponentials.  0: one fp32 exp2 per element on the exp2 unit; 1: two per issue
 //       through the unit's packed f16x2 form (see pack_f16x2); 11, 12, 13: fp32, with 1, 2 or 3 of every 8 column pairs
 //       on a polynomial on the FMA pipe instead.
+#ifndef FCK_P_HALVES
+#define FCK_P_HALVES 1
+#endif
 template <typename T, int EXPM, int VAR, int SPLIT, int HDIM = 128>
 __global__ void __launch_bounds__(NTHREADS, 1)
 fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -551,6 +555,7 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     static_assert(!BIAS || (SPLIT == 0 && EXPM == 0 && !F8), "the bias instances are prefill forms with fp32 exponentials");
     constexpr int NPOLY8 = EXPM >= 11 ? EXPM - 10 : 0;
     constexpr bool HEXP = EXPM == 1;
+    constexpr bool HALVES = FCK_P_HALVES != 0 && SPLIT == 0;  // P reaches the PV in two halves of 64 keys
 
     // ---- shared memory carve-up ----
     const uint32_t raw = smem_u32(smem_raw);
@@ -580,6 +585,7 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         for (int i = 0; i < 2; ++i) {
             mbar_init(&ctrl->s_full[i], 1);
             mbar_init(&ctrl->p_full[i], 4);  // one arrival per softmax warp
+            mbar_init(&ctrl->p_full2[i], 4);
             mbar_init(&ctrl->o_full[i], 1);
             mbar_init(&ctrl->pv_done[i], 1);
         }
@@ -910,6 +916,12 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
             const uint64_t dV0 = make_smem_desc(smem_u32(sV), HALF_BYTES, 1024);
             const uint64_t dV1 = make_smem_desc(smem_u32(sV + TILE_BYTES), HALF_BYTES, 1024);
             const bool leader = elect_one_sync();
+            // A wait of the convergent issuing warp: every lane probes, all leave together with one outcome.  Without the
+            // vote a lane could fall two phases of a barrier behind the elected one and then read the parity of a
+            // later phase as "not complete yet".
+            auto wait_all = [&](uint64_t* bar, uint32_t parity, volatile int* af, int* st, int code) {
+                return __all_sync(0xffffffffu, mbar_wait_bounded(bar, parity, af, st, code)) != 0;
+            };
             auto commit = [&](uint64_t* bar) { if (leader) umma_commit(bar); };
             auto issue_qk = [&](int i, int s) {  // S_i = Q_i K^T : 8 steps of 16 along the head dim
                 const uint64_t qd = i ? dQ1 : dQ0, kd = dK0 + (uint64_t)((s * TILE_BYTES) >> 4);
@@ -922,13 +934,22 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                     }
                 }
             };
-            auto issue_pv = [&](int i, int s, bool accumulate) {  // O_i += P_i V : 8 steps of 16 keys
+            // O_i += P_i V : 8 steps of 16 keys; `part` 0 / 1 = the steps of keys 0-63 / 64-127, 2 = all of them
+            auto issue_pv = [&](int i, int s, bool accumulate, int part = 2) {
                 const uint64_t vd = s ? dV1 : dV0;
                 const uint32_t d = tO[i], a = tS[i];
+                constexpr int STEPS = BN / KK;
                 if (leader) {
+                    if (part != 1) {
 #pragma unroll
-                    for (int ks = 0; ks < BN / KK; ++ks)  // KK keys = KK rows of 128 bytes of the V tile, 8 columns of P
-                        umma_ts<F8>(d, a + ks * 8, vd + (uint64_t)((ks * KK * 128) >> 4), idesc_pv, (accumulate || ks > 0) ? 1u : 0u);
+                        for (int ks = 0; ks < STEPS / 2; ++ks)  // KK keys = KK rows of 128 bytes of the V tile, 8 columns of P
+                            umma_ts<F8>(d, a + ks * 8, vd + (uint64_t)((ks * KK * 128) >> 4), idesc_pv, (accumulate || ks > 0) ? 1u : 0u);
+                    }
+                    if (part != 0) {
+#pragma unroll
+                        for (int ks = STEPS / 2; ks < STEPS; ++ks)
+                            umma_ts<F8>(d, a + ks * 8, vd + (uint64_t)((ks * KK * 128) >> 4), idesc_pv, 1u);
+                    }
                 }
             };
             // split modes: tile 0's Q against S buffer `buf` (the S columns of either tile), P read from the same buffer
@@ -955,12 +976,12 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                     get_item<SPLIT>(ctrl, p, rnd, total_items, lane, it);
                     if (!it.valid || it.N == 0) continue;
                     const int N = it.N;
-                    bool ok = mbar_wait_bounded(&ctrl->q_full, q_cnt & 1u, abort_flag, p.status, 0x40);
+                    bool ok = wait_all(&ctrl->q_full, q_cnt & 1u, abort_flag, p.status, 0x40);
                     for (int n = 0; ok && n < N; ++n) {
                         const uint32_t kc = kv_cnt + n, g = sc0 + n, b = g & 1u;
                         const int s = kc % KS;
-                        if (!(ok = mbar_wait_bounded(&ctrl->k_full[s], (kc / KS) & 1u, abort_flag, p.status, 0x41))) break;
-                        if (g >= 2 && !(ok = mbar_wait_bounded(&ctrl->pv_done[b], ((g >> 1) + 1u) & 1u, abort_flag, p.status, 0x44))) break;
+                        if (!(ok = wait_all(&ctrl->k_full[s], (kc / KS) & 1u, abort_flag, p.status, 0x41))) break;
+                        if (g >= 2 && !(ok = wait_all(&ctrl->pv_done[b], ((g >> 1) + 1u) & 1u, abort_flag, p.status, 0x44))) break;
                         tc_fence_after();
                         issue_qk_to(b, s);
                         commit(&ctrl->s_full[b]);
@@ -988,8 +1009,8 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                     int nN = 0, nN0 = 0, nN1 = 0;
                     if (N > 0) {
                         const int s0 = kv_cnt % KS;
-                        ok = mbar_wait_bounded(&ctrl->q_full, q_cnt & 1u, abort_flag, p.status, 0x40) &&
-                             mbar_wait_bounded(&ctrl->k_full[s0], (kv_cnt / KS) & 1u, abort_flag, p.status, 0x41);
+                        ok = wait_all(&ctrl->q_full, q_cnt & 1u, abort_flag, p.status, 0x40) &&
+                             wait_all(&ctrl->k_full[s0], (kv_cnt / KS) & 1u, abort_flag, p.status, 0x41);
                         if (ok) {
                             tc_fence_after();
                             if (N0 > 0) { issue_qk(0, s0); commit(&ctrl->s_full[0]); }
@@ -1011,23 +1032,41 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                             // barriers are looked at here, under the wait for P that follows, because even a passing
                             // probe costs the issuing thread ~100 clocks -- between PV0 and QK0 those would be idle
                             // clocks of the tensor pipe
-                            if (!(ok = mbar_wait_bounded(&ctrl->v_full[s], ph, abort_flag, p.status, 0x42))) break;
+                            if (!(ok = wait_all(&ctrl->v_full[s], ph, abort_flag, p.status, 0x42))) break;
                             if (n + 1 < N) {
-                                if (!(ok = mbar_wait_bounded(&ctrl->k_full[s1], ph1, abort_flag, p.status, 0x44))) break;
+                                if (!(ok = wait_all(&ctrl->k_full[s1], ph1, abort_flag, p.status, 0x44))) break;
                             }
                             if (n < N0) {
-                                if (!(ok = mbar_wait_bounded(&ctrl->p_full[0], (sc0 + n) & 1u, abort_flag, p.status, 0x43))) break;
-                                tc_fence_after();
-                                issue_pv(0, s, n > 0);
+                                if constexpr (HALVES) {
+                                    if (!(ok = wait_all(&ctrl->p_full[0], (sc0 + n) & 1u, abort_flag, p.status, 0x43))) break;
+                                    tc_fence_after();
+                                    issue_pv(0, s, n > 0, 0);
+                                    if (!(ok = wait_all(&ctrl->p_full2[0], (sc0 + n) & 1u, abort_flag, p.status, 0x43))) break;
+                                    tc_fence_after();
+                                    issue_pv(0, s, true, 1);
+                                } else {
+                                    if (!(ok = wait_all(&ctrl->p_full[0], (sc0 + n) & 1u, abort_flag, p.status, 0x43))) break;
+                                    tc_fence_after();
+                                    issue_pv(0, s, n > 0);
+                                }
                                 if (n == N0 - 1) commit(&ctrl->o_full[0]);
                             } else {
                                 tc_fence_after();
                             }
                             if (n + 1 < N0) { issue_qk(0, s1); commit(&ctrl->s_full[0]); }
                             if (n < N1) {
-                                if (!(ok = mbar_wait_bounded(&ctrl->p_full[1], (sc1 + n) & 1u, abort_flag, p.status, 0x45))) break;
-                                tc_fence_after();
-                                issue_pv(1, s, n > 0);
+                                if constexpr (HALVES) {
+                                    if (!(ok = wait_all(&ctrl->p_full[1], (sc1 + n) & 1u, abort_flag, p.status, 0x45))) break;
+                                    tc_fence_after();
+                                    issue_pv(1, s, n > 0, 0);
+                                    if (!(ok = wait_all(&ctrl->p_full2[1], (sc1 + n) & 1u, abort_flag, p.status, 0x45))) break;
+                                    tc_fence_after();
+                                    issue_pv(1, s, true, 1);
+                                } else {
+                                    if (!(ok = wait_all(&ctrl->p_full[1], (sc1 + n) & 1u, abort_flag, p.status, 0x45))) break;
+                                    tc_fence_after();
+                                    issue_pv(1, s, n > 0);
+                                }
                                 if (n == N1 - 1) commit(&ctrl->o_full[1]);
                             }
                             commit(&ctrl->v_empty[s]);
@@ -1077,8 +1116,8 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                     for (int n = 0; n < N; ++n, ++g) {
                         const uint32_t kc = kv_cnt + n, b = g & 1u;
                         const int s = kc % KV_SLOTS;
-                        if (!(ok = mbar_wait_bounded(&ctrl->v_full[s], (kc / KV_SLOTS) & 1u, abort_flag, p.status, 0x42))) break;
-                        if (!(ok = mbar_wait_bounded(&ctrl->p_full[b], (g >> 1) & 1u, abort_flag, p.status, 0x43))) break;
+                        if (!(ok = __all_sync(0xffffffffu, mbar_wait_bounded(&ctrl->v_full[s], (kc / KV_SLOTS) & 1u, abort_flag, p.status, 0x42)))) break;
+                        if (!(ok = __all_sync(0xffffffffu, mbar_wait_bounded(&ctrl->p_full[b], (g >> 1) & 1u, abort_flag, p.status, 0x43)))) break;
                         tc_fence_after();
                         const uint64_t vd = s ? dV1 : dV0;
                         if (lead4) {
@@ -1347,11 +1386,24 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                     tmem_st32(tSb + (SPLIT == 2 ? khalf : c) * 32, pk);
                     }
                 };
+                // Prefill forms: P is handed over in two halves (a barrier each: with one barrier the second arrival could
+                // complete before the issuer has looked at the first), so that the PV of keys 0-63 is on the tensor pipe
+                // while the exponentials of keys 64-127 are taken.
+                auto hand_over_first_half = [&]() {
+                    if constexpr (HALVES) {
+                        tmem_wait_st();
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&ctrl->p_full[sb]);
+                    }
+                };
                 if (need_mask) {
                     exp_half(0, std::integral_constant<int, 0>{});
+                    hand_over_first_half();
                     if (SPLIT != 2) exp_half(1, std::integral_constant<int, 0>{});
                 } else {
                     exp_half(0, std::integral_constant<int, NPOLY8>{});
+                    hand_over_first_half();
                     if (SPLIT != 2) exp_half(1, std::integral_constant<int, NPOLY8>{});
                 }
                 if (SPLIT == 2) {  // this copy of the row gives the other 64 keys no weight
@@ -1364,7 +1416,7 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                 tmem_wait_st();
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&ctrl->p_full[sb]);
+                if (lane == 0) mbar_arrive(HALVES ? &ctrl->p_full2[sb] : &ctrl->p_full[sb]);
             }
             if (!ok) break;
             sc += Ni;
