@@ -511,12 +511,11 @@ __device__ __forceinline__ void get_item(const Ctrl* ctrl, const Sm100Dev& p, in
 //          (-slope * |i + sk - sq - j|, BiasEnum::ALIBI, fmha_library.h:124) -- applied to the score registers before
 //          the mask.
 // VAR bit 2 (BIAS): an elementwise bias tensor (BiasEnum::ELEMENTWISE_BIAS) is added to the scaled (and capped) scores.
-//          A softmax warp fetches the 32 x 128 bias values of its rows and key tile before it waits for S, so the
-//          loads travel under the QK^T: four lanes read 64 contiguous bytes of one row, eight rows per instruction (a
-//          thread reading its own row would touch 32 cache lines per instruction and thrash the small L1 that the
-//          tiles leave).  S is then read 32 columns at a time; the matching 32 x 32 bias block goes through the warp's
-//          2 KB of O staging (free until the epilogue) to the thread that owns the row.  Implies the score arithmetic of
-//          EXTRA.
+//          Each softmax thread fetches the 128 bias values of its row and key tile (256 contiguous bytes, sixteen
+//          16-byte loads; element loads for unaligned rows and the tail tile) before it waits for S, then reads S 32
+//          columns at a time and adds the bias words as it arrives, so that scores and bias are never live in full
+//          together.  (Fetching through the warp -- four lanes per row, the block handed on through shared memory --
+//          measured the same; fetching a step ahead spilled and lost.)  Implies the score arithmetic of EXTRA.
 // VAR bit 0 (WINDOW): the mask has a left window or a right window other than 0 (everything but no mask / causal); a separate
 // instance, so that the common masks do not carry the second bound of the visible range through the softmax loop.
 // SPLIT 1: the split-KV form described at Sm100Dev (one Q tile per item; work cut as described at kItemCostDefault).  The S
@@ -1197,14 +1196,6 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                 else off += (p.bias_el_rank == 2 ? (int64_t)it.b * p.hq * plane : 0) + (int64_t)row * p.bias_sk;
                 if (row_ok) bias_row = reinterpret_cast<const unsigned short*>(p.bias_el) + off;
             }
-            // the rows whose bias this lane fetches: rows 8 i + lane / 4 of the warp, 16-byte piece lane % 4 of each chunk
-            [[maybe_unused]] const unsigned short* fetch_row[BIAS ? 4 : 1];
-            if constexpr (BIAS) {
-#pragma unroll
-                for (int fi = 0; fi < 4; ++fi)
-                    fetch_row[fi] = reinterpret_cast<const unsigned short*>(
-                        __shfl_sync(0xffffffffu, (unsigned long long)bias_row, fi * 8 + (lane >> 2)));
-            }
             for (int n = 0; n < Ni; ++n) {
                 // warp-uniform outcome: the loads, votes and stores below are warp-collective
                 // The split modes have one Q tile and use the other tile's S columns as a second S buffer: the QK^T of
@@ -1216,15 +1207,10 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                 const int key0 = (it.n0 + n) * BN + khalf * 64;
                 [[maybe_unused]] const bool capped = EXTRA && p.soft_cap > 0.f;
                 [[maybe_unused]] const float inv_cap = capped ? 1.f / p.soft_cap : 0.f;
-                [[maybe_unused]] uint4 bw[BIAS ? 16 : 1];  // [chunk of 32 keys][row group]
-                if constexpr (BIAS) {  // (issued before the wait: the bytes arrive while the QK^T runs)
+                [[maybe_unused]] uint4 bw[BIAS ? 16 : 1];  // the 128 bias values of this thread's row and key tile
+                if constexpr (BIAS) {  // (issued before the wait for S)
 #pragma unroll
-                    for (int c = 0; c < 4; ++c)
-#pragma unroll
-                        for (int fi = 0; fi < 4; ++fi) {
-                            const int col = key0 + c * 32 + (lane & 3) * 8;
-                            bw[c * 4 + fi] = load_bias_piece(fetch_row[fi], col, sk - col);
-                        }
+                    for (int v = 0; v < 16; ++v) bw[v] = load_bias_piece(bias_row, key0 + v * 8, sk - key0 - v * 8);
                 }
                 ok = __all_sync(0xffffffffu, mbar_wait_bounded(&ctrl->s_full[sb], (SPLIT ? (gstep >> 1) : gstep) & 1u, abort_flag,
                                                                p.status, 0x100 << i));
@@ -1233,31 +1219,15 @@ fmha_fwd_sm100_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                 constexpr int NC = SPLIT == 2 ? 64 : 128;  // columns of the row this thread handles
                 uint32_t sreg[NC];
                 if constexpr (BIAS) {
-                    uint8_t* stage = sStage + warp * STAGE_BYTES;  // 32 rows x 64 bytes, 16-byte pieces rotated by row pair
-                    if (n == 0) {  // the previous item's last O store has read the staging buffer
-                        if (lane == 0) tma_store_wait_read();
-                        __syncwarp();
-                    }
 #pragma unroll
                     for (int c = 0; c < 4; ++c) {
                         tmem_ld32(tSb + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&sreg[c * 32]));
-#pragma unroll
-                        for (int fi = 0; fi < 4; ++fi) {
-                            const int r = fi * 8 + (lane >> 2);
-                            *reinterpret_cast<uint4*>(stage + r * 64 + (((lane & 3) ^ (r >> 1)) & 3) * 16) = bw[c * 4 + fi];
-                        }
-                        __syncwarp();
-                        uint32_t mine[16];  // this row's 32 values
-#pragma unroll
-                        for (int v4 = 0; v4 < 4; ++v4) {
-                            const uint4 x = *reinterpret_cast<const uint4*>(stage + lane * 64 + ((v4 ^ (lane >> 1)) & 3) * 16);
-                            mine[4 * v4] = x.x; mine[4 * v4 + 1] = x.y; mine[4 * v4 + 2] = x.z; mine[4 * v4 + 3] = x.w;
-                        }
-                        __syncwarp();  // (the rows are read before the next chunk overwrites them)
                         tmem_wait_ld();
 #pragma unroll
                         for (int j = 0; j < 32; ++j) {
-                            const float bj = bias_elem<T>(mine[j >> 1], j & 1), sj = __uint_as_float(sreg[c * 32 + j]);
+                            const uint4 q4 = bw[c * 4 + (j >> 3)];
+                            const uint32_t w = ((j >> 1) & 3) == 0 ? q4.x : ((j >> 1) & 3) == 1 ? q4.y : ((j >> 1) & 3) == 2 ? q4.z : q4.w;
+                            const float bj = bias_elem<T>(w, j & 1), sj = __uint_as_float(sreg[c * 32 + j]);
                             float x;
                             if (capped) x = (p.soft_cap * tanh_inline(sj * p.scale * inv_cap) + bj) * kLog2e;
                             else x = fmaf(sj, p.scale_log2, bj * kLog2e);  // (the two products of the sum in base-2 units)
